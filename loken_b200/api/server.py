@@ -86,7 +86,7 @@ def ops_router(ctx: ServerContext):
 
     def _describe() -> dict:
         models = ctx.registry.list()
-        free = sum(m.engine.alloc.num_free() for m in models if hasattr(m.engine.alloc, "num_free"))
+        free = sum(m.engine.alloc.free_blocks() for m in models)
         return {"models": [m.model_id for m in models], "load": float(sum(len(m.worker.tickets) for m in models)),
                 "tok_per_s": 0.0, "free_kv_blocks": int(free)}
 
@@ -130,7 +130,7 @@ def ops_router(ctx: ServerContext):
         for m in ctx.registry.list():
             a = m.engine.alloc
             tag = m.model_id.replace('"', "")
-            g[f'loken_kv_blocks_free{{model="{tag}"}}'] = a.num_free() if hasattr(a, "num_free") else 0
+            g[f'loken_kv_blocks_free{{model="{tag}"}}'] = a.free_blocks()
             g[f'loken_engine_steps_total{{model="{tag}"}}'] = m.engine.stats.steps
             g[f'loken_preemptions_total{{model="{tag}"}}'] = m.engine.stats.preemptions
             g[f'loken_requests_running{{model="{tag}"}}'] = len(m.worker.tickets)
@@ -141,10 +141,12 @@ def ops_router(ctx: ServerContext):
 
     @r.post("/reset_prefix_cache")
     async def reset_prefix_cache():
+        from starlette.concurrency import run_in_threadpool
+
+        # the allocator belongs to the engine thread: the drop runs there, between two steps
         n = 0
         for m in ctx.registry.list():
-            if hasattr(m.engine.alloc, "reset_prefix_cache"):
-                n += m.engine.alloc.reset_prefix_cache()
+            n += int(await run_in_threadpool(m.on_engine_thread, lambda eng: eng.reset_prefix_cache()) or 0)
         return {"status": "ok", "blocks_dropped": n}
 
     @r.get("/api/inflight")

@@ -83,8 +83,9 @@ def serve(cfg, requant=None) -> int:
             comm.fused_gemm = i.tp_sum == "fused"
     llm = LLM.load(i.model, model_id=i.model_id, requant=requant, kv_format=cfg.kv_format, tp_rank=rank,
                    tp_size=world, comm=comm, max_seqs=i.max_seqs, max_ctx=i.max_ctx,
-                   max_prefill_tokens=i.max_prefill_tokens, lora=i.lora)
-    if i.draft_model:
+                   max_prefill_tokens=i.max_prefill_tokens, lora=i.lora,
+                   **({"draft": (i.draft_model, i.draft_k)} if (i.draft_model and world > 1) else {}))
+    if i.draft_model and world == 1:
         from ..serve.speculative import attach_draft
 
         attach_draft(llm, i.draft_model, k=i.draft_k)
@@ -93,7 +94,7 @@ def serve(cfg, requant=None) -> int:
     if rank != 0:
         from ..parallel.follower import follow
 
-        return follow(llm, llm.control_group)
+        return follow(llm, llm.control_group, llm.watchdog)
     reg = ModelRegistry()
     reg.add(llm, default=True)
     http_serve(reg, ServerSettings(host=s.host, port=s.port, api_keys=s.api_keys, require_auth=s.require_auth,

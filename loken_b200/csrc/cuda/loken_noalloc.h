@@ -16,11 +16,16 @@
 //   * The array holds LK_DECODE_STATIC_WS_FLOATS floats of partial results and
 //     LK_DECODE_STATIC_COUNTERS arrival counters.  A call needs
 //     lk_attn_decode_ws_floats(rows, n_q, n_kv, hd, nsplit) floats and rows * n_kv counters;
-//     a call that needs more returns LKH_TOO_LARGE (-4) and launches nothing.
+//     a call that needs more returns LKH_TOO_LARGE (-4) and launches nothing.  A call with
+//     nsplit <= 1 uses neither and is never refused for its size.
 //     lk_attn_decode_static_limits() reports both limits.
-//   * The first call on each device looks up the array's address (cudaGetSymbolAddress, with
-//     that device current) and remembers it.  Make that first call during start-up, outside any
-//     stream capture; later calls on that device only enqueue work on the given stream.
+//   * The first call in each CUDA context looks up the array's address (cudaGetSymbolAddress, with
+//     that context's device current) and remembers it for that context: the address is a
+//     property of the context, so a plug-in called from several contexts on one device, or after
+//     the host program reset the device, gets the array of the context it is called in.  Make
+//     that first call during start-up, outside any stream capture; later calls in that context
+//     only enqueue work on the given stream.  At most 64 contexts are remembered; beyond that
+//     (or when the driver's context query is unavailable) the address is looked up on every call.
 //   * Every call clears the counters it is about to use on the caller's stream before the
 //     kernel runs, so a call that was abandoned half-way cannot poison the next one.
 //   * All calls on a device share the one array.  Calls ordered on one stream are safe.  Two

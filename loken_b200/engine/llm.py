@@ -189,6 +189,7 @@ class LLM:
         engine.eos.update(ends)          # in place: `engine` may be a lock-step wrapper
         engine.runner.end_ids = sorted(engine.eos)
         self.control_group = None
+        self.watchdog = None
         from ..text.grammar import GrammarSession
 
         factory = lambda spec: GrammarSession(tokenizer, spec[0], spec[1])
@@ -210,13 +211,25 @@ class LLM:
         (directory, weight) pairs, merged into a bf16 / block-fp8 checkpoint as it loads."""
         dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         group = None
+        watchdog = None
+        draft = engine_kw.pop("draft", None)       # (model, k): a drafter attached on every rank before wrapping
         if tp_size > 1:
+            import torch.distributed as dist
+
             from ..parallel.follower import LockstepEngine, control_group
+            from ..parallel.watchdog import RankWatchdog
 
             group = control_group()          # collective: every rank creates it here
+            store = getattr(dist.distributed_c10d, "_get_default_store", lambda: None)()
+            if store is not None:
+                watchdog = RankWatchdog(store, tp_rank, tp_size, interval_s=1.0, timeout_s=15.0).start()
 
         def wrap(eng):
-            return LockstepEngine(eng, group) if tp_size > 1 and tp_rank == 0 else eng
+            if draft is not None:
+                from ..serve.speculative import attach_draft_engine
+
+                attach_draft_engine(eng, draft[0], k=draft[1], tp_rank=tp_rank, tp_size=tp_size, comm=comm)
+            return LockstepEngine(eng, group, watchdog) if tp_size > 1 and tp_rank == 0 else eng
 
         if os.path.isdir(model) and os.path.exists(os.path.join(model, "config.json")):
             # a Hugging Face checkpoint directory (bf16 or block-fp8 safetensors + tokenizer.json)
@@ -248,7 +261,7 @@ class LLM:
                 tk = ByteTokenizer(w.cfg.vocab)
             eng = LLMEngine(w.cfg, weights=w, device=dev, tp_rank=tp_rank, tp_size=tp_size, comm=comm, **engine_kw)
             llm = cls(wrap(eng), tk, model_id or os.path.basename(os.path.normpath(model)), hf, path=model)
-            llm.control_group = group
+            llm.control_group, llm.watchdog = group, watchdog
             return llm
         if lora:
             raise ValueError("adapters merge into a Hugging Face checkpoint directory (bf16 or block-fp8)")
@@ -261,14 +274,14 @@ class LLM:
             eng = LLMEngine(w.cfg, weights=w, device=dev, tp_rank=tp_rank, tp_size=tp_size, comm=comm, **engine_kw)
             name = model_id or os.path.splitext(os.path.basename(model))[0]
             llm = cls(wrap(eng), tk, name, meta, path=model)
-            llm.control_group = group
+            llm.control_group, llm.watchdog = group, watchdog
             return llm
         cfg = get_config(model)
         if kv_format:
             cfg.kv_format = kv_format
         eng = LLMEngine(cfg, device=dev, seed=seed, tp_rank=tp_rank, tp_size=tp_size, comm=comm, **engine_kw)
         llm = cls(wrap(eng), ByteTokenizer(cfg.vocab), model_id or model, {"general.architecture": cfg.arch})
-        llm.control_group = group
+        llm.control_group, llm.watchdog = group, watchdog
         return llm
 
     def close(self):

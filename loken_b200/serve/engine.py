@@ -115,6 +115,10 @@ class LLMEngine:
             raise ValueError("empty prompt")
         if len(prompt) >= self.max_ctx:
             raise ValueError(f"prompt of {len(prompt)} tokens does not fit the {self.max_ctx}-token window")
+        if self.alloc.blocks_needed(len(prompt) + 1 + self.sched.lookahead) > self.alloc.num_blocks:
+            # refused before an id is taken, so ranks that mirror this engine keep the same ids
+            raise ValueError(f"a request of {len(prompt)} tokens needs more KV blocks than the pool has "
+                             f"({self.alloc.num_blocks} x {self.alloc.block_size} tokens)")
         sid = self.next_id
         self.next_id += 1
         seq = Sequence(sid, list(prompt), params, arrival=time.perf_counter(), salt=salt)
@@ -162,6 +166,10 @@ class LLMEngine:
         n = import_sequence(self.runner, self.alloc, tmp, blob, salt)
         self.alloc.free(tmp)     # the blocks stay published (evictable) under their content hashes
         return n
+
+    def reset_prefix_cache(self) -> int:
+        """Drops the idle cached blocks; returns how many.  Call between steps."""
+        return int(self.alloc.reset_prefix_cache() or 0)
 
     def embed(self, tokens, pooling: str = "last"):
         """Unit-norm embedding of a prompt (not batched with generation; call between steps)."""
@@ -237,6 +245,8 @@ class LLMEngine:
         self.cancelled.clear()
         plan = self.sched.schedule()
         self.stats.preemptions += len(plan.preempted)
+        for seq in plan.rejected:
+            outs[seq.seq_id] = StepOutput(seq.seq_id, [], True, "error")
         if plan.empty:
             return list(outs.values())
         lps: Dict[int, tuple] = {}

@@ -195,12 +195,20 @@ class PagedKvAllocator:
         for b in reversed(s.blocks):
             self._release(b)
 
-    def reset_prefix_cache(self):
+    def num_free(self) -> int:
+        """Blocks a new sequence could take right now (free list + idle cached blocks)."""
+        return self.free_blocks()
+
+    def reset_prefix_cache(self) -> int:
+        """Drops every idle cached block; returns how many went back to the free list.  Blocks
+        still referenced by a running sequence stay published."""
+        dropped = len(self.evictable)
         for b in list(self.evictable):
             self.block_hash[b] = None
             self.free_list.append(b)
         self.evictable.clear()
         self.cached = {h: b for h, b in self.cached.items() if self.ref[b] > 0}
+        return dropped
 
     # ---- views ----
     def length(self, seq_id: int) -> int:

@@ -9,7 +9,10 @@ Semantics follow the reference's `Scheduler` (`src/inference/serve/scheduler.rs:
      sequences run and the step's prefill tokens stay within `max_prefill_tokens` (the first
      prefill of a step is always admitted, so a long prompt cannot starve);
   3. admission goes through the prefix cache, so only the uncached suffix is prefilled;
-  4. `trim` cuts a sequence back after a speculative reject.
+  4. `trim` cuts a sequence back after a speculative reject;
+  5. a request the pool can never hold (its prompt, or its prompt plus what it had generated before
+     a preemption, needs more blocks than exist) is finished with reason "error" instead of waiting
+     for ever at the head of the first-come-first-served queue.
 A prompt longer than `max_prefill_tokens` is read in chunks over several steps.
 """
 from __future__ import annotations
@@ -64,6 +67,7 @@ class StepPlan:
     prefills: List[PrefillItem] = field(default_factory=list)
     decodes: List[Sequence] = field(default_factory=list)
     preempted: List[Sequence] = field(default_factory=list)
+    rejected: List[Sequence] = field(default_factory=list)   # finished with "error": the pool can never hold them
 
     @property
     def empty(self) -> bool:
@@ -81,9 +85,15 @@ class Scheduler:
         self.running: List[Sequence] = []   # admission order: oldest first
         self.finished: List[Sequence] = []
 
+    def fits_pool(self, seq: Sequence) -> bool:
+        """Could the whole pool, with nothing else in it, hold this sequence and its next token?"""
+        return self.alloc.blocks_needed(seq.total_len + 1 + self.lookahead) <= self.alloc.num_blocks
+
     def add_request(self, seq: Sequence):
         seq.state = "waiting"
         self.waiting.append(seq)
+        if not self.fits_pool(seq):
+            self.finish(seq, "error")
 
     def has_work(self) -> bool:
         return bool(self.waiting or self.running)
@@ -139,11 +149,21 @@ class Scheduler:
         # 3. admit waiting requests FCFS
         while self.waiting and len(self.running) < self.max_running:
             seq = self.waiting[0]
+            if not self.fits_pool(seq):
+                # grown past the pool while it ran (preempted with its output): it can never come back
+                self.finish(seq, "error")
+                plan.rejected.append(seq)
+                continue
             toks = seq.tokens
             if plan.prefills and budget <= 0:
                 break
             cached = self.alloc.allocate_with_prefix(seq.seq_id, toks, seq.salt)
             if cached is None:
+                if not self.running and not plan.prefills and not plan.decodes:
+                    # nothing runs, so nothing will ever free a block for it
+                    self.finish(seq, "error")
+                    plan.rejected.append(seq)
+                    continue
                 break
             uncached = len(toks) - cached
             if plan.prefills and uncached > budget and uncached <= self.max_prefill_tokens:

@@ -323,8 +323,20 @@ class Speculator:
 
 def attach_draft(llm, draft: Optional[str], k: int = 4, method: str = "model") -> dict:
     """Attaches a drafter to a loaded model at run time (`/api/draft/attach`).  `draft` is a GGUF
-    path or a built-in shape name; the drafter must share the target's vocabulary."""
-    eng = llm.engine
+    path or a built-in shape name; the drafter must share the target's vocabulary.  Under tensor
+    parallelism a drafter is attached on every rank at load time instead (`LLM.load(draft=...)`):
+    the ranks' schedules have to change at the same step."""
+    if hasattr(llm.engine, "_e"):
+        raise RuntimeError("under tensor parallelism a drafter is attached on every rank at load time "
+                           "([inference] draft_model / --draft-model), not at run time")
+    return attach_draft_engine(llm.engine, draft, k, method)
+
+
+def attach_draft_engine(eng, draft: Optional[str], k: int = 4, method: str = "model", tp_rank: int = 0,
+                        tp_size: int = 1, comm=None) -> dict:
+    """The same on a bare engine.  Every tensor-parallel rank holds a whole copy of the (small)
+    drafter and runs it redundantly, so all ranks propose the same tokens without a collective."""
+    del tp_rank, tp_size, comm
     if method == "prompt_lookup" or not draft:
         drafter = PromptLookupDrafter()
     else:

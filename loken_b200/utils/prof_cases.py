@@ -6,6 +6,9 @@
     python -m loken_b200.utils.prof_cases decode_step --layers 4 --batch 64 --ctx 1024 [--tp 8]
     python -m loken_b200.utils.prof_cases attn_decode --batch 64 --ctx 1024
     python -m loken_b200.utils.prof_cases sampler --batch 64
+    python -m loken_b200.utils.prof_cases attn_prefill --seqs 8 --ctx 2048
+    python -m loken_b200.utils.prof_cases add_rmsnorm --batch 64      # also glu, rope_kv, embed
+    python -m loken_b200.utils.prof_cases moe --batch 128 --fmt mxfp4
 
 Each case warms up, then runs the measured launches between cudaProfilerStart/Stop, so a
 profiler started with `--profile-from-start off` sees only those.  Inputs are larger than the L2
@@ -152,10 +155,120 @@ def sampler_case(batch: int, vocab: int):
     print(f"sampler batch={batch} vocab={vocab}: {ms * 1e3:.1f} us, {batch * vocab * 4 / ms / 1e6:.0f} GB/s of logits")
 
 
+def attn_prefill_case(n_seqs: int, ctx: int, n_q: int, n_kv: int):
+    """Variable-length flash prefill over keys gathered from the q8 paged cache (kv_gather +
+    attn_prefill_kernel), `n_seqs` prompts of `ctx` tokens."""
+    from ..ops import attention, rows
+
+    hd, bs = 128, 16
+    nb = (ctx + bs - 1) // bs
+    cache = rows.KVCacheLayer(n_seqs * nb * bs, n_kv, hd, "cuda", q8=True)
+    cache.k.copy_(torch.randint(-127, 128, cache.k.shape, device="cuda").to(torch.int8))
+    cache.v.copy_(torch.randint(-127, 128, cache.v.shape, device="cuda").to(torch.int8))
+    cache.k_scale.fill_(0.01)
+    cache.v_scale.fill_(0.01)
+    bt = torch.arange(n_seqs * nb, device="cuda", dtype=torch.int32).view(n_seqs, nb)
+    plan = attention.plan_prefill([ctx] * n_seqs, [ctx] * n_seqs, n_q // n_kv, "cuda")
+    q = torch.randn(n_seqs * ctx, n_q, hd, device="cuda").bfloat16()
+    out = torch.empty(n_seqs * ctx, n_q * hd, device="cuda", dtype=torch.bfloat16)
+    kbuf, vtbuf = attention.kv_gather(cache, bt, plan, bs)
+
+    def fn():
+        attention.kv_gather(cache, bt, plan, bs, kbuf, vtbuf)
+        attention.prefill(q, kbuf, vtbuf, plan, out=out)
+
+    for _ in range(3):
+        fn()
+    ms = _bracket(fn)
+    flops = 4.0 * n_seqs * n_q * hd * ctx * ctx / 2
+    print(f"attn_prefill seqs={n_seqs} ctx={ctx} n_q={n_q} n_kv={n_kv}: {ms * 1e3:.1f} us (gather + attention), "
+          f"{flops / ms / 1e9:.1f} TFLOP/s causal")
+
+
+def rows_case(which: str, T: int, H: int, I: int):
+    """The row kernels of a decode step at `T` rows: add_rmsnorm (+ e4m3 quantise), glu (+ quantise),
+    rope_kv (q/k norm + RoPE + q8 paged KV write), embed.  Buffers rotate through more than the L2."""
+    from ..ops import rows
+
+    nrot = max(1, (160 << 20) // max(1, T * max(H, 2 * I) * 2))
+    if which == "add_rmsnorm":
+        xs = [torch.randn(T, H, device="cuda").bfloat16() for _ in range(nrot)]
+        d = torch.randn(T, H, device="cuda").bfloat16()
+        w = torch.ones(H, device="cuda")
+        o8 = rows.alloc_fp8_act(T, H, "cuda")
+        it = [0]
+
+        def fn():
+            it[0] = (it[0] + 1) % nrot
+            rows.add_rmsnorm(xs[it[0]], w, 1e-5, delta=d, out_fp8=o8, rows=T)
+        nbytes = T * H * (2 + 2 + 2 + 1)
+    elif which == "glu":
+        gs = [torch.randn(T, 2 * I, device="cuda").bfloat16() for _ in range(nrot)]
+        o8 = rows.alloc_fp8_act(T, I, "cuda")
+        it = [0]
+
+        def fn():
+            it[0] = (it[0] + 1) % nrot
+            rows.glu(gs[it[0]], out_fp8=o8, rows=T)
+        nbytes = T * I * (4 + 1)
+    elif which == "rope_kv":
+        n_q, n_kv, hd = 64, 8, 128
+        qkv = torch.randn(T, (n_q + 2 * n_kv) * hd, device="cuda").bfloat16()
+        cache = rows.KVCacheLayer(T * 64, n_kv, hd, "cuda", q8=True)
+        pos = torch.arange(T, device="cuda", dtype=torch.int32)
+        slots = (torch.arange(T, device="cuda", dtype=torch.int32) * 61) % (T * 64)
+        inv = 1.0 / (5e5 ** (torch.arange(0, hd, 2, device="cuda").float() / hd))
+        qo = torch.empty(T, n_q, hd, device="cuda", dtype=torch.bfloat16)
+        fn = lambda: rows.rope_kv(qkv, pos, slots, cache, n_q, inv, pairing=0, q_out=qo, rows=T)
+        nbytes = T * (n_q + 2 * n_kv) * hd * 2 + T * n_q * hd * 2 + T * 2 * n_kv * hd
+    else:
+        V = 128256
+        table = torch.randn(V, H, device="cuda").bfloat16()
+        tok = torch.randint(0, V, (T,), device="cuda", dtype=torch.int32)
+        out = torch.empty(T, H, device="cuda", dtype=torch.bfloat16)
+        fn = lambda: rows.embed(tok, table, out=out)
+        nbytes = T * H * 4
+    for _ in range(3):
+        fn()
+    ms = _bracket(fn)
+    print(f"{which} T={T} H={H} I={I}: {ms * 1e3:.2f} us, {nbytes / ms / 1e6:.0f} GB/s")
+
+
+def moe_case(T: int, fmt: str, experts: int, top_k: int, H: int, I: int):
+    """One gpt-oss-shaped mixture layer on one GPU: router GEMM, lk_moe_route, lk_moe_plan,
+    lk_moe_permute, grouped gate_up GEMM, clamped GLU, grouped down GEMM, lk_moe_combine."""
+    from ..models.config import get_config
+    from ..models.moe import MoeRunner, random_moe
+
+    cfg = dataclasses.replace(get_config("gpt-oss-120b"), n_experts=experts, top_k=top_k, hidden=H,
+                              expert_intermediate=I, weight_format=fmt, n_layers=1)
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    moe = random_moe(cfg, gen, "cuda", 0.02)
+
+    class _W:
+        pass
+    w = _W()
+    w.embed = torch.zeros(1, device="cuda")
+    lay = _W()
+    lay.moe = moe
+    w.layers = [lay]
+    run = MoeRunner(cfg, w, T)
+    h = torch.randn(T, H, device="cuda").bfloat16()
+    out = torch.empty(T, H, device="cuda", dtype=torch.bfloat16)
+    fn = lambda: run.forward(0, moe, h, out, T)
+    for _ in range(3):
+        fn()
+    ms = _bracket(fn)
+    wb = (moe.gate_up.nbytes() + moe.down.nbytes()) if fmt != "bf16" else (moe.gate_up.numel() + moe.down.numel()) * 2
+    print(f"moe T={T} fmt={fmt} experts={experts} top_k={top_k} H={H} I={I}: {ms * 1e3:.1f} us per layer, "
+          f"expert weights {wb / 1e6:.0f} MB ({wb / ms / 1e6:.0f} GB/s if all were read)")
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("case", choices=["gemm_fp8", "gemm_bf16", "gemm_q8_0", "gemm_q4_k", "gemm_q6_k", "gemm_mxfp4",
-                                    "decode_step", "attn_decode", "sampler"])
+                                    "decode_step", "attn_decode", "sampler", "attn_prefill", "add_rmsnorm", "glu",
+                                    "rope_kv", "embed", "moe"])
     ap.add_argument("--m", type=int, default=64)
     ap.add_argument("--n", type=int, default=57344)
     ap.add_argument("--k", type=int, default=8192)
@@ -167,6 +280,12 @@ def main(argv=None):
     ap.add_argument("--n-q", type=int, default=64)
     ap.add_argument("--n-kv", type=int, default=8)
     ap.add_argument("--vocab", type=int, default=128256)
+    ap.add_argument("--seqs", type=int, default=8, help="attn_prefill: number of prompts")
+    ap.add_argument("--hidden", type=int, default=8192)
+    ap.add_argument("--inter", type=int, default=28672)
+    ap.add_argument("--fmt", default="mxfp4", help="moe: expert weight format (mxfp4 | bf16 | q8_0 | q4_k)")
+    ap.add_argument("--experts", type=int, default=128)
+    ap.add_argument("--top-k", type=int, default=4)
     ap.add_argument("--swap-max-m", type=int, default=-1, help="fp8 GEMM: largest M run with weights on the MMA M side")
     ap.add_argument("--gemm-splits", type=int, default=0, help="K splits of a GEMM with fewer tiles than SMs (0 = the library's choice)")
     ap.add_argument("--bn", type=int, default=0, help="fp8 GEMM: N-tile width of the tokens-on-M form (0 = the library's choice)")
@@ -178,6 +297,13 @@ def main(argv=None):
         decode_step_case(a.layers, a.batch, a.ctx, a.tp, a.model)
     elif a.case == "attn_decode":
         attn_decode_case(a.batch, a.ctx, a.n_q, a.n_kv, a.splits)
+    elif a.case == "attn_prefill":
+        attn_prefill_case(a.seqs, a.ctx, a.n_q, a.n_kv)
+    elif a.case in ("add_rmsnorm", "glu", "rope_kv", "embed"):
+        rows_case(a.case, a.batch, a.hidden, a.inter)
+    elif a.case == "moe":
+        moe_case(a.batch, a.fmt, a.experts, a.top_k, a.hidden if a.hidden != 8192 else 2880,
+                 a.inter if a.inter != 28672 else 2880)
     else:
         sampler_case(a.batch, a.vocab)
 

@@ -9,6 +9,7 @@ import torch
 
 from loken_b200.models.config import tiny
 from loken_b200.serve.engine import EngineStats, StepOutput
+from loken_b200.serve.kv_manager import PagedKvAllocator
 from loken_b200.serve.params import SamplingParams
 
 
@@ -30,7 +31,8 @@ class FakeEngine:
         self.max_ctx = max_ctx
         self.eos = {257}
         self.runner = types.SimpleNamespace(end_ids=[257], model=None)
-        self.alloc = types.SimpleNamespace(num_free=lambda: 100, reset_prefix_cache=lambda: 3)
+        # the real allocator: the ops routes are tested against the API the engine really has
+        self.alloc = PagedKvAllocator(100, 16)
         self.seqs: Dict[int, FakeSeq] = {}
         self.rngs: Dict[int, object] = {}
         self.cancelled = set()
@@ -53,6 +55,9 @@ class FakeEngine:
 
     def abort(self, sid):
         self.cancelled.add(sid)
+
+    def reset_prefix_cache(self) -> int:
+        return int(self.alloc.reset_prefix_cache() or 0)
 
     def layer_perf(self, n_tokens=1):
         return [{"stage": "embed", "ms": 0.01}, {"stage": "layer 0", "ms": 0.1}, {"stage": "head", "ms": 0.02}]

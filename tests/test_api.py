@@ -159,12 +159,23 @@ def test_auth_rate_limit_and_ops():
     assert c.get("/v1/models", headers={"x-api-key": "k1"}).status_code == 200
     r = c.get("/v1/models", headers=h)
     assert r.status_code == 429 and int(r.headers["retry-after"]) >= 1
-    c2, _ = client()
+    c2, reg2 = client()
     c2.post("/v1/completions", json={"prompt": "x", "max_tokens": 3})
     m = c2.get("/metrics").text
     assert 'loken_requests_total{model="fake-model",finish_reason="length"} 1' in m
     assert "loken_generation_tokens_total" in m and "loken_gate_active 0" in m
+    # three full blocks published by a finished sequence become idle cached blocks; the route drops
+    # them on the engine thread and the freed capacity shows in /metrics and the gossip payload
+    alloc = reg2.get(None).engine.alloc
+    toks = list(range(50))
+    assert alloc.allocate_with_prefix(7, toks) == 0
+    alloc.commit_prefix(7, toks)
+    alloc.free(7)
+    assert len(alloc.evictable) == 3 and alloc.free_blocks() == 100
+    assert 'loken_kv_blocks_free{model="fake-model"} 100' in c2.get("/metrics").text
     assert c2.post("/reset_prefix_cache").json()["blocks_dropped"] == 3
+    assert len(alloc.evictable) == 0 and len(alloc.free_list) == 100
+    assert c2.get("/api/cluster/state").json()["self_state"]["free_kv_blocks"] == 100
     assert c2.get("/api/inflight").json()["requests"] == []
     assert c2.get("/api/stage_perf").json() == {"stages": []}
 

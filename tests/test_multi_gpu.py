@@ -31,8 +31,7 @@ def test_peer_memory_allreduce(tmp_path):
     n = min(_ngpu(), 8)
     n = 8 if n >= 8 else 4 if n >= 4 else 2
     rep = _run("mp_collectives_worker.py", n, str(tmp_path / "ar.json"), 29631)
-    os.makedirs(os.path.join(os.path.dirname(HERE), "gpurun_out"), exist_ok=True)
-    json.dump(rep, open(os.path.join(os.path.dirname(HERE), "gpurun_out", f"allreduce_{n}gpu.json"), "w"), indent=1)
+    print(json.dumps(rep))          # the timing table, for `pytest -s`
     assert rep["ok"], rep
     assert rep["timeout_reported"] is True
     assert rep["recovers_after_timeout"] is True

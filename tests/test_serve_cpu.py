@@ -149,3 +149,74 @@ def test_prompt_lookup_and_draft_length():
         bad.observe_plain(0.008)
     assert bad.holdoff == 0
     assert DraftLength(fixed=4).choose() == 4
+
+
+def test_request_that_can_never_fit_is_rejected_not_queued_for_ever():
+    a = PagedKvAllocator(4, 16)
+    s = Scheduler(a, max_running=8, max_prefill_tokens=512)
+    big = Sequence(1, list(range(100)), GREEDY)      # needs 7 blocks of a 4-block pool
+    s.add_request(big)
+    assert big.state == "finished" and big.finish_reason == "error" and not s.has_work()
+    # a sequence that outgrew the pool while it ran (preempted with its output) is dropped at readmission
+    ok = Sequence(2, list(range(40)), GREEDY)
+    s.add_request(ok)
+    plan = s.schedule()
+    assert [it.seq.seq_id for it in plan.prefills] == [2]
+    s.on_step_done(plan)
+    ok.output = list(range(30))
+    s._preempt(ok)
+    plan = s.schedule()
+    assert plan.empty and plan.rejected == [ok] and ok.finish_reason == "error" and not s.has_work()
+    # a prompt that fits the pool but not what is free now waits while something runs, and is
+    # finished once nothing is left that could free a block
+    a2 = PagedKvAllocator(4, 16)
+    s2 = Scheduler(a2, max_running=8, max_prefill_tokens=512)
+    assert a2.allocate(99, 40)                       # blocks held by somebody outside the scheduler
+    waiting = Sequence(3, list(range(40)), GREEDY)
+    s2.add_request(waiting)
+    plan = s2.schedule()
+    assert plan.empty and plan.rejected == [waiting] and not s2.has_work()
+
+
+def test_handover_import_checks_the_container_before_it_allocates():
+    import types
+
+    import torch
+
+    from loken_b200.cluster.handover import export_sequence, import_sequence
+    from loken_b200.models.config import tiny
+    from loken_b200.ops.rows import KVCacheLayer
+
+    def engine(n_layers=2, name="a"):
+        cfg = tiny("llama", n_layers=n_layers)
+        cfg.name = name
+        kv = [KVCacheLayer(8 * 16, 2, cfg.head_dim, "cpu", q8=True) for _ in range(n_layers)]
+        runner = types.SimpleNamespace(cfg=cfg, kv=kv, device=torch.device("cpu"),
+                                       w=types.SimpleNamespace(n_kv_local=2))
+        return runner, PagedKvAllocator(8, 16)
+
+    src, sa = engine()
+    toks = list(range(40))
+    assert sa.allocate(1, 40)
+    for l in src.kv:
+        l.k.random_(-100, 100)
+        l.v.random_(-100, 100)
+        l.k_scale.fill_(0.5)
+        l.v_scale.fill_(0.25)
+    blob = export_sequence(src, sa, 1, toks)
+    dst, da = engine()
+    assert import_sequence(dst, da, 5, blob) == 40
+    s_src = torch.tensor(sa.slots_for_range(1, 0, 40))
+    s_dst = torch.tensor(da.slots_for_range(5, 0, 40))
+    assert torch.equal(dst.kv[1].k[s_dst], src.kv[1].k[s_src])
+    da.free(5)
+    free0 = da.free_blocks()
+    # wrong layer count, another model, a short payload, a token list that does not match
+    for bad_engine, bad_blob in ((engine(n_layers=3), blob), (engine(name="b"), blob), (engine(), blob[:-7]),
+                                 (engine(), blob.replace(b'"n": 40', b'"n": 39'))):
+        r, al = bad_engine
+        f0 = al.free_blocks()
+        with pytest.raises(ValueError):
+            import_sequence(r, al, 9, bad_blob)
+        assert al.free_blocks() == f0 and 9 not in al.seqs
+    assert da.free_blocks() == free0
