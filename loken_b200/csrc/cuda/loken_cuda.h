@@ -166,6 +166,11 @@ int lk_symm_view_size(void);
 void lk_allreduce_set_mode(int mode);   /* 0 auto, 1 one-shot, 2 two-shot; the same on every rank */
 int lk_allreduce_push(const void* view, void* data, int rows, int cols, long long ld, const void* residual,
                       int* status, void* stream);
+// Row-parallel layer boundary in one kernel: reduce-scatter of the ranks' partial rows, residual add
+// and RMSNorm on the owner of each row, (e4m3 quantise,) all-gather of the normalised rows (tp_fused.cu).
+int lk_tp_sum_norm(const void* view, const void* partial, long long ld_p, void* x, long long ld_x, const float* w,
+                   float eps, int T, int H, void* out_bf16, long long ld_o, void* out_fp8, float* scales_t,
+                   long long scale_ld, int gather, int* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -4,6 +4,9 @@
 //   [0, 64)                 control words: epoch, finished-CTA counter
 //   flags_off               flags[2 halves][MAX_RANKS sources][max_chunks] : unsigned epoch values
 //   recv_off                recv[2 halves][MAX_RANKS sources][slot_bytes]  : payload slots
+//   ll_off                  ll[2 halves][ll_half_bytes] : flag-in-data areas (tp_fused.cu, ep_moe.cu), zero at
+//                           allocation; inside a half, [0, ll_hop2_off) takes the first hop of a collective and
+//                           [ll_hop2_off, ll_half_bytes) the second
 // A collective takes the next epoch number; the half in use is epoch & 1.
 #pragma once
 #include <cuda_runtime.h>
@@ -20,6 +23,7 @@ struct SymmView {
   long long flags_off, recv_off, slot_bytes;
   int max_chunks;
   int pad;
+  long long ll_off, ll_half_bytes, ll_hop2_off;
 };
 
 #ifndef LK_PEER_WAIT_CYCLES

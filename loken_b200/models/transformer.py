@@ -9,6 +9,14 @@ captured in a CUDA graph as is.  Per layer (dense, block-fp8):
   add+RMSNorm(+e4m3 quantise) -> qkv GEMM -> q/k norm + RoPE + paged KV write -> attention
   (-> e4m3) -> o_proj GEMM [-> sum over tensor-parallel ranks] -> add+RMSNorm(+quantise)
   -> gate_up GEMM -> SwiGLU(+quantise) -> down GEMM [-> sum over ranks]
+
+Under tensor parallelism with symmetric memory and a decode-size step, the sum over ranks, the
+residual add, the norm and the quantise of each boundary are ONE kernel (`SymmComm.sum_norm`,
+csrc/cuda/tp_fused.cu) and the residual stream is sharded by rows between the row-parallel
+layers: a rank only ever updates and normalises the rows it owns, and the all-gather carries the
+next GEMM's e4m3 input.  The reference keeps the stream replicated and runs all-reduce, add and
+norm as separate launches over every row on every card
+(`src/inference/generic_transformer/tp_forward.rs:70-128`).
 """
 from __future__ import annotations
 
@@ -172,35 +180,52 @@ class DecoderModel:
         assert T <= self.buf.cap
         rows.embed(inp.tokens[:T], self.w.embed, out=self.buf.x[:T], scale=self.cfg.embedding_scale)
 
+    def sharded(self, T: int) -> bool:
+        """True when this step keeps the residual stream sharded by rows over the tensor-parallel
+        ranks: `delta` then holds this rank's PARTIAL sums and every norm is `comm.sum_norm`."""
+        c = self.comm
+        return (c is not None and c.size > 1 and getattr(c, "fused_norm", False) and not self.cfg.is_moe
+                and getattr(self.w, "layer_range", None) is None and c.can_sum_norm(T, self.cfg.hidden))
+
+    def _norm(self, x, w, delta, T: int, f8: bool, shard: bool, out=None):
+        """x += delta; RMSNorm(x) * w -> b.h8 (e4m3) or `out` / b.h (bf16).  Sharded: `delta` is this
+        rank's partial of a row-parallel layer and the sum over ranks happens here."""
+        b = self.buf
+        out = b.h if out is None else out
+        if shard and delta is not None:
+            self.comm.sum_norm(delta, x, w, self.cfg.rms_eps, T, out=None if f8 else out,
+                               out_fp8=b.h8 if f8 else None)
+        else:
+            rows.add_rmsnorm(x, w, self.cfg.rms_eps, delta=delta, out=None if f8 else out,
+                             out_fp8=b.h8 if f8 else None, rows=T)
+
     def run_layers(self, inp: StepInputs, lo: int, hi: int, delta: Optional[torch.Tensor] = None):
         """Layers [lo, hi) over the residual stream in `buf.x`; returns the pending residual update
-        (the next norm, or `fold_residual`, adds it)."""
+        (the next norm, or `fold_residual`, adds it).  In a sharded step (see `sharded`) the update
+        is this rank's partial sum and `buf.x` is current only in the rows this rank owns."""
         cfg, w, b = self.cfg, self.w, self.buf
         T = inp.T
+        shard = self.sharded(T)
         for il in range(lo, hi):
             lw = w.layers[il]
             # attention block
-            f8 = lw.wqkv.wants_fp8
-            rows.add_rmsnorm(b.x, lw.attn_norm, cfg.rms_eps, delta=delta, out=None if f8 else b.h,
-                             out_fp8=b.h8 if f8 else None, rows=T)
+            self._norm(b.x, lw.attn_norm, delta, T, lw.wqkv.wants_fp8, shard)
             self._linear(lw.wqkv, b.h, b.h8, b.qkv, T)
             got8 = self._attention(il, inp, T, lw.wo.wants_fp8)
             if lw.wo.wants_fp8 and not got8:
                 rows.quant_fp8(b.attn, out=b.attn8, rows=T)
-            self._linear(lw.wo, b.attn, b.attn8, b.delta, T, reduce=True)
+            self._linear(lw.wo, b.attn, b.attn8, b.delta, T, reduce=not shard)
             # feed-forward block
             if cfg.is_moe:
                 rows.add_rmsnorm(b.x, lw.ffn_norm, cfg.rms_eps, delta=b.delta, out=b.h, rows=T)
                 self.moe_runner.forward(il, lw.moe, b.h, b.delta, T)
             else:
-                f8 = lw.w_gate_up.wants_fp8
-                rows.add_rmsnorm(b.x, lw.ffn_norm, cfg.rms_eps, delta=b.delta, out=None if f8 else b.h,
-                                 out_fp8=b.h8 if f8 else None, rows=T)
+                self._norm(b.x, lw.ffn_norm, b.delta, T, lw.w_gate_up.wants_fp8, shard)
                 self._linear(lw.w_gate_up, b.h, b.h8, b.gu, T)
                 d8 = lw.w_down.wants_fp8
                 rows.glu(b.gu, mode=cfg.glu_mode, alpha=cfg.glu_alpha, limit=cfg.glu_limit,
                          out=None if d8 else b.act, out_fp8=b.act8 if d8 else None, rows=T)
-                self._linear(lw.w_down, b.act, b.act8, b.delta, T, reduce=True)
+                self._linear(lw.w_down, b.act, b.act8, b.delta, T, reduce=not shard)
             delta = b.delta
         return delta
 
@@ -215,7 +240,7 @@ class DecoderModel:
     def head(self, inp: StepInputs, delta: Optional[torch.Tensor]) -> torch.Tensor:
         cfg, w, b = self.cfg, self.w, self.buf
         T = inp.T
-        rows.add_rmsnorm(b.x, w.out_norm, cfg.rms_eps, delta=delta, out=b.h, rows=T)
+        self._norm(b.x, w.out_norm, delta, T, False, self.sharded(T))
         if inp.logit_rows is not None:
             n = inp.n_logit_rows
             torch.index_select(b.h, 0, inp.logit_rows[:n], out=b.hsel[:n])

@@ -28,13 +28,15 @@ MAX_RANKS = 8
 class SymmViewC(C.Structure):
     _fields_ = [("base", C.c_void_p * MAX_RANKS), ("world", C.c_int), ("rank", C.c_int),
                 ("flags_off", C.c_longlong), ("recv_off", C.c_longlong), ("slot_bytes", C.c_longlong),
-                ("max_chunks", C.c_int), ("pad", C.c_int)]
+                ("max_chunks", C.c_int), ("pad", C.c_int),
+                ("ll_off", C.c_longlong), ("ll_half_bytes", C.c_longlong), ("ll_hop2_off", C.c_longlong)]
 
 
 class SymmHeap:
     """One rank's heap plus the mapped heaps of its peers."""
 
-    def __init__(self, slot_bytes: int, max_chunks: int = 256, group=None):
+    def __init__(self, slot_bytes: int, max_chunks: int = 256, group=None, ll_hop1_bytes: int = 0,
+                 ll_hop2_bytes: int = 0):
         lib = cuda_lib()
         assert lib.lk_symm_view_size() == C.sizeof(SymmViewC), "SymmView layout mismatch"
         self.group = group
@@ -46,7 +48,11 @@ class SymmHeap:
         self.flags_off = 256
         flags_bytes = 2 * MAX_RANKS * max_chunks * 4
         self.recv_off = (self.flags_off + flags_bytes + 1023) // 1024 * 1024
-        self.bytes = self.recv_off + 2 * MAX_RANKS * self.slot_bytes
+        # flag-in-data areas (two halves): first-hop region, then second-hop region
+        self.ll_off = (self.recv_off + 2 * MAX_RANKS * self.slot_bytes + 1023) // 1024 * 1024
+        self.ll_hop2_off = (ll_hop1_bytes + 1023) // 1024 * 1024
+        self.ll_half_bytes = self.ll_hop2_off + (ll_hop2_bytes + 1023) // 1024 * 1024
+        self.bytes = self.ll_off + 2 * self.ll_half_bytes
         p = C.c_void_p()
         check(lib.lk_symm_alloc(C.c_longlong(self.bytes), C.byref(p)), "lk_symm_alloc")
         self.local = p.value
@@ -71,6 +77,7 @@ class SymmHeap:
         v.world, v.rank = self.world, self.rank
         v.flags_off, v.recv_off, v.slot_bytes = self.flags_off, self.recv_off, self.slot_bytes
         v.max_chunks = max_chunks
+        v.ll_off, v.ll_half_bytes, v.ll_hop2_off = self.ll_off, self.ll_half_bytes, self.ll_hop2_off
         self.view = v
 
     def close(self):
@@ -93,7 +100,13 @@ class SymmComm:
         self.group = group
         self.size = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
-        self.heap = SymmHeap(max_rows * hidden * 2, group=group)
+        # flag-in-data areas of the fused layer-boundary kernel: partial rows (4 bytes per value, every
+        # source's share of this rank's rows) and normalised rows (at most 4 bytes per value + scales)
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.max_rows, self.hidden = max_rows, hidden
+        hop1 = (max_rows + world) * hidden * 4
+        hop2 = max_rows * (hidden * 4 + hidden // 16 + 16)
+        self.heap = SymmHeap(max_rows * hidden * 2, group=group, ll_hop1_bytes=hop1, ll_hop2_bytes=hop2)
         self.nccl = NcclComm(group)
         self.push_max_bytes = min(push_max_bytes, self.heap.slot_bytes)
         self.wsp = Workspace.get(device)
@@ -101,6 +114,32 @@ class SymmComm:
         # True: row-parallel GEMMs sum inside their epilogue; False: GEMM, then `all_reduce`.  Measured on
         # the 70B decode step the second is faster at 2 and at 8 ranks (17.7 / 12.4 against 19.1 / 13.7 ms).
         self.fused_gemm = False
+        # True: a row-parallel layer's partial sums go through `sum_norm` (reduce-scatter + residual +
+        # RMSNorm + quantise + all-gather in one kernel, residual stream sharded by rows in between)
+        self.fused_norm = True
+
+    def can_sum_norm(self, rows: int, hidden: int) -> bool:
+        return self.size > 1 and self.fused_norm and rows <= self.max_rows and hidden == self.hidden \
+            and hidden % 8 == 0 and self.size in (2, 4, 8)
+
+    def sum_norm(self, partial: torch.Tensor, x: torch.Tensor, w: torch.Tensor, eps: float, rows: int, *,
+                 out: Optional[torch.Tensor] = None, out_fp8=None, gather: bool = True):
+        """x[own rows] += sum over ranks of partial[own rows]; normalised rows -> `out` (bf16) or `out_fp8`
+        (e4m3 + per-128 scales): every row on every rank when `gather`, else the owned rows only.
+        Row r belongs to rank r // ceil(rows / world)."""
+        H = x.shape[1]
+        check(cuda_lib().lk_tp_sum_norm(C.byref(self.heap.view), ptr(partial), C.c_longlong(partial.stride(0)),
+                                        ptr(x), C.c_longlong(x.stride(0)), ptr(w), C.c_float(eps), rows, H,
+                                        ptr(out), C.c_longlong(out.stride(0) if out is not None else 0),
+                                        ptr(out_fp8.data) if out_fp8 is not None else None,
+                                        ptr(out_fp8.scale_t) if out_fp8 is not None else None,
+                                        C.c_longlong(out_fp8.scale_t.stride(0) if out_fp8 is not None else 0),
+                                        int(gather), ptr(self.wsp.status), stream()), "lk_tp_sum_norm")
+        self.collectives += 1
+
+    def owned_rows(self, rows: int) -> tuple:
+        rpr = (rows + self.size - 1) // self.size
+        return min(rows, self.rank * rpr), min(rows, (self.rank + 1) * rpr)
 
     def all_reduce(self, t: torch.Tensor, rows: int, residual: Optional[torch.Tensor] = None):
         if self.size == 1:
