@@ -39,9 +39,11 @@ def parse():
     ap.add_argument("--model", default="llama-3.3-70b")
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--prompt-len", type=int, default=1024)
-    ap.add_argument("--comm", default="auto", choices=["auto", "fused", "push", "nccl"],
-                    help="tensor-parallel sums: GEMM-epilogue kernels over peer memory, the stand-alone peer-memory "
-                         "all-reduce kernel, or NCCL; auto picks by world size from measurements")
+    ap.add_argument("--comm", default="auto", choices=["auto", "sum_norm", "fused", "push", "nccl"],
+                    help="tensor-parallel layer boundaries: sum_norm = one kernel over peer memory that does "
+                         "reduce-scatter + residual + RMSNorm + quantise + all-gather with the residual stream "
+                         "sharded by rows (the default); fused = all-reduce inside the GEMM epilogue; push = the "
+                         "stand-alone peer-memory all-reduce kernel; nccl = the library baseline")
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (marks the result invalid)")
     return ap.parse_args()
 
@@ -110,7 +112,7 @@ class ClockSampler:
 
 
 # collectives per tensor-parallel degree, by measured ms/step on this benchmark
-AUTO_COMM = {2: "push", 4: "push", 8: "push"}
+AUTO_COMM = {2: "sum_norm", 4: "sum_norm", 8: "sum_norm"}
 
 
 def main():
@@ -147,13 +149,16 @@ def main():
         mode = args.comm
         if mode == "auto":
             mode = AUTO_COMM.get(world, "nccl")
-        if mode in ("fused", "push"):
+        if mode in ("fused", "push", "sum_norm"):
             from loken_b200.parallel.symm import SymmComm
 
             comm = SymmComm(dev, max_rows=max(args.batch, 256), hidden=cfg.hidden)
             comm.fused_gemm = mode == "fused"
-            comm_name = ("GEMM-epilogue all-reduce over peer memory" if mode == "fused"
-                         else "peer-memory all-reduce kernel")
+            comm.fused_norm = mode == "sum_norm"
+            comm_name = {"fused": "GEMM-epilogue all-reduce over peer memory",
+                         "push": "peer-memory all-reduce kernel",
+                         "sum_norm": "one peer-memory kernel per layer boundary: reduce-scatter + residual + RMSNorm + "
+                                     "e4m3 quantise + all-gather, residual stream sharded by rows"}[mode]
         else:
             comm = NcclComm()
             comm_name = "nccl"

@@ -66,7 +66,8 @@ def random_moe(cfg: ModelConfig, gen, device, std: float, ep_rank: int = 0, ep_s
     if fmt == "bf16":
         gu_w, dn_w = gu.bfloat16().contiguous(), dn.bfloat16().contiguous()
     else:
-        gu_w, dn_w = quant.quantize_weight(gu, fmt), quant.quantize_weight(dn, fmt)
+        qz = quant.quantize_weight_torch if gu.is_cuda else quant.quantize_weight
+        gu_w, dn_w = qz(gu, fmt), qz(dn, fmt)
     return MoeWeights(router_w, router_b, gu_w, dn_w,
                       torch.stack(gub).contiguous() if gub else None,
                       torch.stack(dnb).contiguous() if dnb else None, elo, ecnt, fmt)

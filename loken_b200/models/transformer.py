@@ -86,6 +86,7 @@ class DecoderModel:
         self.buf = Buffers(self.cfg, weights, max_tokens, self.device)
         self.moe_runner = moe_runner
         self._kg = None    # gathered K / V^T scratch for prefill, grown on demand
+        self.sharded_steps = 0   # forwards issued with the row-sharded residual stream (eager or captured)
 
     # ---- one linear layer in whatever format its weights are held ----
     def _linear(self, lin: Linear, x_bf16, x_fp8: Optional[Fp8Act], out, T: int, reduce: bool = False):
@@ -206,6 +207,7 @@ class DecoderModel:
         cfg, w, b = self.cfg, self.w, self.buf
         T = inp.T
         shard = self.sharded(T)
+        self.sharded_steps += int(shard)
         for il in range(lo, hi):
             lw = w.layers[il]
             # attention block

@@ -74,7 +74,10 @@ def make_linear(w: torch.Tensor, fmt: str, bias: Optional[torch.Tensor] = None) 
         return Linear("bf16", w.bfloat16().contiguous(), bias, n_out, n_in)
     from ..ops import quant
 
-    return Linear("gguf", quant.quantize_weight(w, fmt), bias, n_out, n_in)
+    # on the GPU the torch encoders write the device planes directly (seconds for billions of values);
+    # on the host the C++ encoders of the file formats are used
+    q = quant.quantize_weight_torch(w, fmt) if w.is_cuda else quant.quantize_weight(w, fmt)
+    return Linear("gguf", q, bias, n_out, n_in)
 
 
 def dequant_linear(lin: Linear) -> torch.Tensor:

@@ -174,3 +174,68 @@ def linear_gguf(x: torch.Tensor, w: QuantWeight, *, bias: Optional[torch.Tensor]
     a.aq_ld, a.aq_sld = w.codes.stride(0), w.scales.stride(0)
     check(cuda_lib().lk_gemm_tc(C.byref(a), stream()), "lk_gemm_tc (quantised A)")
     return out
+
+
+# ---- quantisers in torch (any device) ------------------------------------------------------------
+# Round-to-nearest encoders that write the device planes directly.  They produce valid blocks of each
+# format (what `dequantize_weight` and the kernels decode), with the plain amax scale choice instead
+# of the host encoders' error-minimising search; random-init benchmark models of tens of billions of
+# values are quantised with these on the GPU in seconds instead of minutes on the host.
+
+_E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+
+
+def _nibble_pack_t(v: torch.Tensor) -> torch.Tensor:
+    """[..., K] uint8 values 0..15 -> [..., K/2]: value k in byte k/2, low nibble for even k."""
+    return (v[..., 0::2] | (v[..., 1::2] << 4)).to(torch.uint8)
+
+
+def quantize_weight_torch(w: torch.Tensor, fmt: str) -> QuantWeight:
+    ty = TYPE_OF_NAME[fmt]
+    rows, K = w.shape
+    w = w.float()
+    dev = w.device
+    if fmt == "q8_0":
+        g = w.view(rows, K // 32, 32)
+        d = (g.abs().amax(2) / 127.0).half()
+        df = d.float().clamp_min(1e-30)
+        q = torch.round(g / df[:, :, None]).clamp(-127, 127).to(torch.int8)
+        return QuantWeight(AQ_W8, ty, rows, K, q.view(rows, K).view(torch.uint8).contiguous(),
+                           d.contiguous().view(torch.uint8).view(rows, K // 32 * 2))
+    if fmt == "mxfp4":
+        g = w.view(rows, K // 32, 32)
+        amax = g.abs().amax(2).clamp_min(2.0 ** -120)
+        e = torch.floor(torch.log2(amax)) - 2.0            # 6 = 1.5 * 2^2 is the largest magnitude
+        e = e.clamp(-126, 127)
+        x = g / torch.exp2(e)[:, :, None]
+        lut = torch.tensor(_E2M1, device=dev)
+        mag = (x.abs().unsqueeze(-1) - lut).abs().argmin(-1).to(torch.uint8)
+        code = mag | ((x < 0).to(torch.uint8) << 3)
+        codes = _nibble_pack_t(code.view(rows, K))
+        return QuantWeight(AQ_MX4, ty, rows, K, codes.contiguous(), (e + 127).to(torch.uint8).contiguous())
+    if fmt == "q4_k":
+        g = w.view(rows, K // 256, 8, 32)
+        mn = (-g.amin(3)).clamp_min(0.0)
+        sc = (g.amax(3) + mn) / 15.0
+        d = (sc.amax(2) / 63.0).half()
+        dm = (mn.amax(2) / 63.0).half()
+        df, dmf = d.float().clamp_min(1e-30), dm.float().clamp_min(1e-30)
+        sci = torch.round(sc / df[:, :, None]).clamp(0, 63)
+        mni = torch.round(mn / dmf[:, :, None]).clamp(0, 63)
+        step = (df[:, :, None] * sci).clamp_min(1e-30)
+        q = torch.round((g + (dmf[:, :, None] * mni)[..., None]) / step[..., None]).clamp(0, 15).to(torch.uint8)
+        codes = _nibble_pack_t(q.view(rows, K))
+        rec = torch.cat([d.view(torch.uint8).view(rows, K // 256, 2), dm.view(torch.uint8).view(rows, K // 256, 2),
+                         sci.to(torch.uint8), mni.to(torch.uint8)], dim=2)
+        return QuantWeight(AQ_W4, ty, rows, K, codes.contiguous(), rec.view(rows, K // 256 * 20).contiguous())
+    if fmt == "q6_k":
+        g = w.view(rows, K // 256, 16, 16)
+        s = g.abs().amax(3) / 31.0
+        d = (s.amax(2) / 127.0).half()
+        df = d.float().clamp_min(1e-30)
+        sci = torch.round(s / df[:, :, None]).clamp(1, 127)
+        q = torch.round(g / (df[:, :, None] * sci)[..., None]).clamp(-32, 31).to(torch.int8)
+        rec = torch.cat([d.view(torch.uint8).view(rows, K // 256, 2), sci.to(torch.int8).view(torch.uint8)], dim=2)
+        return QuantWeight(AQ_W8G16, ty, rows, K, q.view(rows, K).view(torch.uint8).contiguous(),
+                           rec.view(rows, K // 256 * 18).contiguous())
+    raise ValueError(fmt)

@@ -1,6 +1,9 @@
 """Row-parallel projection + all-reduce, timed four ways on the ranks of one node:
 
     gemm          the fp8 GEMM alone (no sum: the floor)
+    gemm+sum_norm GEMM, then the layer-boundary kernel: reduce-scatter + residual + RMSNorm + e4m3
+                  quantise + all-gather (what the decoder runs by default; the others are followed by
+                  the stand-alone add + RMSNorm + quantise kernel in "+norm" columns)
     gemm+push     GEMM, then this library's one-shot all-reduce kernel over peer memory
     gemm+nccl     GEMM, then ncclAllReduce
     fused         the GEMM whose epilogue pushes its tiles to the peers and sums them
@@ -20,7 +23,7 @@ import json
 import torch
 import torch.distributed as dist
 
-from ..ops import gemm
+from ..ops import gemm, rows as row_ops
 from ..ops._lib import Workspace
 from ..parallel.comm import init_distributed
 from ..parallel.symm import SymmComm
@@ -91,6 +94,28 @@ def main():
         def fused():
             gemm.linear_fp8(x, w, out=out, residual=res, symm=comm.heap)
 
+        # what follows a row-parallel layer in the decoder: residual add + RMSNorm + e4m3 quantise
+        xres = torch.randn(M, H, device=dev).bfloat16()
+        wn = torch.ones(H, device=dev)
+        h8 = row_ops.alloc_fp8_act(M, H, dev)
+
+        def push_norm():
+            gemm.linear_fp8(x, w, out=out)
+            comm.all_reduce(out, M)
+            row_ops.add_rmsnorm(xres, wn, 1e-5, delta=out, out_fp8=h8, rows=M)
+
+        def nccl_norm():
+            gemm.linear_fp8(x, w, out=out)
+            comm.nccl.all_reduce(out, M)
+            row_ops.add_rmsnorm(xres, wn, 1e-5, delta=out, out_fp8=h8, rows=M)
+
+        def sum_norm():
+            gemm.linear_fp8(x, w, out=out)
+            comm.sum_norm(out, xres, wn, 1e-5, M, out_fp8=h8)
+
+        def sum_norm_alone():
+            comm.sum_norm(out, xres, wn, 1e-5, M, out_fp8=h8)
+
         # the fused result must be the sum the library computes
         with_nccl()
         ref = out.float().clone()
@@ -99,7 +124,9 @@ def main():
         assert gemm.gemm_raw.last_fused, "the fused path was not taken"
         err = float(((out.float() - ref).abs().max() / ref.abs().max()).item())
         r = {"layer": name, "M": M, "N": H, "K": K, "rel_err_fused_vs_nccl": err}
-        for key, fn in (("gemm", plain), ("gemm+push", with_push), ("gemm+nccl", with_nccl), ("fused", fused)):
+        for key, fn in (("gemm", plain), ("gemm+push", with_push), ("gemm+nccl", with_nccl), ("fused", fused),
+                        ("gemm+push+norm", push_norm), ("gemm+nccl+norm", nccl_norm), ("gemm+sum_norm", sum_norm),
+                        ("sum_norm_alone", sum_norm_alone)):
             r[key + "_us"] = round(_graph_time(fn, args.inner, args.reps), 2)
         rows.append(r)
     status = wsp.read_status()

@@ -84,6 +84,38 @@ def main():
                                     ms_one_shot=t1))
         ok &= err < 2e-2 and same
     SymmComm.set_allreduce_mode(0)
+    # layer-boundary kernel: reduce-scatter + residual + RMSNorm (+ e4m3 quantise) + all-gather, against
+    # an NCCL sum followed by the same arithmetic in fp32 torch
+    from loken_b200.ops import gemm as _gemm, rows as _rows
+    for rows in (1, 5, 64, 200, 256):
+        for f8 in (False, True):
+            torch.manual_seed(300 + rank)
+            part = (torch.randn(rows, H, device=dev) * 0.5).bfloat16()
+            gen = torch.Generator(device=dev).manual_seed(9)
+            x0 = torch.randn(rows, H, device=dev, generator=gen).bfloat16()
+            wn = (torch.rand(H, device=dev, generator=gen) + 0.5).float()
+            tot = part.float().clone()
+            dist.all_reduce(tot)
+            xr = (tot + x0.float()).bfloat16().float()
+            want = xr * torch.rsqrt((xr * xr).mean(1, keepdim=True) + 1e-5) * wn
+            x = x0.clone()
+            out = torch.zeros(rows, H, device=dev, dtype=torch.bfloat16)
+            o8 = _rows.alloc_fp8_act(rows, H, dev) if f8 else None
+            comm.sum_norm(part, x, wn, 1e-5, rows, out=None if f8 else out, out_fp8=o8)
+            torch.cuda.synchronize()
+            got = _gemm.dequantize_act_fp8(o8, rows) if f8 else out.float()
+            tol = 0.07 if f8 else 0.01          # e4m3 has 3 mantissa bits
+            err = ((got - want).abs().max() / want.abs().max()).item()
+            lo, hi = comm.owned_rows(rows)
+            xerr = ((x[lo:hi].float() - xr[lo:hi]).abs().max() / xr.abs().max()).item() if hi > lo else 0.0
+            payload = o8.data.view(torch.uint8) if f8 else out
+            gathered = [torch.empty_like(payload) for _ in range(world)]
+            dist.all_gather(gathered, payload.contiguous())
+            same = all(torch.equal(gathered[0], g) for g in gathered)
+            t = timed(lambda: comm.sum_norm(part, x, wn, 1e-5, rows, out=None if f8 else out, out_fp8=o8))
+            report["cases"].append(dict(rows=rows, kernel="sum_norm", fp8=f8, rel_err=err, x_err=xerr, same_bits=same,
+                                        ms=t))
+            ok &= err < tol and xerr < 0.01 and same
     status_ok = wsp.read_status() == 0
     # bounded wait: rank 0 alone starts a collective; nobody answers; it must come back with a
     # status code.  The other ranks then run theirs alone (rank 0's flags are already there), which

@@ -1,6 +1,12 @@
-"""Child process of the tensor-parallel test: the same tiny model at TP = world (NCCL sums, then
-this library's peer-memory sums, with and without the fused GEMM epilogue) against the fp32
-oracle of the whole model on rank 0."""
+"""Child process of the tensor-parallel test: the same tiny model at TP = world against the TP = 1
+ENGINE on the same GPU (same kernels, same fp8 numerics), for every way the row-parallel layers can
+be summed: NCCL, this library's all-reduce kernels ("push"), the GEMM-epilogue all-reduce ("fused")
+and the layer-boundary kernel with the row-sharded residual stream ("sum_norm", the default).
+With bf16 weights degree N must reproduce degree 1: logits cosine >= 0.9999 and the same greedy
+tokens (a token may differ only where degree 1's own top-2 gap is under 1 % of its largest logit).
+With block-scaled fp8 a perturbation of one bf16 rounding step flips e4m3 roundings of the
+activations (one step = 6 %), so two correct runs differ by the format's own noise (measured:
+cosine 0.9945 between degree 1 and degree 2 summed by NCCL); there the bound is cosine >= 0.99."""
 import json
 import os
 import sys
@@ -11,7 +17,6 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 from loken_b200.models.config import tiny  # noqa: E402
-from loken_b200.models.reference import forward_ref  # noqa: E402
 from loken_b200.models.weights import random_weights  # noqa: E402
 from loken_b200.parallel.comm import NcclComm, init_distributed  # noqa: E402
 from loken_b200.parallel.symm import SymmComm  # noqa: E402
@@ -19,22 +24,15 @@ from loken_b200.serve.engine import LLMEngine  # noqa: E402
 from loken_b200.serve.params import SamplingParams  # noqa: E402
 
 
-MISSES = []
-
-
-def check_tokens(w_full, prompt, out, tie=0.03):
-    """Every generated token must be the oracle's first or (on a near tie) second choice."""
-    seq = list(prompt)
-    for step, t in enumerate(out):
-        ref = forward_ref(w_full, seq)[-1]
-        top = torch.topk(ref, 2)
-        if t != int(top.indices[0]):
-            if not (t == int(top.indices[1]) and (top.values[0] - top.values[1]) < tie * ref.abs().max()):
-                MISSES.append(dict(step=step, got=int(t), got_logit=float(ref[t]), top=[int(i) for i in top.indices],
-                                   top_logits=[float(v) for v in top.values], absmax=float(ref.abs().max())))
-                return False
-        seq.append(t)
-    return True
+def run(eng, prompts, sp, n_steps):
+    """Greedy decode by hand so the logits of every step can be kept: [(tokens, logits per step)]."""
+    ids = [eng.add_request(p, sp) for p in prompts]
+    steps = []
+    while eng.has_work():
+        eng.step()
+        lg = eng.runner.last_logits
+        steps.append(lg.float().clone() if lg is not None else None)
+    return [eng.seqs[i].output for i in ids], steps
 
 
 def main():
@@ -42,39 +40,53 @@ def main():
     rank, world, local = init_distributed()
     dev = torch.device("cuda", local)
     fmt = sys.argv[2] if len(sys.argv) > 2 else "fp8_block"
-    cfg = tiny("llama", weight_format=fmt, head_dim=128, n_q=4, n_kv=2, hidden=512, intermediate=1024, vocab=1024)
+    cfg = tiny("llama", weight_format=fmt, head_dim=128, n_q=8, n_kv=8, hidden=1024, intermediate=1024 * world,
+               vocab=1024, n_layers=3)
     g = torch.Generator().manual_seed(7)
-    prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (21, 50)]
+    prompts = [torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for n in (21, 50, 9)]
     sp = SamplingParams(temperature=0.0, top_k=0, top_p=1.0, max_tokens=6)
-    w_full = random_weights(cfg, dev, seed=3, std=0.05)
+    kw = dict(num_blocks=64, max_seqs=8, max_prefill_tokens=256, max_ctx=256)
     rep = {"world": world, "format": fmt}
-    for name in ("nccl", "push", "fused"):
+    # degree 1: the whole model on this GPU through the same engine
+    w1 = random_weights(cfg, dev, seed=3, std=0.05)
+    e1 = LLMEngine(cfg, weights=w1, device=dev, **kw)
+    ref_tokens, ref_logits = run(e1, prompts, sp, 6)
+    del e1
+    for name in ("nccl", "push", "fused", "sum_norm"):
         comm = NcclComm() if name == "nccl" else SymmComm(dev, max_rows=256, hidden=cfg.hidden)
         if name != "nccl":
             comm.fused_gemm = name == "fused"
+            comm.fused_norm = name == "sum_norm"
         w = random_weights(cfg, dev, seed=3, std=0.05, tp_rank=rank, tp_size=world)
-        eng = LLMEngine(cfg, weights=w, device=dev, tp_rank=rank, tp_size=world, comm=comm, num_blocks=64,
-                        max_seqs=8, max_prefill_tokens=256, max_ctx=256)
-        res = eng.generate(prompts, sp)
-        logits = eng.runner.model.buf.logits   # local vocabulary slice of the last step
-        # block-scaled fp8 activations and weights: logits agree with the fp32 oracle to about 1 % (cosine
-        # 0.994), so a second choice within a tenth of the largest logit counts as a tie
-        tie = 0.12 if fmt == "fp8_block" else 0.03
-        ok = all(check_tokens(w_full, p, r.output, tie) for p, r in zip(prompts, res))
-        # logits of a fresh single prompt against the oracle
-        eng.add_request(prompts[0], sp)
-        eng.step()
-        full = comm.all_gather_cols(eng.runner.model.buf.logits[:1])
-        ref = forward_ref(w_full, prompts[0])[-1]
-        cos = torch.nn.functional.cosine_similarity(full[0].float(), ref, dim=0).item()
-        flag = torch.tensor([int(ok)], device=dev)
+        eng = LLMEngine(cfg, weights=w, device=dev, tp_rank=rank, tp_size=world, comm=comm, **kw)
+        toks, logits = run(eng, prompts, sp, 6)
+        # row i of every step's logits is sequence i (all prompts are read in the first step and decode
+        # together).  A sequence is compared until its first token that differs from degree 1; that
+        # token must be a near tie of degree 1's own logits, and from then on the two runs are fed
+        # different tokens, so the sequence drops out.
+        cos_min, ok = 1.0, True
+        alive = [True] * len(prompts)
+        for step, (a, b) in enumerate(zip(logits, ref_logits)):
+            if a is None or b is None or a.shape != b.shape:
+                ok = False
+                break
+            for i in range(len(prompts)):
+                if not alive[i]:
+                    continue
+                cos_min = min(cos_min, torch.nn.functional.cosine_similarity(a[i], b[i], dim=0).item())
+                if int(a[i].argmax()) != int(b[i].argmax()):
+                    top2 = torch.topk(b[i], 2).values
+                    ok &= bool((top2[0] - top2[1]) < 0.01 * b[i].abs().max())
+                    alive[i] = False
+        passed = (ok and cos_min >= 0.9999) if fmt == "bf16" else cos_min >= 0.99
+        flag = torch.tensor([int(passed)], device=dev)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-        rep[f"tokens_match_{name}"] = bool(flag.item())
-        rep[f"logits_cos_{name}"] = cos
+        rep[f"tokens_equal_{name}"] = toks == ref_tokens
+        rep[f"match_{name}"] = bool(flag.item())
+        rep[f"logits_cos_min_{name}"] = cos_min
         rep[f"status_{name}"] = eng.runner.wsp.read_status()
-        rep[f"misses_{name}"] = list(MISSES)
-        MISSES.clear()
-        del eng, logits
+        rep[f"sharded_steps_{name}"] = int(getattr(eng.runner.model, "sharded_steps", 0))
+        del eng
         if name != "nccl":
             torch.cuda.synchronize()
             dist.barrier()

@@ -183,3 +183,20 @@ def test_device_repack_keeps_the_format_numerics(name):
     q = quant.from_blocks(raw, ty, rows, K, torch.device("cpu"))
     got = quant.dequantize_weight(q).numpy()
     assert np.array_equal(got, want)
+
+
+def test_torch_encoders_write_valid_device_planes():
+    """The round-to-nearest encoders in torch (used on the GPU for large random-init models) produce
+    the same plane shapes as the host encoders and decode to within the format's own error."""
+    import torch
+
+    from loken_b200.ops import quant
+
+    torch.manual_seed(0)
+    w = torch.randn(8, 512) * 0.02
+    for fmt in ("q8_0", "mxfp4", "q4_k", "q6_k"):
+        a, b = quant.quantize_weight_torch(w, fmt), quant.quantize_weight(w, fmt)
+        assert a.codes.shape == b.codes.shape and a.scales.shape == b.scales.shape and a.aq_fmt == b.aq_fmt
+        ea = (quant.dequantize_weight(a) - w).abs().max().item()
+        eb = (quant.dequantize_weight(b) - w).abs().max().item()
+        assert ea <= 1.25 * eb + 1e-6, (fmt, ea, eb)

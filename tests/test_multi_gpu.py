@@ -38,13 +38,21 @@ def test_peer_memory_allreduce(tmp_path):
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs two GPUs")
-def test_tensor_parallel_matches_single_gpu(tmp_path):
-    n = 2
-    rep = _run("mp_tp_worker.py", n, str(tmp_path / "tp.json"), 29641)
-    assert rep["tokens_match_nccl"], rep
-    assert rep["tokens_match_fused"], rep
-    assert rep["tokens_match_push"], rep
-    assert rep["logits_cos_fused"] > 0.99      # block-scaled fp8 weights and activations
+@pytest.mark.parametrize("fmt", ["bf16", "fp8_block"])
+def test_tensor_parallel_matches_single_gpu(tmp_path, fmt):
+    n = min(_ngpu(), 8)
+    n = 8 if n >= 8 else 4 if n >= 4 else 2
+    rep = _run("mp_tp_worker.py", n, str(tmp_path / "tp.json"), 29641, (fmt,))
+    print(json.dumps(rep))
+    # every way of summing the row-parallel layers reproduces the degree-1 ENGINE (same kernels, same
+    # numerics): bf16 weights to cosine >= 0.9999 with the same greedy tokens, block-scaled fp8 to the
+    # format's own noise (cosine >= 0.99)
+    bound = 0.9999 if fmt == "bf16" else 0.99
+    for name in ("nccl", "push", "fused", "sum_norm"):
+        assert rep[f"match_{name}"], (name, rep)
+        assert rep[f"logits_cos_min_{name}"] >= bound, (name, rep)
+        assert rep[f"status_{name}"] == 0, (name, rep)
+    assert rep["sharded_steps_sum_norm"] > 0 and rep["sharded_steps_push"] == 0
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs two GPUs")
