@@ -119,10 +119,18 @@ def router(ctx: ServerContext) -> APIRouter:
                     return out + _ev("content_block_start", {"type": "content_block_start", "index": block,
                                                              "content_block": cb})
 
+                figs, cached = None, 0
                 for ev in ctx.run(llm, ids, params, request_id=rid, scope=scope):
                     if ev.error:
                         yield _ev("error", {"type": "error", "error": {"type": "api_error", "message": ev.error}})
                         return
+                    if ev.progress is not None:
+                        from .common import prefill_comment
+
+                        yield prefill_comment(ev.progress)
+                        continue
+                    if ev.finished:
+                        figs, cached = ev.figures, ev.cached_tokens
                     n_out += len(ev.token_ids)
                     reason = ev.finish_reason or reason
                     for kind, text in split.push(ev.text) + (split.flush() if ev.finished else []):
@@ -161,7 +169,8 @@ def router(ctx: ServerContext) -> APIRouter:
                     yield _ev("content_block_stop", {"type": "content_block_stop", "index": block})
                 yield _ev("message_delta", {"type": "message_delta", "delta": {
                     "stop_reason": _stop_reason(reason, calls, False), "stop_sequence": None},
-                    "usage": {"output_tokens": n_out}})
+                    "usage": {"output_tokens": n_out, "cache_read_input_tokens": cached,
+                              **({"loken": figs} if figs else {})}})
                 yield _ev("message_stop", {"type": "message_stop"})
 
             return StreamingResponse(iterate_in_threadpool(gen()), media_type="text/event-stream",
@@ -169,9 +178,12 @@ def router(ctx: ServerContext) -> APIRouter:
 
         def run_all():
             text, n_out, reason = "", 0, None
+            figs, cached = None, 0
             for ev in ctx.run(llm, ids, params, request_id=rid, scope=scope):
                 if ev.error:
                     raise ApiError(500, ev.error, "api_error")
+                if ev.finished:
+                    figs, cached = ev.figures, ev.cached_tokens
                 text += ev.text
                 n_out += len(ev.token_ids)
                 reason = ev.finish_reason or reason
@@ -189,7 +201,8 @@ def router(ctx: ServerContext) -> APIRouter:
                                 "input": json.loads(c["function"]["arguments"] or "{}")})
             return {"id": rid, "type": "message", "role": "assistant", "model": llm.model_id, "content": content,
                     "stop_reason": _stop_reason(reason, calls, False), "stop_sequence": None,
-                    "usage": {"input_tokens": len(ids), "output_tokens": n_out}}
+                    "usage": {"input_tokens": len(ids), "output_tokens": n_out, "cache_read_input_tokens": cached,
+                              **({"loken": figs} if figs else {})}}
 
         return JSONResponse(await run_in_threadpool(run_all), headers={"x-request-id": rid})
 

@@ -360,10 +360,22 @@ class Usage:
     cached_tokens: int = 0
     accepted_prediction_tokens: int = 0
     rejected_prediction_tokens: int = 0
+    figures: Optional[dict] = None     # the request's own figures (`usage.loken`, utils/figures.py)
 
     def openai(self) -> dict:
-        return {"prompt_tokens": self.prompt_tokens, "completion_tokens": self.completion_tokens,
-                "total_tokens": self.prompt_tokens + self.completion_tokens,
-                "prompt_tokens_details": {"cached_tokens": self.cached_tokens},
-                "completion_tokens_details": {"accepted_prediction_tokens": self.accepted_prediction_tokens,
-                                              "rejected_prediction_tokens": self.rejected_prediction_tokens}}
+        out = {"prompt_tokens": self.prompt_tokens, "completion_tokens": self.completion_tokens,
+               "total_tokens": self.prompt_tokens + self.completion_tokens,
+               "prompt_tokens_details": {"cached_tokens": self.cached_tokens},
+               "completion_tokens_details": {"accepted_prediction_tokens": self.accepted_prediction_tokens,
+                                             "rejected_prediction_tokens": self.rejected_prediction_tokens}}
+        if self.figures:
+            out["loken"] = self.figures
+        return out
+
+
+def prefill_comment(progress) -> bytes:
+    """SSE comment line that reports how far a prompt has been read (clients that follow the SSE
+    specification ignore comment lines)."""
+    import json as _json
+
+    return (": loken-prefill " + _json.dumps({"done": int(progress[0]), "total": int(progress[1])}) + "\n\n").encode()

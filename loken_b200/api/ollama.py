@@ -77,9 +77,9 @@ def router(ctx: ServerContext) -> APIRouter:
                         "expires_at": "0001-01-01T00:00:00Z", "context_length": m.engine.max_ctx})
         return {"models": out}
 
-    def _final(llm, t0, t_first, n_in, n_out, reason) -> dict:
+    def _final(llm, t0, t_first, n_in, n_out, reason, cached: int = 0) -> dict:
         now = time.perf_counter()
-        return {"done": True, "done_reason": "length" if reason == "length" else "stop",
+        return {"prompt_eval_cached_count": int(cached), "done": True, "done_reason": "length" if reason == "length" else "stop",
                 "total_duration": int((now - t0) * 1e9), "load_duration": 0, "prompt_eval_count": n_in,
                 "prompt_eval_duration": int(((t_first or now) - t0) * 1e9), "eval_count": n_out,
                 "eval_duration": int((now - (t_first or now)) * 1e9)}

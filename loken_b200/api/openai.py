@@ -18,7 +18,7 @@ from starlette.concurrency import iterate_in_threadpool, run_in_threadpool
 
 from ..text.chat import parse_tool_calls
 from ..text.stream import ThinkingSplitter, split_thinking
-from .common import ApiError, Usage, check_messages, new_request_id, params_from_openai
+from .common import ApiError, Usage, check_messages, new_request_id, params_from_openai, prefill_comment
 from .context import ServerContext
 
 
@@ -192,11 +192,17 @@ def router(ctx: ServerContext) -> APIRouter:
                 split = ThinkingSplitter()
                 n_out, held, reason = 0, "", None
                 tool_mode, sent_any = False, False
+                figs, cached = None, 0
                 try:
                     for ev in ctx.run(llm, ids, params, priority=priority, request_id=rid, scope=scope):
                         if ev.error:
                             yield _sse({"error": {"message": ev.error, "type": "server_error"}})
                             break
+                        if ev.progress is not None:
+                            yield prefill_comment(ev.progress)
+                            continue
+                        if ev.finished:
+                            figs, cached = ev.figures, ev.cached_tokens
                         n_out += len(ev.token_ids)
                         for kind, text in split.push(ev.text) + (split.flush() if ev.finished else []):
                             if kind == "reasoning":
@@ -245,7 +251,8 @@ def router(ctx: ServerContext) -> APIRouter:
                     fin = "tool_calls" if calls else ("length" if reason == "length" else "stop")
                     yield _sse({**base, "choices": [{"index": 0, "delta": {}, "finish_reason": fin}]})
                     if include_usage:
-                        yield _sse({**base, "choices": [], "usage": Usage(len(ids), n_out).openai()})
+                        yield _sse({**base, "choices": [],
+                                    "usage": Usage(len(ids), n_out, cached, figures=figs).openai()})
                     yield b"data: [DONE]\n\n"
                 except ApiError as e:
                     yield _sse({"error": {"message": e.message, "type": e.kind, "code": e.code}})
@@ -254,8 +261,11 @@ def router(ctx: ServerContext) -> APIRouter:
                                      headers={"x-request-id": rid, "cache-control": "no-cache"})
 
         def run_all():
+            from ..utils.figures import sum_figures
+
             choices = []
             total_out = 0
+            fig_parts, cached = [], 0
             for idx in range(params.n):
                 text, toks, lps, reason = "", [], [], None
                 p = params
@@ -270,6 +280,9 @@ def router(ctx: ServerContext) -> APIRouter:
                     toks += ev.token_ids
                     lps += ev.logprobs or []
                     reason = ev.finish_reason or reason
+                    if ev.finished and ev.figures:
+                        fig_parts.append(ev.figures)
+                        cached = ev.cached_tokens
                 reasoning, answer = split_thinking(text)
                 calls = []
                 if tools:
@@ -286,7 +299,8 @@ def router(ctx: ServerContext) -> APIRouter:
                 choices.append(ch)
                 total_out += len(toks)
             return {"id": rid, "object": "chat.completion", "created": created, "model": llm.model_id,
-                    "choices": choices, "usage": Usage(len(ids), total_out).openai()}
+                    "choices": choices,
+                    "usage": Usage(len(ids), total_out, cached, figures=sum_figures(fig_parts)).openai()}
 
         out = await run_in_threadpool(run_all)
         return JSONResponse(out, headers={"x-request-id": rid})

@@ -303,7 +303,7 @@ attn_decode_kernel(const DecodeParams p) {
       // hd == 128: the head is exactly one 128-group of the o_proj input
       const float r = bf2f(f2bf(d < HD ? val : 0.f));
       const float amax = block_max(fabsf(r), red);
-      const float sc = amax > 0.f ? amax * (1.f / 448.f) : 1.f;
+      const float sc = e4m3_group_scale(amax);
       if (d < HD) p.out_fp8[(long long)row * p.n_q * HD + head * HD + d] = f2e4m3(r / sc);
       if (d == 0) p.out_scales_t[(long long)head * p.scale_ld + row] = sc;
     }

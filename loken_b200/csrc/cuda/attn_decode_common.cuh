@@ -121,7 +121,7 @@ __device__ __forceinline__ void decode_finish(const DecodeParamsV2& p, int row, 
       if ((d & 31) == 0) red[d >> 5] = a;
       asm volatile("bar.sync 2, 128;" ::: "memory");
       const float amax = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
-      const float sc = amax > 0.f ? amax * (1.f / 448.f) : 1.f;
+      const float sc = e4m3_group_scale(amax);
       if (d < HD) p.out_fp8[(long long)row * p.n_q * HD + head * HD + d] = f2e4m3(r / sc);
       if (d == 0) p.out_scales_t[(long long)head * p.scale_ld + row] = sc;
     }

@@ -53,6 +53,17 @@ __device__ __forceinline__ float e4m32f(uint8_t v) {
   return __half2float(*reinterpret_cast<__half*>(&h));
 }
 
+// Scale of an e4m3 activation group: the smallest power of two s with amax / s <= 448.  Powers of two
+// make the scaling exact and let the block-scaled MMA take the scale as an E8M0 exponent
+// (gemm_mx.cu); the per-K-block fold of gemm_tc.cuh accepts any f32 and so these too.
+__device__ __forceinline__ float e4m3_group_scale(float amax) {
+  if (!(amax > 0.f)) return 1.f;
+  const uint32_t bits = __float_as_uint(__fdiv_rn(amax, 448.f));     // IEEE division: the same bits as the host reference
+  int ex = (int)((bits >> 23) & 0xFF) + ((bits & 0x7FFFFF) ? 1 : 0);
+  ex = ex < 1 ? 1 : ex > 254 ? 254 : ex;
+  return __uint_as_float((uint32_t)ex << 23);
+}
+
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
 
 // Programmatic dependent launch (see lkh::launch_pdl): `pdl_wait` returns when the preceding kernel

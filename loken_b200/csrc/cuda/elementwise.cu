@@ -43,7 +43,7 @@ __device__ __forceinline__ void quant8(const float (&v)[8], uint8_t* dst, float*
   const unsigned hm = 0xFFFFu << (threadIdx.x & 16);
 #pragma unroll
   for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(hm, amax, o));
-  const float scale = amax > 0.f ? amax * (1.f / 448.f) : 1.f;
+  const float scale = e4m3_group_scale(amax);
   const float inv = 1.f / scale;
   uint2 q;
   uint8_t* b = reinterpret_cast<uint8_t*>(&q);
@@ -177,7 +177,7 @@ glu_kernel(const __nv_bfloat16* __restrict__ gu, long long ld_in, int I, int mod
 #pragma unroll
     for (int s = 8; s > 0; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
     if (live) {
-      const float scale = amax > 0.f ? amax * (1.f / 448.f) : 1.f;
+      const float scale = e4m3_group_scale(amax);
       const float inv = 1.f / scale;
       uint2 q;
       uint8_t* b = reinterpret_cast<uint8_t*>(&q);
@@ -205,7 +205,7 @@ quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, long long ld_in, int K, ui
 #pragma unroll
   for (int s = 8; s > 0; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
   if (live) {
-    const float scale = amax > 0.f ? amax * (1.f / 448.f) : 1.f;
+    const float scale = e4m3_group_scale(amax);
     const float inv = 1.f / scale;
     uint2 q;
     uint8_t* b = reinterpret_cast<uint8_t*>(&q);

@@ -55,6 +55,24 @@ inline int make_tmap_2d(CUtensorMap* tm, const void* base, CUtensorMapDataType d
   return r == CUDA_SUCCESS ? LKH_OK : LKH_TMAP_FAIL;
 }
 
+// 2-D row-major byte tensor [rows, row_bytes] read in boxes of box_rows x box_bytes WITHOUT swizzle
+// (shared-memory image = the box's rows back to back); box_bytes a multiple of 16.
+inline int make_tmap_2d_plain(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t row_bytes, uint64_t ld_bytes,
+                              uint32_t box_rows, uint32_t box_bytes) {
+  PFN_cuTensorMapEncodeTiled enc = get_encode_fn();
+  if (!enc) return LKH_NO_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (ld_bytes & 15) || box_rows > 256 || (box_bytes & 15) || box_bytes > 256)
+    return LKH_BAD_ARG;
+  cuuint64_t gdim[2] = {row_bytes, rows};
+  cuuint64_t gstr[1] = {ld_bytes};
+  cuuint32_t box[2] = {box_bytes, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gdim, gstr, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? LKH_OK : LKH_TMAP_FAIL;
+}
+
 // 3-D variant: [d2, rows, cols] with byte pitches ld1 (row) and ld2 (outer).
 inline int make_tmap_3d(CUtensorMap* tm, const void* base, CUtensorMapDataType dt, int esize, uint64_t d2,
                         uint64_t rows, uint64_t cols, uint64_t ld1, uint64_t ld2, uint32_t box_rows,

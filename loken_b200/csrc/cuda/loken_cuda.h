@@ -53,6 +53,14 @@ typedef struct LkGemmArgs {
 
 int lk_gemm_tc(const LkGemmArgs* args, void* stream);
 unsigned long long lk_launch_count(void);
+// Block-scaled GEMM (gemm_mx.cu): MXFP4 weights on the M side (`aq` nibbles, `aq_scale` E8M0 exponents per 32
+// values), e4m3 token rows with E8M0 exponents on the N side (`B`, `b_scale` as bytes, pitch `b_ld`); scales
+// applied by `tcgen05.mma.kind::mxf8f6f4.block_scale`.
+int lk_gemm_mx(const LkGemmArgs* args, void* stream);
+// bf16 rows -> e4m3 + one E8M0 exponent per 32 values, fused with a row gather or a GLU (mx_quant.cu)
+int lk_quant_mx8(const void* x, long long ldx, int rows, int K, int mode, const int* pair_row, int kdiv,
+                 int glu_mode, float alpha, float limit, void* out, long long ldo, void* sf, long long sf_ld,
+                 void* stream);
 
 // ---- row kernels (elementwise.cu) -------------------------------------------------------
 int lk_embed_bf16(const int* tokens, const void* table, void* out, int T, int H, int vocab, float scale,
@@ -147,6 +155,9 @@ int lk_advance_decode(int* tokens, int* positions, int* slots, int* seq_lens, co
 // mode: 0 softmax over the chosen logits, 1 full softmax (renorm optional), 2 sigmoid (renorm optional)
 int lk_moe_route(const float* logits, long long ld, int T, int E, int k, int mode, int renorm, int* ids,
                  float* wts, void* stream);
+// router GEMV + top-k in one launch (decode-size steps): h bf16 [T, ldh], w bf16 [E, H]
+int lk_moe_router(const void* h, long long ldh, const void* w, const float* bias, int T, int H, int E, int k,
+                  int mode, int renorm, int* ids, float* wts, float* logits_out, long long ldl, void* stream);
 int lk_moe_plan(const int* ids, int P, int E_total, int e_lo, int e_cnt, int BN, int max_tiles, int* offsets,
                 int* pair_row, int* tile_expert, int* tile_row0, int* tile_rows, int* ntiles, int* status,
                 void* stream);
@@ -168,9 +179,24 @@ int lk_allreduce_push(const void* view, void* data, int rows, int cols, long lon
                       int* status, void* stream);
 // Row-parallel layer boundary in one kernel: reduce-scatter of the ranks' partial rows, residual add
 // and RMSNorm on the owner of each row, (e4m3 quantise,) all-gather of the normalised rows (tp_fused.cu).
+// gather: 0 = normalised rows stay on their owner, 1 = every rank receives every row.
+// local: 1 = `partial` already holds the complete update of the rows this rank owns (nothing is summed
+// over ranks; expert-parallel combine output), 0 = it is this rank's partial of every row.
 int lk_tp_sum_norm(const void* view, const void* partial, long long ld_p, void* x, long long ld_x, const float* w,
                    float eps, int T, int H, void* out_bf16, long long ld_o, void* out_fp8, float* scales_t,
-                   long long scale_ld, int gather, int* status, void* stream);
+                   long long scale_ld, int gather, int local, int* status, void* stream);
+// Expert-parallel dispatch / combine over peer memory (ep_moe.cu)
+int lk_ep_slots(const void* view, int T, int k);
+int lk_ep_dispatch(const void* view, const void* h, long long ldh, const int* ids, int T, int H, int k,
+                   int n_experts, int* status, void* stream);
+int lk_ep_meta(const void* view, int T, int H, int k, int n_experts, int* slot_expert, int* slot_src, int* status,
+               void* stream);
+int lk_ep_gather(const void* view, int T, int H, int k, int n_experts, const int* slot_expert, void* xr,
+                 long long ldx, int* status, void* stream);
+int lk_ep_return(const void* view, int T, int H, int k, int n_experts, const int* slot_src, const int* pair_row,
+                 const void* y, long long ldy, void* stream);
+int lk_ep_combine(const void* view, int T, int H, int k, int n_experts, const float* wts, void* out, long long ldo,
+                  int* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -23,23 +23,16 @@ namespace {
 constexpr int MAX_E = 256;
 constexpr int MAX_K = 8;
 
-__global__ void __launch_bounds__(128)
-moe_route_kernel(const float* __restrict__ logits, long long ld, int T, int E, int k, int mode, int renorm,
-                 int* __restrict__ ids, float* __restrict__ wts) {
-  const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (t >= T) return;
+// One warp: scores of E experts (v[j] = score of expert j * 32 + lane, -inf past E) -> the k best ids and
+// their weights.  mode 0: softmax over the chosen logits; 1: full softmax first (renorm optional);
+// 2: sigmoid scores (renorm optional).  Ties go to the lowest expert id.
+__device__ __forceinline__ void route_warp(float (&v)[MAX_E / 32], int lane, int E, int k, int mode, int renorm,
+                                           int* __restrict__ ids, float* __restrict__ wts) {
   constexpr int PER = MAX_E / 32;
-  float v[PER];
-  const float* x = logits + (long long)t * ld;
-  float mx = -INFINITY;
-#pragma unroll
-  for (int j = 0; j < PER; ++j) {
-    const int e = j * 32 + lane;
-    v[j] = e < E ? x[e] : -INFINITY;
-    mx = fmaxf(mx, v[j]);
-  }
   if (mode == 1) {            // full softmax first
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) mx = fmaxf(mx, v[j]);
     mx = warp_max(mx);
     float z = 0.f;
 #pragma unroll
@@ -84,8 +77,8 @@ moe_route_kernel(const float* __restrict__ logits, long long ld, int T, int E, i
     for (int j = 0; j < PER; ++j)
       if (j * 32 + lane == bi) v[j] = -INFINITY;
   }
-  // weights
-  float wsum = 0.f, cm = cv[0];
+  float wsum = 0.f;
+  const float cm = cv[0];
   if (mode == 0) {
     for (int r = 0; r < k; ++r) {
       cv[r] = __expf(cv[r] - cm);
@@ -99,9 +92,79 @@ moe_route_kernel(const float* __restrict__ logits, long long ld, int T, int E, i
   }
   if (lane == 0) {
     for (int r = 0; r < k; ++r) {
-      ids[(long long)t * k + r] = ci[r] < E ? ci[r] : 0;
-      wts[(long long)t * k + r] = cv[r];
+      ids[r] = ci[r] < E ? ci[r] : 0;
+      wts[r] = cv[r];
     }
+  }
+}
+
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ logits, long long ld, int T, int E, int k, int mode, int renorm,
+                 int* __restrict__ ids, float* __restrict__ wts) {
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (t >= T) return;
+  constexpr int PER = MAX_E / 32;
+  float v[PER];
+  const float* x = logits + (long long)t * ld;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int e = j * 32 + lane;
+    v[j] = e < E ? x[e] : -INFINITY;
+  }
+  route_warp(v, lane, E, k, mode, renorm, ids + (long long)t * k, wts + (long long)t * k);
+}
+
+// Router in one launch: logits = W_r h + b_r for one token per CTA (each warp walks a quarter of the
+// experts, its lanes striding over the hidden row with 16-byte loads of the bf16 router matrix, which
+// stays in L2), then the top-k of `route_warp`.  For the decode-size steps of a mixture layer this
+// replaces a GEMM launch whose single output tile cannot occupy the chip, plus the routing launch.
+constexpr int RT_WARPS = 8;
+__global__ void __launch_bounds__(RT_WARPS * 32)
+moe_router_kernel(const __nv_bfloat16* __restrict__ h, long long ldh, const __nv_bfloat16* __restrict__ w,
+                  const float* __restrict__ bias, int T, int H, int E, int k, int mode, int renorm,
+                  int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ logits_out, long long ldl) {
+  pdl_wait();
+  pdl_launch();
+  extern __shared__ __align__(16) uint8_t rt_smem[];
+  __nv_bfloat16* hs = reinterpret_cast<__nv_bfloat16*>(rt_smem);            // [H]
+  float* sc = reinterpret_cast<float*>(rt_smem + (((size_t)H * 2 + 15) & ~size_t(15)));   // [MAX_E]
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nchunk = H >> 3;
+  for (int c = threadIdx.x; c < nchunk; c += RT_WARPS * 32)
+    reinterpret_cast<uint4*>(hs)[c] = *reinterpret_cast<const uint4*>(h + (long long)t * ldh + c * 8);
+  __syncthreads();
+  for (int e = warp; e < E; e += RT_WARPS) {
+    const __nv_bfloat16* wr = w + (long long)e * H;
+    float acc = 0.f;
+    for (int c = lane; c < nchunk; c += 32) {
+      const uint4 a = __ldg(reinterpret_cast<const uint4*>(wr) + c);
+      const uint4 b = reinterpret_cast<const uint4*>(hs)[c];
+      const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+      const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 x = __bfloat1622float2(a2[q]), y = __bfloat1622float2(b2[q]);
+        acc = fmaf(x.x, y.x, acc);
+        acc = fmaf(x.y, y.y, acc);
+      }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) sc[e] = acc + (bias ? bias[e] : 0.f);
+  }
+  __syncthreads();
+  if (logits_out)
+    for (int e = threadIdx.x; e < E; e += RT_WARPS * 32) logits_out[(long long)t * ldl + e] = sc[e];
+  if (warp == 0) {
+    constexpr int PER = MAX_E / 32;
+    float v[PER];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int e = j * 32 + lane;
+      v[j] = e < E ? sc[e] : -INFINITY;
+    }
+    route_warp(v, lane, E, k, mode, renorm, ids + (long long)t * k, wts + (long long)t * k);
   }
 }
 
@@ -118,6 +181,7 @@ moe_plan_kernel(const int* __restrict__ ids, int P, int E_total, int e_lo, int e
   __syncthreads();
   for (int p = threadIdx.x; p < P; p += blockDim.x) {
     const int id = ids[p];
+    if (id == -1) continue;        // an empty slot (expert-parallel receive buffer): no pair
     if (id < 0 || id >= E_total) {
       if (status) atomicCAS(status, 0, LK_ERR_BOUNDS | (5 << 8));
       continue;
@@ -217,6 +281,20 @@ LK_API int lk_moe_route(const float* logits, long long ld, int T, int E, int k, 
   if (T <= 0) return LKH_OK;
   if (E > MAX_E || k > MAX_K || k > E || k < 1) return LKH_BAD_ARG;
   moe_route_kernel<<<(T + 3) / 4, 128, 0, (cudaStream_t)stream>>>(logits, ld, T, E, k, mode, renorm, ids, wts);
+  lkh::count_launch();
+  return lkh::launch_status();
+}
+
+// h bf16 [T, ldh], w bf16 [E, H] (router matrix), bias f32 [E] or null -> ids / wts [T, k]; logits_out optional.
+LK_API int lk_moe_router(const void* h, long long ldh, const void* w, const float* bias, int T, int H, int E, int k,
+                         int mode, int renorm, int* ids, float* wts, float* logits_out, long long ldl, void* stream) {
+  if (T <= 0) return LKH_OK;
+  if (E > MAX_E || k > MAX_K || k > E || k < 1 || (H & 7) || (ldh & 7)) return LKH_BAD_ARG;
+  const size_t smem = (((size_t)H * 2 + 15) & ~size_t(15)) + MAX_E * sizeof(float);
+  if (smem > 48 * 1024) return LKH_TOO_LARGE;
+  lkh::launch_pdl(moe_router_kernel, dim3(T), dim3(RT_WARPS * 32), smem, (cudaStream_t)stream,
+                  (const __nv_bfloat16*)h, ldh, (const __nv_bfloat16*)w, bias, T, H, E, k, mode, renorm, ids, wts,
+                  logits_out, ldl);
   lkh::count_launch();
   return lkh::launch_status();
 }

@@ -54,6 +54,7 @@ struct TpNormParams {
   float* scales_t;                // [H / 128, scale_ld]
   long long scale_ld;
   int gather;                     // 0: the normalised rows stay on their owner (no phase C)
+  int local;                      // 1: `partial` is already the whole update of the owned rows (no phase A)
   int* status;
 };
 
@@ -153,7 +154,8 @@ tp_sum_norm_kernel(const TpNormParams p) {
   const long long hop2_row = hop2_row_bytes(H, f8);
 
   // ---- phase A: my partial of a row somebody else owns goes to its owner ----
-  for (int r = blockIdx.x; r < T; r += gridDim.x) {
+  const bool local = p.local != 0;
+  for (int r = blockIdx.x; r < T && !local; r += gridDim.x) {
     const int own = r / rpr;
     if (own == me) continue;
     char* dst = reinterpret_cast<char*>(p.sv.base[own]) + half_off + ((long long)me * rpr + (r - own * rpr)) * hop1_row;
@@ -182,7 +184,7 @@ tp_sum_norm_kernel(const TpNormParams p) {
         for (int s = 0; s < W; ++s) {
           if (s == me) {
             q[s][0] = *reinterpret_cast<const uint4*>(p.partial + (long long)r * p.ld_p + c * 8);
-          } else {
+          } else if (!local) {
             const char* src = mine + ((long long)s * rpr + rl) * hop1_row + (long long)c * 32;
             q[s][0] = ld_ll16(src);
             q[s][1] = ld_ll16(src + 16);
@@ -196,7 +198,7 @@ tp_sum_norm_kernel(const TpNormParams p) {
             add_bf16x2(q[s][0].y, a[2], a[3]);
             add_bf16x2(q[s][0].z, a[4], a[5]);
             add_bf16x2(q[s][0].w, a[6], a[7]);
-          } else {
+          } else if (!local) {
             const char* src = mine + ((long long)s * rpr + rl) * hop1_row + (long long)c * 32;
             if (!(q[s][0].y == epoch && q[s][0].w == epoch)) ll_wait16(src, epoch, q[s][0], ab, p.status, s);
             if (!(q[s][1].y == epoch && q[s][1].w == epoch)) ll_wait16(src + 16, epoch, q[s][1], ab, p.status, s);
@@ -254,7 +256,7 @@ tp_sum_norm_kernel(const TpNormParams p) {
           const unsigned hm = 0xFFFFu << (threadIdx.x & 16);
 #pragma unroll
           for (int s = 8; s > 0; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(hm, amax, s));
-          const float scale = amax > 0.f ? amax * (1.f / 448.f) : 1.f;
+          const float scale = e4m3_group_scale(amax);
           const float inv = 1.f / scale;
           uint2 q8;
           uint8_t* b = reinterpret_cast<uint8_t*>(&q8);
@@ -331,7 +333,7 @@ tp_sum_norm_kernel(const TpNormParams p) {
 // when `gather` is set, only the owned ones otherwise.
 LK_API int lk_tp_sum_norm(const void* view, const void* partial, long long ld_p, void* x, long long ld_x,
                           const float* w, float eps, int T, int H, void* out_bf16, long long ld_o, void* out_fp8,
-                          float* scales_t, long long scale_ld, int gather, int* status, void* stream) {
+                          float* scales_t, long long scale_ld, int gather, int local, int* status, void* stream) {
   if (!view || !partial || !x || !w || (!out_bf16 && !out_fp8)) return LKH_BAD_ARG;
   if (T <= 0) return LKH_OK;
   TpNormParams p;
@@ -360,6 +362,7 @@ LK_API int lk_tp_sum_norm(const void* view, const void* partial, long long ld_p,
   p.scales_t = scales_t;
   p.scale_ld = scale_ld;
   p.gather = gather;
+  p.local = local;
   p.status = status;
   const int grid = T < 148 ? T : 148;        // every CTA waits on peers: all of them resident at once
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);

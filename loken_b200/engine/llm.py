@@ -47,6 +47,9 @@ class StreamEvent:
     finish_reason: Optional[str] = None
     logprobs: Optional[List[tuple]] = None
     error: Optional[str] = None
+    progress: Optional[tuple] = None     # (prompt tokens read, prompt tokens to read) while a prompt is read
+    figures: Optional[dict] = None       # the request's `loken` figures, on the last event
+    cached_tokens: int = 0               # prompt tokens served from the prefix cache, on the last event
 
 
 @dataclass
@@ -62,6 +65,7 @@ class Completion:
     logprobs: Optional[List[tuple]] = None
     reasoning: str = ""
     tool_calls: List[dict] = field(default_factory=list)
+    figures: Optional[dict] = None
 
 
 class _Ticket:
@@ -71,6 +75,9 @@ class _Ticket:
         self.seq_id: Optional[int] = None
         self.t0 = time.perf_counter()
         self.on_event = None         # optional callable(event) invoked from the worker thread
+        from ..utils.figures import RequestFigures
+
+        self.fig = RequestFigures(arrival=self.t0)
 
 
 class EngineWorker(threading.Thread):
@@ -89,6 +96,11 @@ class EngineWorker(threading.Thread):
         self.last_error: Optional[str] = None
         self.busy_s = 0.0
         self.steps = 0
+        from ..utils.figures import EnergyLedger
+
+        dev = getattr(engine, "device", None)
+        self.ledger = (EnergyLedger.default(dev.index or 0) if dev is not None and dev.type == "cuda"
+                       else EnergyLedger())
 
     def submit(self, t: _Ticket):
         if not self.healthy:
@@ -122,6 +134,8 @@ class EngineWorker(threading.Thread):
                 try:
                     t.seq_id = self.engine.add_request(t.prompt_ids, t.params, salt=t.salt)
                     self.tickets[t.seq_id] = t
+                    t.fig.prompt_total = len(t.prompt_ids)
+                    self.ledger.open(t.fig)
                 except Exception as e:          # bad request: report to its caller only
                     self._deliver(t, e)
             elif op == "abort" and t.seq_id is not None:
@@ -159,15 +173,58 @@ class EngineWorker(threading.Thread):
                         self._forget(sid)
                     return
                 continue
-            self.busy_s += time.perf_counter() - t0
+            now = time.perf_counter()
+            self.busy_s += now - t0
             self.steps += 1
+            self._note_progress(t0, now)
             for o in outs:
                 t = self.tickets.get(o.seq_id)
                 if t is None:
                     continue
+                self.ledger.note_tokens(t.fig, len(o.new_tokens))
+                if o.finished:
+                    self._close_figures(t, o.seq_id, now)
+                    o.figures = t.fig.to_json()
+                    o.cached_tokens = getattr(self.engine.seqs.get(o.seq_id), "cached_tokens", 0)
                 self._deliver(t, o)
                 if o.finished:
                     self._forget(o.seq_id)
+
+    def _note_progress(self, step_start: float, now: float):
+        """After a step: which requests have started their prompt, how far each prompt has been read,
+        who produced a first token (request figures and the `loken-prefill` progress lines)."""
+        for sid, t in self.tickets.items():
+            seq = self.engine.seqs.get(sid)
+            if seq is None:
+                continue
+            f = t.fig
+            state = getattr(seq, "state", "running")
+            if f.prefill_start is None and state != "waiting":
+                f.prefill_start = step_start
+            cached = getattr(seq, "cached_tokens", 0)
+            n_prompt = len(getattr(seq, "prompt", t.prompt_ids))
+            computed = getattr(seq, "computed", n_prompt)
+            total = max(0, n_prompt - cached)
+            done = max(0, min(computed, n_prompt) - cached)
+            self.ledger.note_tokens(f, max(0, done - f.prompt_done))
+            f.prompt_total, f.prompt_done = total, done
+            if f.first_token is None and getattr(seq, "output", None):
+                f.first_token = now
+
+    def _close_figures(self, t: "_Ticket", sid: int, now: float):
+        f = t.fig
+        seq = self.engine.seqs.get(sid)
+        if f.prefill_start is None:
+            f.prefill_start = now
+        f.end = now
+        alloc = getattr(self.engine, "alloc", None)
+        if seq is not None and alloc is not None and hasattr(alloc, "num_blocks"):
+            f.kv_used = len(getattr(seq, "prompt", [])) + len(getattr(seq, "output", []))
+            f.kv_capacity = alloc.num_blocks * alloc.block_size
+        if seq is not None:
+            f.accepted_drafts = getattr(seq, "accepted_drafts", 0)
+            f.rejected_drafts = getattr(seq, "rejected_drafts", 0)
+        self.ledger.close(f)
 
     def _forget(self, sid: int):
         self.tickets.pop(sid, None)
@@ -375,14 +432,24 @@ class LLM:
         budget = params.thinking_token_budget
         open_tag, close_tag = "<think>", "</think>"
         n_think, inside, seen_text, all_tokens = 0, False, "", []
+        deadline = time.monotonic() + timeout_s
+        got_token = False
         try:
             while True:
                 try:
-                    ev = ticket.events.get(timeout=timeout_s)
+                    # until the first token arrives the wait wakes every 250 ms to report how far the prompt
+                    # has been read (`docs/API.md:499-514` of the reference: `: loken-prefill` comment lines)
+                    ev = ticket.events.get(timeout=timeout_s if got_token else 0.25)
                 except queue.Empty:
+                    if not got_token and time.monotonic() < deadline:
+                        f = ticket.fig
+                        if f.prompt_total > 0:
+                            yield StreamEvent(progress=(int(f.prompt_done), int(f.prompt_total)))
+                        continue
                     self.abort(ticket)
                     yield StreamEvent(finished=True, finish_reason="timeout", error="generation timed out")
                     return
+                got_token = True
                 if isinstance(ev, Exception):
                     yield StreamEvent(finished=True, finish_reason="error", error=str(ev))
                     return
@@ -396,7 +463,8 @@ class LLM:
                 out, hit = stops.push(text)
                 if hit:
                     self.abort(ticket)
-                    yield StreamEvent(out, list(ev.new_tokens), True, "stop", ev.logprobs)
+                    yield StreamEvent(out, list(ev.new_tokens), True, "stop", ev.logprobs,
+                                      figures=self._figures_now(ticket, ev), cached_tokens=self._cached(ticket, ev))
                     return
                 if budget is not None and not ev.finished:
                     all_tokens += list(ev.new_tokens)
@@ -418,12 +486,29 @@ class LLM:
                         return
                 if ev.finished:
                     out += stops.flush()
-                    yield StreamEvent(out, list(ev.new_tokens), True, ev.finish_reason, ev.logprobs)
+                    yield StreamEvent(out, list(ev.new_tokens), True, ev.finish_reason, ev.logprobs,
+                                      figures=self._figures_now(ticket, ev), cached_tokens=self._cached(ticket, ev))
                     return
                 yield StreamEvent(out, list(ev.new_tokens), False, None, ev.logprobs)
         finally:
             if ticket.seq_id is not None and ticket.seq_id in self.worker.tickets:
                 self.abort(ticket)
+
+    @staticmethod
+    def _figures_now(ticket: _Ticket, ev) -> dict:
+        """The request's figures: what the worker closed at the last token, or (a stop string ended the
+        request here, before the engine's own end) a closing made now."""
+        figs = getattr(ev, "figures", None)
+        if figs is not None:
+            return figs
+        f = ticket.fig
+        if f.end is None:
+            f.end = time.perf_counter()
+        return f.to_json()
+
+    @staticmethod
+    def _cached(ticket: _Ticket, ev) -> int:
+        return int(getattr(ev, "cached_tokens", 0) or 0)
 
     def generate(self, prompt=None, params: Optional[GenerationParams] = None, *, messages=None, tools=None,
                  **render_kw) -> Completion:

@@ -125,12 +125,17 @@ class MoePlan:
         self.tile_rows = torch.zeros(self.max_tiles, **i32)
         self.ntiles = torch.zeros(1, **i32)
         self.bn = 16
+        # expert-parallel receive side: expert id (-1 = empty) and (source rank, token, choice) of every slot
+        self.slot_expert = torch.full((P,), -1, **i32)
+        self.slot_src = torch.zeros(P, **i32)
 
 
 def pick_group_bn(pairs: int, e_cnt: int, quantised: bool) -> int:
     avg = pairs / max(e_cnt, 1)
     if avg <= 16:
         return 16
+    if avg <= 32 and quantised:
+        return 32 if avg > 16 else 16
     if avg <= 64 or quantised and avg <= 96:
         return 64
     return 128 if quantised else 256
@@ -144,6 +149,8 @@ class MoeRunner:
         self.device = dev
         m0 = next(l for l in weights.layers if l is not None).moe
         k, H, I = cfg.top_k, cfg.hidden, cfg.expert_intermediate
+        world = comm.size if comm is not None else 1
+        cap = cap + (world if world > 1 else 0)     # receive slots are rounded up to whole rows per rank
         self.cap = cap
         self.plan = MoePlan(cap, k, m0.e_cnt, dev)
         bf = dict(dtype=torch.bfloat16, device=dev)
@@ -153,14 +160,32 @@ class MoeRunner:
         self.gu = torch.zeros(P + 256, 2 * I, **bf)
         self.act = torch.zeros(P + 256, I, **bf)
         self.y = torch.zeros(P + 256, H, **bf)
+        self.xr = torch.zeros(P, H, **bf) if world > 1 else None     # rows received from other ranks, one per slot
         self.wsp = Workspace.get(dev)
+        # MXFP4 experts run as stored on the block-scaled tensor-core path (ops/mx.py): activations are
+        # quantised to e4m3 + E8M0 exponents by the gather and by the GLU, nothing is dequantised
+        self.use_mx = (m0.fmt == "mxfp4" and H % 32 == 0 and I % 32 == 0)
+        if self.use_mx:
+            from ..ops import mx
+
+            self.xs8 = mx.alloc_mx_act(P + 256, H, dev)
+            self.act8 = mx.alloc_mx_act(P + 256, I, dev)
+
+    ROUTER_FUSED_MAX_T = 512     # above it the router runs as a tensor-core GEMM + the routing kernel
 
     def route(self, moe: MoeWeights, h: torch.Tensor, T: int):
+        """Router logits and top-k of rows h[:T] -> plan.ids / plan.wts [T, k]."""
         cfg, pl = self.cfg, self.plan
+        lib = cuda_lib()
+        if T <= self.ROUTER_FUSED_MAX_T and cfg.hidden * 2 + 1024 <= 48 * 1024 and moe.router_w.is_contiguous():
+            check(lib.lk_moe_router(ptr(h), C.c_longlong(h.stride(0)), ptr(moe.router_w), ptr(moe.router_b), T,
+                                    cfg.hidden, cfg.n_experts, cfg.top_k, ROUTER_MODE[cfg.router], int(cfg.renorm),
+                                    ptr(pl.ids), ptr(pl.wts), None, C.c_longlong(0), stream()), "lk_moe_router")
+            return
         gemm.linear_bf16(h[:T], moe.router_w, bias=moe.router_b, out=self.logits[:T], out_fp32=True)
-        check(cuda_lib().lk_moe_route(ptr(self.logits), C.c_longlong(self.logits.stride(0)), T, cfg.n_experts,
-                                      cfg.top_k, ROUTER_MODE[cfg.router], int(cfg.renorm), ptr(pl.ids), ptr(pl.wts),
-                                      stream()), "lk_moe_route")
+        check(lib.lk_moe_route(ptr(self.logits), C.c_longlong(self.logits.stride(0)), T, cfg.n_experts,
+                               cfg.top_k, ROUTER_MODE[cfg.router], int(cfg.renorm), ptr(pl.ids), ptr(pl.wts),
+                               stream()), "lk_moe_route")
 
     def make_plan(self, moe: MoeWeights, T: int):
         cfg, pl = self.cfg, self.plan
@@ -171,20 +196,79 @@ class MoeRunner:
                                      ptr(pl.tile_rows), ptr(pl.ntiles), ptr(self.wsp.status), stream()),
               "lk_moe_plan")
 
+    def expert_gemms(self, moe: MoeWeights, h: torch.Tensor, P: int, k: int):
+        """gate_up -> GLU -> down over the planned pairs: pair p reads row p // k of `h`, its output lands
+        in row plan.pair_row[p] of `self.y`."""
+        cfg, pl = self.cfg, self.plan
+        H, I = cfg.hidden, cfg.expert_intermediate
+        lib = cuda_lib()
+        if self.use_mx:
+            from ..ops import mx
+
+            if getattr(moe, "gate_up_mx", None) is None:
+                moe.gate_up_mx, moe.down_mx = mx.mx_weight(moe.gate_up), mx.mx_weight(moe.down)
+            mx.quant_mx8(h, out=self.xs8, rows=P, K=H, pair_row=pl.pair_row, kdiv=k)
+            mx.grouped_linear_mx(self.xs8, moe.gate_up_mx, 2 * I, pl, moe.gate_up_b, self.gu)
+            mx.quant_mx8(self.gu, out=self.act8, rows=P, K=I, glu_mode=cfg.glu_mode, alpha=cfg.glu_alpha,
+                         limit=cfg.glu_limit)
+            mx.grouped_linear_mx(self.act8, moe.down_mx, H, pl, moe.down_b, self.y)
+        else:
+            check(lib.lk_moe_permute(ptr(h), C.c_longlong(h.stride(0)), ptr(pl.pair_row), P, k, H, ptr(self.xs),
+                                     C.c_longlong(self.xs.stride(0)), stream()), "lk_moe_permute")
+            grouped_linear(self.xs, moe.gate_up, 2 * I, pl, moe.gate_up_b, self.gu)
+            rows.glu(self.gu, mode=cfg.glu_mode, alpha=cfg.glu_alpha, limit=cfg.glu_limit, out=self.act, rows=P)
+            grouped_linear(self.act, moe.down, H, pl, moe.down_b, self.y)
+
     def experts(self, moe: MoeWeights, h: torch.Tensor, T: int, out: torch.Tensor, accumulate: bool = False):
         """Runs this rank's experts over the planned pairs of h[:T] and writes (or adds) the
         weighted sum of their outputs to out[:T]."""
         cfg, pl = self.cfg, self.plan
-        k, H, I = cfg.top_k, cfg.hidden, cfg.expert_intermediate
-        P = T * k
+        k, H = cfg.top_k, cfg.hidden
+        self.expert_gemms(moe, h, T * k, k)
+        check(cuda_lib().lk_moe_combine(ptr(self.y), C.c_longlong(self.y.stride(0)), ptr(pl.pair_row), ptr(pl.wts),
+                                        T, k, H, ptr(out), C.c_longlong(out.stride(0)), int(accumulate), stream()),
+              "lk_moe_combine")
+
+    # ---- expert parallelism with a token-sharded residual stream (csrc/cuda/ep_moe.cu) ----
+    def can_dispatch(self, T: int) -> bool:
+        c = self.comm
+        if c is None or c.size <= 1 or not hasattr(c, "heap") or self.cfg.n_experts % c.size:
+            return False
+        H, k = self.cfg.hidden, self.cfg.top_k
+        rpr = (T + c.size - 1) // c.size
+        need = 256 + c.size * rpr * k * (16 + 4 * H)
+        return (T + c.size) * k <= self.plan.pair_row.numel() and need <= c.heap.ll_half_bytes
+
+    def forward_ep(self, il: int, moe: MoeWeights, h: torch.Tensor, out: torch.Tensor, T: int):
+        """Rows [lo, hi) of `h` are this rank's normalised hidden rows (the residual stream is sharded by
+        rows); rows [lo, hi) of `out` receive their mixture output.  Every (token, choice) pair travels to
+        the rank that holds its expert and its result travels back: dispatch -> grouped expert GEMMs ->
+        combine in choice order with the router weights, all over peer memory, no host round trip."""
+        cfg, pl, comm = self.cfg, self.plan, self.comm
         lib = cuda_lib()
-        check(lib.lk_moe_permute(ptr(h), C.c_longlong(h.stride(0)), ptr(pl.pair_row), P, k, H, ptr(self.xs),
-                                 C.c_longlong(self.xs.stride(0)), stream()), "lk_moe_permute")
-        grouped_linear(self.xs, moe.gate_up, 2 * I, pl, moe.gate_up_b, self.gu)
-        rows.glu(self.gu, mode=cfg.glu_mode, alpha=cfg.glu_alpha, limit=cfg.glu_limit, out=self.act, rows=P)
-        grouped_linear(self.act, moe.down, H, pl, moe.down_b, self.y)
-        check(lib.lk_moe_combine(ptr(self.y), C.c_longlong(self.y.stride(0)), ptr(pl.pair_row), ptr(pl.wts), T, k, H,
-                                 ptr(out), C.c_longlong(out.stride(0)), int(accumulate), stream()), "lk_moe_combine")
+        view = C.byref(comm.heap.view)
+        k, H, E = cfg.top_k, cfg.hidden, cfg.n_experts
+        lo, hi = comm.owned_rows(T)
+        n = hi - lo
+        st = ptr(self.wsp.status)
+        if n > 0:
+            self.route(moe, h[lo:hi], n)
+        check(lib.lk_ep_dispatch(view, ptr(h), C.c_longlong(h.stride(0)), ptr(pl.ids), T, H, k, E, st, stream()),
+              "lk_ep_dispatch")
+        check(lib.lk_ep_meta(view, T, H, k, E, ptr(pl.slot_expert), ptr(pl.slot_src), st, stream()), "lk_ep_meta")
+        S = int(lib.lk_ep_slots(view, T, k))
+        pl.bn = pick_group_bn(T * k * moe.e_cnt // E, moe.e_cnt, not isinstance(moe.gate_up, torch.Tensor))
+        check(lib.lk_moe_plan(ptr(pl.slot_expert), S, E, moe.e_lo, moe.e_cnt, pl.bn, pl.max_tiles, ptr(pl.offsets),
+                              ptr(pl.pair_row), ptr(pl.tile_expert), ptr(pl.tile_row0), ptr(pl.tile_rows),
+                              ptr(pl.ntiles), st, stream()), "lk_moe_plan")
+        check(lib.lk_ep_gather(view, T, H, k, E, ptr(pl.slot_expert), ptr(self.xr), C.c_longlong(self.xr.stride(0)),
+                               st, stream()), "lk_ep_gather")
+        self.expert_gemms(moe, self.xr, S, 1)
+        check(lib.lk_ep_return(view, T, H, k, E, ptr(pl.slot_src), ptr(pl.pair_row), ptr(self.y),
+                               C.c_longlong(self.y.stride(0)), stream()), "lk_ep_return")
+        check(lib.lk_ep_combine(view, T, H, k, E, ptr(pl.wts), ptr(out), C.c_longlong(out.stride(0)), st, stream()),
+              "lk_ep_combine")
+        comm.collectives += 2
 
     def forward(self, il: int, moe: MoeWeights, h: torch.Tensor, out: torch.Tensor, T: int):
         """h [T, H] bf16 (normalised hidden states, replicated on every rank) -> out [T, H]."""

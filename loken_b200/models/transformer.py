@@ -86,6 +86,7 @@ class DecoderModel:
         self.buf = Buffers(self.cfg, weights, max_tokens, self.device)
         self.moe_runner = moe_runner
         self._kg = None    # gathered K / V^T scratch for prefill, grown on demand
+        self._delta_local = False   # the pending update is complete for the owned rows (after a sharded mixture layer)
         self.sharded_steps = 0   # forwards issued with the row-sharded residual stream (eager or captured)
 
     # ---- one linear layer in whatever format its weights are held ----
@@ -185,17 +186,22 @@ class DecoderModel:
         """True when this step keeps the residual stream sharded by rows over the tensor-parallel
         ranks: `delta` then holds this rank's PARTIAL sums and every norm is `comm.sum_norm`."""
         c = self.comm
-        return (c is not None and c.size > 1 and getattr(c, "fused_norm", False) and not self.cfg.is_moe
-                and getattr(self.w, "layer_range", None) is None and c.can_sum_norm(T, self.cfg.hidden))
+        if not (c is not None and c.size > 1 and getattr(c, "fused_norm", False)
+                and getattr(self.w, "layer_range", None) is None and c.can_sum_norm(T, self.cfg.hidden)):
+            return False
+        # a mixture model also needs the expert-parallel dispatch to fit this step
+        return not self.cfg.is_moe or self.moe_runner.can_dispatch(T)
 
-    def _norm(self, x, w, delta, T: int, f8: bool, shard: bool, out=None):
+    def _norm(self, x, w, delta, T: int, f8: bool, shard: bool, out=None, gather: bool = True,
+              local: bool = False):
         """x += delta; RMSNorm(x) * w -> b.h8 (e4m3) or `out` / b.h (bf16).  Sharded: `delta` is this
-        rank's partial of a row-parallel layer and the sum over ranks happens here."""
+        rank's partial of a row-parallel layer (or, `local`, the finished update of the rows it owns)
+        and the sum over ranks happens here; without `gather` the normalised rows stay on their owner."""
         b = self.buf
         out = b.h if out is None else out
         if shard and delta is not None:
             self.comm.sum_norm(delta, x, w, self.cfg.rms_eps, T, out=None if f8 else out,
-                               out_fp8=b.h8 if f8 else None)
+                               out_fp8=b.h8 if f8 else None, gather=gather, local=local)
         else:
             rows.add_rmsnorm(x, w, self.cfg.rms_eps, delta=delta, out=None if f8 else out,
                              out_fp8=b.h8 if f8 else None, rows=T)
@@ -211,14 +217,21 @@ class DecoderModel:
         for il in range(lo, hi):
             lw = w.layers[il]
             # attention block
-            self._norm(b.x, lw.attn_norm, delta, T, lw.wqkv.wants_fp8, shard)
+            self._norm(b.x, lw.attn_norm, delta, T, lw.wqkv.wants_fp8, shard, local=self._delta_local)
+            self._delta_local = False
             self._linear(lw.wqkv, b.h, b.h8, b.qkv, T)
             got8 = self._attention(il, inp, T, lw.wo.wants_fp8)
             if lw.wo.wants_fp8 and not got8:
                 rows.quant_fp8(b.attn, out=b.attn8, rows=T)
             self._linear(lw.wo, b.attn, b.attn8, b.delta, T, reduce=not shard)
             # feed-forward block
-            if cfg.is_moe:
+            if cfg.is_moe and shard:
+                # token-sharded mixture layer: the owner of a row normalises it, routes it and sends its
+                # pairs to the experts' ranks; the combined output is the finished update of its own rows
+                self._norm(b.x, lw.ffn_norm, b.delta, T, False, True, gather=False)
+                self.moe_runner.forward_ep(il, lw.moe, b.h, b.delta, T)
+                self._delta_local = True
+            elif cfg.is_moe:
                 rows.add_rmsnorm(b.x, lw.ffn_norm, cfg.rms_eps, delta=b.delta, out=b.h, rows=T)
                 self.moe_runner.forward(il, lw.moe, b.h, b.delta, T)
             else:
@@ -242,7 +255,8 @@ class DecoderModel:
     def head(self, inp: StepInputs, delta: Optional[torch.Tensor]) -> torch.Tensor:
         cfg, w, b = self.cfg, self.w, self.buf
         T = inp.T
-        self._norm(b.x, w.out_norm, delta, T, False, self.sharded(T))
+        self._norm(b.x, w.out_norm, delta, T, False, self.sharded(T), local=self._delta_local)
+        self._delta_local = False
         if inp.logit_rows is not None:
             n = inp.n_logit_rows
             torch.index_select(b.h, 0, inp.logit_rows[:n], out=b.hsel[:n])

@@ -27,10 +27,19 @@ class Fp8Weight:
     (the `weight` / `weight_scale_inv` pair of block-fp8 checkpoints)."""
     data: torch.Tensor
     scale: torch.Tensor
+    _pow2: Optional[bool] = None
 
     @property
     def shape(self):
         return self.data.shape
+
+    @property
+    def pow2(self) -> bool:
+        """Every block scale is a power of two (E8M0 checkpoints): the block-scaled MMA applies them."""
+        if self._pow2 is None:
+            m, _ = torch.frexp(self.scale.float())
+            self._pow2 = bool(((m == 0.5) & (self.scale > 0)).all().item())
+        return self._pow2
 
 
 @dataclass
@@ -107,6 +116,9 @@ def gemm_raw(kind, A, B, out, out_sa, out_sb, *, bias=None, bias_on_a=False, res
 
 
 SWAP_MAX_M = 256
+FP8_MX = True           # block-fp8 weights with power-of-two scales run on the block-scaled MMA (lk_gemm_mx)
+FP8_MX_MAX_M = 256      # ... for decode-size batches (tokens on the MMA N side)
+FP8_MX_BN = 0           # measurement hook: N tile of that path (0 = the launcher's choice)
 # fp8 carries one activation scale per token in the swapped form: measured faster only for a handful of tokens
 FP8_BN_OVERRIDE = 0     # measurement hook: N-tile width of the tokens-on-M form (0 = the rule in linear_fp8)
 FP8_SWAP_MAX_M = 16     # measured: up to 16 tokens the weights-on-M form is faster (93 vs 107 us on 57344 x 8192)
@@ -142,6 +154,25 @@ def linear_fp8(x: Fp8Act, w: Fp8Weight, *, bias: Optional[torch.Tensor] = None,
         out = torch.empty(M, N, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=xd.device)
     ldo = out.stride(0)
     sld = x.scale_t.stride(0)
+    if FP8_MX and M <= FP8_MX_MAX_M and symm is None and not out_fp32 and residual is None and w.pow2:
+        # power-of-two block scales: one accumulation over all of K on the block-scaled MMA (gemm_mx.cu)
+        wsp = Workspace.get(xd.device)
+        a = GemmArgs()
+        a.kind = KIND_F8BLK
+        a.A, a.B = ptr(w.data), ptr(xd)
+        a.Ra, a.Rb, a.K = N, M, K
+        a.lda, a.ldb = w.data.stride(0), xd.stride(0)
+        a.out, a.out_sa, a.out_sb = ptr(out), 1, ldo
+        a.bias, a.bias_on_a = ptr(bias), 1
+        a.a_scale, a.a_mode, a.a_ld = ptr(w.scale), SCALE_WBLOCK, w.scale.stride(0)
+        a.b_scale, a.b_mode, a.b_ld = ptr(x.scale_t), SCALE_ACT_T, sld
+        a.bn, a.splits = FP8_MX_BN, splits
+        a.ws, a.ws_floats = ptr(wsp.ws), wsp.ws.numel()
+        a.counters, a.n_counters = ptr(wsp.counters), wsp.counters.numel()
+        a.status = ptr(wsp.status)
+        check(cuda_lib().lk_gemm_mx(C.byref(a), stream()), "lk_gemm_mx (fp8)")
+        gemm_raw.last_fused = False
+        return out
     if M <= FP8_SWAP_MAX_M:
         gemm_raw(KIND_F8BLK, w.data, xd, out, 1, ldo, bias=bias, bias_on_a=True, residual=residual,
                  a_scale=w.scale, a_mode=SCALE_WBLOCK, a_ld=w.scale.stride(0), b_scale=x.scale_t,
@@ -156,8 +187,20 @@ def linear_fp8(x: Fp8Act, w: Fp8Weight, *, bias: Optional[torch.Tensor] = None,
 
 # ---- quantisers used at load time and by the tests (plain torch, not a hot path) -------------
 
-def quantize_weight_fp8(w: torch.Tensor) -> Fp8Weight:
-    """[N, K] float -> e4m3 with one f32 scale per 128x128 block (amax / 448)."""
+def pow2_ceil(t: torch.Tensor) -> torch.Tensor:
+    """Smallest power of two >= t (t > 0), exactly (no log2 rounding)."""
+    m, e = torch.frexp(t)            # t = m * 2^e, m in [0.5, 1)
+    return torch.ldexp(torch.ones_like(t), torch.where(m == 0.5, e - 1, e))
+
+
+WEIGHT_SCALE_UE8M0 = True    # random-init block-fp8 weights get power-of-two (E8M0) block scales
+
+
+def quantize_weight_fp8(w: torch.Tensor, ue8m0: Optional[bool] = None) -> Fp8Weight:
+    """[N, K] float -> e4m3 with one f32 scale per 128x128 block.  `ue8m0` (the default): the scale is
+    the smallest power of two with amax / scale <= 448, the E8M0 `.scale` variant of block-fp8
+    checkpoints, which the block-scaled MMA applies in hardware; otherwise amax / 448 (`weight_scale_inv`)."""
+    ue8m0 = WEIGHT_SCALE_UE8M0 if ue8m0 is None else ue8m0
     N, K = w.shape
     nb, kb = (N + 127) // 128, (K + 127) // 128
     wp = torch.zeros(nb * 128, kb * 128, dtype=torch.float32, device=w.device)
@@ -165,6 +208,8 @@ def quantize_weight_fp8(w: torch.Tensor) -> Fp8Weight:
     blocks = wp.view(nb, 128, kb, 128)
     amax = blocks.abs().amax(dim=(1, 3))
     scale = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax))
+    if ue8m0:
+        scale = pow2_ceil(scale)
     q = (blocks / scale[:, None, :, None]).clamp(-448, 448).view(nb * 128, kb * 128)[:N, :K]
     return Fp8Weight(q.to(torch.float8_e4m3fn).contiguous(), scale.contiguous())
 
@@ -176,12 +221,13 @@ def dequantize_weight_fp8(w: Fp8Weight) -> torch.Tensor:
 
 
 def quantize_act_fp8_ref(x: torch.Tensor, ld: Optional[int] = None) -> Fp8Act:
-    """Reference of the activation quantiser: per token per 128 values, scale = amax / 448."""
+    """Reference of the activation quantiser: per token per 128 values, scale = the smallest power of
+    two with amax / scale <= 448."""
     M, K = x.shape
     assert K % 128 == 0
     g = x.float().view(M, K // 128, 128)
     amax = g.abs().amax(dim=2)
-    scale = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax))
+    scale = torch.where(amax > 0, pow2_ceil((amax / 448.0).clamp_min(2.0 ** -126)), torch.ones_like(amax))
     q = (g / scale[:, :, None]).view(M, K).to(torch.float8_e4m3fn)
     ld = ld or ((M + 3) // 4 * 4)
     st = torch.zeros(K // 128, ld, dtype=torch.float32, device=x.device)

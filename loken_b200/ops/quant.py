@@ -25,6 +25,7 @@ from ._lib import GemmArgs, Workspace, check, cuda_lib, ptr, stream
 from .gemm import KIND_BF16, NUM_SMS
 
 AQ_W8, AQ_W8G16, AQ_W4, AQ_MX4 = 1, 2, 3, 4
+MX_NATIVE = True      # MXFP4 on the block-scaled MMA (False: expanded to bf16 by the dequant warps)
 FMT_OF_TYPE = {gguf.Q8_0: AQ_W8, gguf.Q6_K: AQ_W8G16, gguf.Q4_K: AQ_W4, gguf.MXFP4: AQ_MX4}
 TYPE_OF_NAME = {"q8_0": gguf.Q8_0, "q4_k": gguf.Q4_K, "q6_k": gguf.Q6_K, "mxfp4": gguf.MXFP4}
 
@@ -153,6 +154,15 @@ def linear_gguf(x: torch.Tensor, w: QuantWeight, *, bias: Optional[torch.Tensor]
     assert K == w.K and x.stride(1) == 1
     if out is None:
         out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    if w.aq_fmt == AQ_MX4 and MX_NATIVE and K % 32 == 0:
+        # MXFP4 runs as stored on the block-scaled tensor-core path: activations to e4m3 + E8M0 exponents
+        # per 32 values, weights' nibbles and exponents straight into the MMA (ops/mx.py)
+        from . import mx
+
+        if getattr(w, "_mx", None) is None:
+            w._mx = mx.mx_weight(w)
+        xa = mx.quant_mx8(x, rows=M)
+        return mx.linear_mx(xa, w._mx, bias=bias, out=out, rows=M)
     wsp = Workspace.get(x.device)
     bn = _pick_bn(M)
     tiles = ((N + 127) // 128) * ((M + bn - 1) // bn)

@@ -95,7 +95,8 @@ class SymmHeap:
 
 
 class SymmComm:
-    def __init__(self, device, max_rows: int, hidden: int, group=None, push_max_bytes: int = 4 << 20):
+    def __init__(self, device, max_rows: int, hidden: int, group=None, push_max_bytes: int = 4 << 20,
+                 top_k: int = 0):
         self.device = device
         self.group = group
         self.size = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -106,6 +107,10 @@ class SymmComm:
         self.max_rows, self.hidden = max_rows, hidden
         hop1 = (max_rows + world) * hidden * 4
         hop2 = max_rows * (hidden * 4 + hidden // 16 + 16)
+        if top_k:
+            # expert-parallel dispatch: every (token, choice) pair may land on one rank: a 16-byte header and
+            # 4 bytes per value per slot, world * ceil(max_rows / world) * top_k slots (csrc/cuda/ep_moe.cu)
+            hop1 = max(hop1, 256 + (max_rows + world) * top_k * (16 + hidden * 4) - hop2)
         self.heap = SymmHeap(max_rows * hidden * 2, group=group, ll_hop1_bytes=hop1, ll_hop2_bytes=hop2)
         self.nccl = NcclComm(group)
         self.push_max_bytes = min(push_max_bytes, self.heap.slot_bytes)
@@ -123,10 +128,11 @@ class SymmComm:
             and hidden % 8 == 0 and self.size in (2, 4, 8)
 
     def sum_norm(self, partial: torch.Tensor, x: torch.Tensor, w: torch.Tensor, eps: float, rows: int, *,
-                 out: Optional[torch.Tensor] = None, out_fp8=None, gather: bool = True):
+                 out: Optional[torch.Tensor] = None, out_fp8=None, gather: bool = True, local: bool = False):
         """x[own rows] += sum over ranks of partial[own rows]; normalised rows -> `out` (bf16) or `out_fp8`
         (e4m3 + per-128 scales): every row on every rank when `gather`, else the owned rows only.
-        Row r belongs to rank r // ceil(rows / world)."""
+        Row r belongs to rank r // ceil(rows / world).  `local`: `partial` already is the complete update of
+        the owned rows (the expert-parallel combine's output), nothing is summed over ranks."""
         H = x.shape[1]
         check(cuda_lib().lk_tp_sum_norm(C.byref(self.heap.view), ptr(partial), C.c_longlong(partial.stride(0)),
                                         ptr(x), C.c_longlong(x.stride(0)), ptr(w), C.c_float(eps), rows, H,
@@ -134,7 +140,7 @@ class SymmComm:
                                         ptr(out_fp8.data) if out_fp8 is not None else None,
                                         ptr(out_fp8.scale_t) if out_fp8 is not None else None,
                                         C.c_longlong(out_fp8.scale_t.stride(0) if out_fp8 is not None else 0),
-                                        int(gather), ptr(self.wsp.status), stream()), "lk_tp_sum_norm")
+                                        int(gather), int(local), ptr(self.wsp.status), stream()), "lk_tp_sum_norm")
         self.collectives += 1
 
     def owned_rows(self, rows: int) -> tuple:

@@ -33,6 +33,8 @@ class StepOutput:
     finished: bool = False
     finish_reason: Optional[str] = None
     logprobs: Optional[List[tuple]] = None     # per new token: (logprob, [(token id, logprob), ...])
+    figures: Optional[dict] = None             # filled by the worker on the last output of a request
+    cached_tokens: int = 0
 
 
 @dataclass

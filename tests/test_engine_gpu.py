@@ -41,8 +41,9 @@ def test_prefill_logits_match_oracle(arch, fmt, kw):
     eng.add_request(prompt, GREEDY)
     eng.step()
     got = eng.runner.model.buf.logits[0]
-    # e4m3 activations carry ~3% rounding per element into every product of the fp8 model
-    assert _cos(got, ref[-1]) > (0.99 if fmt == "fp8_block" else 0.998)
+    # e4m3 activations carry ~3% rounding per element into every product of the fp8 model, and into the
+    # expert products of an MXFP4 model (block-scaled MMA: weights as stored, activations e4m3)
+    assert _cos(got, ref[-1]) > (0.99 if fmt in ("fp8_block", "mxfp4") else 0.998)
     gap = torch.topk(ref[-1], 2).values
     if (gap[0] - gap[1]) > 0.05 * ref[-1].abs().max():
         assert int(got.argmax()) == int(ref[-1].argmax())

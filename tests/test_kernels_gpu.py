@@ -67,13 +67,17 @@ def test_linear_bf16_bias_residual_fp32_splitk():
 # ------------------------------------------------------------------ GEMM (block-scaled fp8)
 @pytest.mark.parametrize("M,N,K", [(1, 256, 256), (7, 384, 512), (64, 1024, 1024), (128, 512, 2048),
                                    (256, 256, 384), (400, 768, 1024), (64, 19328, 512), (7, 19200, 384)])
-def test_linear_fp8_block(M, N, K):
+@pytest.mark.parametrize("ue8m0", [True, False])
+def test_linear_fp8_block(M, N, K, ue8m0):
+    """Power-of-two (E8M0) block scales run on the block-scaled MMA for decode-size batches
+    (gemm_mx.cu); arbitrary f32 scales, and larger batches, on the per-K-block fold of gemm_tc.cuh."""
     from loken_b200.ops import gemm
 
     torch.manual_seed(M + N + K)
     x = torch.randn(M, K, device=DEV) * torch.rand(M, 1, device=DEV) * 2
     w = torch.randn(N, K, device=DEV) * 0.05
-    wq = gemm.quantize_weight_fp8(w)
+    wq = gemm.quantize_weight_fp8(w, ue8m0=ue8m0)
+    assert wq.pow2 == ue8m0
     xq = gemm.quantize_act_fp8_ref(x.bfloat16())
     ref = gemm.dequantize_act_fp8(xq, M) @ gemm.dequantize_weight_fp8(wq).t()
     out = gemm.linear_fp8(xq, wq)

@@ -56,6 +56,23 @@ def test_tensor_parallel_matches_single_gpu(tmp_path, fmt):
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("fmt", ["bf16", "mxfp4"])
+def test_expert_parallel_matches_single_gpu(tmp_path, fmt):
+    """EP = N reproduces EP = 1, with the mixture layers run replicated + all-reduce and with the
+    all-to-all dispatch / combine over peer memory on a token-sharded residual stream."""
+    n = min(_ngpu(), 8)
+    n = 8 if n >= 8 else 4 if n >= 4 else 2
+    rep = _run("mp_ep_worker.py", n, str(tmp_path / "ep.json"), 29661, (fmt,))
+    print(json.dumps(rep))
+    bound = 0.9999 if fmt == "bf16" else 0.98
+    for name in ("replicated", "dispatch"):
+        assert rep[f"match_{name}"], (name, rep)
+        assert rep[f"logits_cos_min_{name}"] >= bound, (name, rep)
+        assert rep[f"status_{name}"] == 0, (name, rep)
+    assert rep["sharded_steps_dispatch"] > 0 and rep["sharded_steps_replicated"] == 0
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs two GPUs")
 def test_pipeline_parallel_matches_single_gpu(tmp_path):
     rep = _run("mp_pp_worker.py", 2, str(tmp_path / "pp.json"), 29651)
     assert rep["tokens_match_oracle"] and rep["ranks_agree"], rep
