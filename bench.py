@@ -45,6 +45,18 @@ def parse():
                          "sharded by rows (the default); fused = all-reduce inside the GEMM epilogue; push = the "
                          "stand-alone peer-memory all-reduce kernel; nccl = the library baseline")
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (marks the result invalid)")
+    ap.add_argument("--config", type=int, default=3, choices=[1, 2, 3, 4, 5],
+                    help="which configuration of the benchmark set to run (default 3, the headline): 1 = CPU "
+                         "Qwen3-1.7B-shaped Q8_0, one request; 2 = Llama-3.1-8B-shaped Q4_K_M, 64 requests of "
+                         "128-2048 prompt tokens, 256 out; 3 = Llama-3.3-70B-shaped block-fp8 decode (--batch "
+                         "1/8/64/256); 4 = gpt-oss-120b-shaped MXFP4, expert-parallel over the ranks, 128 requests "
+                         "of 2048 prompt tokens, 256 out (--stream-experts: experts streamed from pinned host "
+                         "memory on one GPU); 5 = speculative decoding, 8B-shaped bf16 target + 1B-shaped drafter, "
+                         "k = 4, 32 conversations sharing a 4096-token prefix")
+    ap.add_argument("--stream-experts", type=int, default=0, metavar="SLOTS",
+                    help="config 4: keep only SLOTS experts per layer on the GPU, the rest in pinned host memory")
+    ap.add_argument("--requests", type=int, default=0, help="configs 2/4/5: number of concurrent requests (0 = the set's)")
+    ap.add_argument("--out-tokens", type=int, default=0, help="configs 1/2/4/5: tokens generated per request (0 = the set's)")
     return ap.parse_args()
 
 
@@ -115,10 +127,166 @@ class ClockSampler:
 AUTO_COMM = {2: "sum_norm", 4: "sum_norm", 8: "sum_norm"}
 
 
+def extra_config(args):
+    """Configurations 1, 2, 4 and 5 of the benchmark set: whole serving runs (utils/serve_bench.py)."""
+    import dataclasses
+
+    import torch
+
+    from loken_b200.models.config import get_config
+
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+    base = {"metric": METRIC, "unit": "tok/s", "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "impl": "ours", "steps": args.steps, "warmup": args.warmup}
+    if args.config == 1:
+        # CPU: Qwen3-1.7B-shaped, Q8_0 GGUF written with random N(0, 0.02) weights, 128-token prompt, 64 greedy tokens
+        import tempfile
+
+        from loken_b200.cpu.engine import CpuModel
+        from loken_b200.models.loader import export_random_gguf
+
+        cfg = dataclasses.replace(get_config("qwen3-1.7b"), weight_format="q8_0")
+        if args.layers:
+            cfg = dataclasses.replace(cfg, n_layers=args.layers)
+        path = os.path.join(tempfile.gettempdir(), f"loken-bench-{cfg.name}-{cfg.n_layers}-q8_0.gguf")
+        if not os.path.exists(path):
+            export_random_gguf(path, cfg, seed=0)
+        m = CpuModel.from_gguf(path)
+        g = torch.Generator().manual_seed(1234)
+        prompt = torch.randint(0, cfg.vocab, (128,), generator=g).tolist()
+        n_out = args.out_tokens or 64
+        m.generate(prompt[:16], max_tokens=4)                 # warm the pool and the page cache
+        r = m.generate(prompt, max_tokens=n_out)
+        line = dict(base, value=round(r["tok_per_s"], 3), n_gpus=0, ms_per_step=round(r["decode_s"] / max(1, n_out - 1) * 1e3, 3),
+                    dtype="Q8_0 weights x Q8_0 activations (int8 dots), Q8_0 KV cache",
+                    data="synthetic: random-init N(0,0.02) weights quantised to a Q8_0 GGUF, uniform random prompt ids",
+                    config={"model": cfg.name + "-shaped" + (" (DEBUG layers)" if args.layers else ""), "global_batch": 1,
+                            "seq_len": 128, "out_tokens": n_out, "parallelism": f"cpu x{m.threads} threads",
+                            "simd_level": m.simd_level},
+                    ttft_p50_s=round(r["prefill_s"], 4), prefill_tok_s=round(128 / r["prefill_s"], 2), gpu_launches=0,
+                    e2e={"value": round(r["tok_per_s"], 3), "unit": "tok/s", "h2d_bytes_per_step": 0,
+                         "d2h_bytes_per_step": 0})
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
+        return 0
+
+    from loken_b200.parallel.comm import init_distributed
+    from loken_b200.serve.engine import LLMEngine
+    from loken_b200.serve.params import SamplingParams
+    from loken_b200.utils import serve_bench
+
+    rank, world, local = init_distributed()
+    if world != args.gpus:
+        print(f"bench.py: --gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run", file=sys.stderr)
+        return 2
+    dev = torch.device("cuda", local)
+    g = torch.Generator().manual_seed(99)
+    sp = SamplingParams(temperature=0.7, top_k=0, top_p=0.9, ignore_eos=True, seed=1234)
+    prefix_len, spec, moe_factory, par = 0, None, None, f"tp{world}"
+    if args.config == 2:
+        cfg = dataclasses.replace(get_config("llama-3.1-8b"), weight_format="q4_k_m")
+        n_req = args.requests or 64
+        lens = torch.randint(128, 2049, (n_req,), generator=g).tolist()
+        n_out, top_k = args.out_tokens or 256, 0
+        dtype = "Q4_K_M weights (Q4_K + Q6_K blocks, dequant-fused tcgen05 GEMM), bf16 activations, q8 paged KV"
+    elif args.config == 4:
+        cfg = get_config("gpt-oss-120b")
+        n_req = args.requests or 128
+        lens = [2048] * n_req
+        n_out, top_k = args.out_tokens or 256, cfg.top_k
+        par = f"ep{world} (attention tp{world})" if world > 1 else "1 gpu"
+        dtype = "MXFP4 experts on the block-scaled MMA (e4m3 activations), bf16 attention, q8 paged KV"
+        if args.stream_experts:
+            from loken_b200.models.expert_tier import TieredMoeRunner
+
+            moe_factory = lambda c, w, cap, comm: TieredMoeRunner(c, w, cap, comm, slots=args.stream_experts)
+            par += f", {args.stream_experts} of {cfg.n_experts} experts per layer resident, the rest streamed from pinned host memory"
+    else:
+        cfg = dataclasses.replace(get_config("llama-3.1-8b"), weight_format="bf16")
+        n_req = args.requests or 32
+        lens = [256] * n_req
+        prefix_len = 4096
+        n_out, top_k = args.out_tokens or 256, 0
+        dtype = "bf16 weights (target and drafter), q8 paged KV"
+    if args.layers:
+        cfg = dataclasses.replace(cfg, n_layers=args.layers)
+    comm, comm_name = None, "none"
+    if world > 1:
+        from loken_b200.parallel.symm import SymmComm
+
+        comm = SymmComm(dev, max_rows=256, hidden=cfg.hidden, top_k=top_k)
+        comm.fused_norm = args.comm in ("auto", "sum_norm")
+        comm_name = "layer-boundary kernel (reduce-scatter + norm + all-gather) and expert dispatch / combine over peer memory" \
+            if comm.fused_norm else "peer-memory all-reduce kernel"
+    max_ctx = (prefix_len + max(lens) + n_out + 64 + 255) // 256 * 256
+    blocks = sum((prefix_len + n + n_out + 31) // 16 for n in lens) + 512
+    eng = LLMEngine(cfg, device=dev, tp_rank=rank, tp_size=world, comm=comm, max_seqs=max(n_req, 8),
+                    max_prefill_tokens=8192, max_ctx=max_ctx, seed=0, num_blocks=blocks, moe_runner_factory=moe_factory,
+                    lookahead=0)
+    if args.config == 5:
+        from loken_b200.serve.speculative import attach_draft_engine
+
+        attach_draft_engine(eng, "llama-3.2-1b", k=4)
+    sampler = ClockSampler(local) if rank == 0 else None
+    r = serve_bench.serving_run(eng, lens=lens, out_tokens=n_out, sp=sp, world=world, prefix_len=prefix_len,
+                                clock_sampler=sampler)
+    if rank == 0:
+        line = dict(base, value=round(r["tok_s"], 2), n_gpus=world, ms_per_step=round(r["ms"] / r["steps"], 4),
+                    steps=r["steps"], warmup=1, dtype=dtype,
+                    data="synthetic: random-init N(0,0.02) weights, uniform random prompt token ids",
+                    value_kind="whole serving run (prefill + decode) through LLMEngine.add_request / step, device-timed",
+                    config={"model": cfg.name + "-shaped" + (f" ({cfg.n_layers} layers, DEBUG)" if args.layers else ""),
+                            "global_batch": n_req, "seq_len": f"{min(lens) + prefix_len}-{max(lens) + prefix_len}",
+                            "out_tokens": n_out, "parallelism": par, "tp_collectives": comm_name,
+                            "kv_cache": "q8 paged, block 16", "sampling": "temperature 0.7 top-p 0.9 on device",
+                            "l2": "inputs larger than L2: every step streams the rank's weight shard and the batch's KV cache",
+                            "shared_prefix_tokens": prefix_len},
+                    e2e={"value": round(r["tok_s"], 2), "unit": "tok/s", "ms_total": round(r["ms"], 2),
+                         "h2d_bytes_per_step": int(r["h2d_bytes_per_step"]), "d2h_bytes_per_step": int(r["d2h_bytes_per_step"])},
+                    gpu_launches=r["gpu_launches"], clocks=r["clocks"],
+                    ttft_p50_s=round(r["ttft_p50_s"], 4) if r["ttft_p50_s"] is not None else None,
+                    out_tokens_total=r["out_tokens"], prompt_tokens_total=r["prompt_tokens"],
+                    cached_prompt_tokens=r["cached_tokens"], preemptions=r["preemptions"])
+        if args.config == 5:
+            tot = r["accepted"] + r["rejected"]
+            line["speculation"] = {"draft_model": "llama-3.2-1b-shaped", "k": 4, "accepted": r["accepted"],
+                                   "rejected": r["rejected"], "acceptance": round(r["accepted"] / tot, 4) if tot else None}
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
+    if world > 1:
+        leave_multi_rank(eng, comm)
+    return 0
+
+
+def leave_multi_rank(eng, comm):
+    """Leave in step: drop the engine (its CUDA graphs hold captured kernels), wait for the device,
+    meet the other ranks, unmap peer memory, exit without tearing the process group down."""
+    import gc
+    import threading
+
+    import torch
+    import torch.distributed as dist
+
+    bail = threading.Timer(45.0, os._exit, [0])   # the result is printed; never hang on the way out
+    bail.daemon = True
+    bail.start()
+    del eng
+    gc.collect()
+    torch.cuda.synchronize()
+    dist.barrier()
+    if hasattr(comm, "close"):
+        comm.close()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.config != 3:
+        return extra_config(args)
     import dataclasses
 
     import torch
@@ -174,10 +342,12 @@ def main():
         base = None   # the reference publishes no number for this configuration
         line = {
             "metric": METRIC, "value": round(r["tok_s"], 2), "unit": "tok/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": round(r["device_ms"] / args.steps, 4),
+            "warmup": max(args.warmup, 3), "warmup_requested": args.warmup, "ms_per_step": round(r["device_ms"] / args.steps, 4),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": base, "dtype": "fp8 (e4m3 block-scaled) weights+activations, bf16 residual/attention",
             "data": "synthetic: random-init N(0,0.02) weights, uniform random prompt token ids",
             "impl": "ours",
+            "value_kind": "device-timed decode steps (CUDA-graph replays, sampled token fed back on the device); "
+                          "the serving figure through LLMEngine.step() is e2e.value",
             "config": {"model": cfg.name + "-shaped" + (f" ({cfg.n_layers} layers, DEBUG)" if args.layers else ""),
                        "global_batch": args.batch, "seq_len": args.prompt_len, "context_at_timing": r["context_len"],
                        "parallelism": f"tp{world}", "tp_collectives": comm_name, "kv_cache": "q8 paged, block 16",

@@ -60,6 +60,8 @@ class ServerContext:
         here, when the measured hand-over rate beats local prefill (the first long prompt measures
         it).  Any failure falls back to reading the prompt locally."""
         peer = self.settings.prefill_peer
+        if hasattr(ids, "embeds"):
+            return False             # a prompt given as embedding rows is read here
         if not peer or not self.handover.ask_peer(len(ids), self.settings.prefill_peer_min_tokens):
             return False
         t0 = time.perf_counter()

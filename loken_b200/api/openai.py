@@ -315,7 +315,23 @@ def router(ctx: ServerContext) -> APIRouter:
         prompts = prompt if isinstance(prompt, list) and prompt and not isinstance(prompt[0], int) else [prompt]
         if body.get("suffix"):
             raise ApiError(400, "suffix (fill-in-the-middle) needs a model with FIM tokens")
-        id_lists = [llm.prompt_ids(p, params=params) for p in prompts]
+        if body.get("prompt_embeds") is not None:
+            # the prompt as embedding rows (loken's container, a torch.save archive read without unpickling,
+            # or bare f32): one prompt per payload, answered in order
+            from ..engine.llm import EmbedsPrompt
+            from ..text.prompt_embeds import decode_request
+
+            if body.get("use_beam_search"):
+                raise ApiError(400, "beam search takes a text prompt, not prompt_embeds")
+            try:
+                arrays = decode_request(body["prompt_embeds"], llm.cfg.hidden, llm.engine.max_ctx)
+            except ValueError as e:
+                raise ApiError(400, str(e))
+            id_lists = [EmbedsPrompt(a) for a in arrays]
+            prompts = [None] * len(id_lists)
+            params.echo = False
+        else:
+            id_lists = [llm.prompt_ids(p, params=params) for p in prompts]
         rid = new_request_id("cmpl")
         created = int(time.time())
         scope = getattr(req.state, "api_key", None)

@@ -116,9 +116,13 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int nkb_total = (p.K + 127) / 128;
   const bool grouped = p.g_rows_per_expert > 0;
   if (grouped) pdl_wait();
+  // the first n_full tiles (a multiple of the grid) run whole; the remainder, which would be a nearly
+  // empty last wave, is cut along K into `splits` units each and spread over all the CTAs
   const int splits = grouped ? 1 : p.splits;
-  const int ntiles = (grouped ? (*p.g_ntiles) * p.tiles_a : p.tiles_a * p.tiles_b) * splits;
-  const int kb_per = (nkb_total + splits - 1) / splits;
+  const int all_tiles = grouped ? (*p.g_ntiles) * p.tiles_a : p.tiles_a * p.tiles_b;
+  const int n_full = grouped ? all_tiles : min(p.n_full, all_tiles);
+  const int nrem = all_tiles - n_full;
+  const int ntiles = n_full + nrem * splits;         // work units
   int* s_last = reinterpret_cast<int*>(tmem_slot + 2);
 
   if (threadIdx.x == 0) {
@@ -144,7 +148,11 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   pdl_launch();
 
 #define MX_TILE(u)                                                              \
-  const int split_ = (u) % splits, tile_ = (u) / splits;                        \
+  const bool whole_ = (u) < n_full;                                             \
+  const int nsp = whole_ ? 1 : splits;                                          \
+  const int split_ = whole_ ? 0 : ((u) - n_full) % splits;                      \
+  const int tile_ = whole_ ? (u) : n_full + ((u) - n_full) / splits;            \
+  const int kb_per = (nkb_total + nsp - 1) / nsp;                               \
   const int tile_a = grouped ? tile_ % p.tiles_a : tile_ / p.tiles_b;           \
   const int tile_b = grouped ? tile_ / p.tiles_a : tile_ % p.tiles_b;           \
   const int kb_begin = split_ * kb_per;                                         \
@@ -314,7 +322,8 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int i = a_row0 + li;
       // one chunk of columns at a time: straight to the output, or to this split's workspace tile
       // [split][tile][column][row]
-      float* mine = splits > 1 ? p.ws + ((long long)split_ * (ntiles / splits) + tile_) * (128 * BN) : nullptr;
+      const int trem = tile_ - n_full;
+      float* mine = nsp > 1 ? p.ws + ((long long)split_ * nrem + trem) * (128 * BN) : nullptr;
       const int buf = ait % NACC;
       if (nkb > 0) {
         ok = mbar_wait(&accf_bar[buf], (ait / NACC) & 1, ab, p.status, 5);
@@ -337,7 +346,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
           for (int e = 0; e < CH; ++e) v[e] = 0.f;
         }
-        if (splits == 1) {
+        if (nsp == 1) {
           store_chunk<CH>(p, tc, i, b_row0 + c * CH, v);
         } else if (i < tc.ra_end) {
 #pragma unroll
@@ -350,28 +359,28 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (lane == 0) mbar_arrive(&acce_bar[buf]);
         ++ait;
       }
-      if (splits > 1) {
+      if (nsp > 1) {
         // the split that arrives last on the tile's counter sums the partials in split order and stores;
         // it leaves the counter at zero
         epi_bar(128);
         if (threadIdx.x == 64) {
           __threadfence();
-          const int prev = atomicAdd(&p.counters[tile_], 1);
+          const int prev = atomicAdd(&p.counters[trem], 1);
           const int last = (prev == splits - 1);
-          if (last) p.counters[tile_] = 0;
+          if (last) p.counters[trem] = 0;
           *s_last = last;
           __threadfence();
         }
         epi_bar(128);
         if (*s_last) {
-          const long long sstride = (long long)(ntiles / splits) * (128 * BN);
+          const long long sstride = (long long)nrem * (128 * BN);
 #pragma unroll
           for (int c = 0; c < NCH; ++c) {
             float v[CH];
 #pragma unroll
             for (int e = 0; e < CH; ++e) v[e] = 0.f;
             if (i < tc.ra_end) {
-              const float* base = p.ws + (long long)tile_ * (128 * BN) + (c * CH) * 128 + li;
+              const float* base = p.ws + (long long)trem * (128 * BN) + (c * CH) * 128 + li;
               for (int sp = 0; sp < splits; ++sp) {
                 float t[CH];
 #pragma unroll
@@ -428,22 +437,30 @@ int launch_mx(const LkGemmArgs& a, const GemmParams& p0, cudaStream_t st) {
   q.tiles_a = grouped ? (a.g_rows_per_expert + 127) / 128 : (a.Ra + 127) / 128;
   q.tiles_b = grouped ? a.g_max_tiles : (a.Rb + BN - 1) / BN;
   const long long tiles = (long long)q.tiles_a * q.tiles_b;
-  // dense launches with fewer tiles than SMs split K so the whole chip streams weights
+  // dense launches: whole tiles for as many full rounds of the SMs as there are; the remainder (all of
+  // the tiles when there are fewer than SMs) is cut along K so the whole chip streams weights
   const int nkb = (a.K + 127) / 128;
   int splits = 1;
-  if (!grouped && tiles < 148 && nkb > 8) {
-    splits = a.splits > 0 ? a.splits : (int)(148 / tiles);
-    if (splits > nkb / 4) splits = nkb / 4;
-    if (splits > 16) splits = 16;
-    if (splits < 1) splits = 1;
-    while (splits > 1 && (long long)((nkb + splits - 1) / splits) * (splits - 1) >= nkb) --splits;
-    if (splits > 1 && (!a.ws || !a.counters || tiles * splits * 128 * BN > a.ws_floats || tiles > a.n_counters))
-      splits = 1;
+  long long n_full = tiles;
+  if (!grouped && nkb > 8) {
+    n_full = tiles / 148 * 148;
+    const long long rem = tiles - n_full;
+    if (rem > 0) {
+      splits = a.splits > 0 ? a.splits : (int)(148 / rem);
+      if (splits > nkb / 4) splits = nkb / 4;
+      if (splits > 16) splits = 16;
+      if (splits < 1) splits = 1;
+      while (splits > 1 && (long long)((nkb + splits - 1) / splits) * (splits - 1) >= nkb) --splits;
+      if (splits > 1 && (!a.ws || !a.counters || rem * splits * 128 * BN > a.ws_floats || rem > a.n_counters))
+        splits = 1;
+    }
+    if (splits == 1) n_full = tiles;
   }
   q.splits = splits;
+  q.n_full = (int)n_full;
   q.ws = a.ws;
   q.counters = a.counters;
-  const long long units = tiles * splits;
+  const long long units = n_full + (tiles - n_full) * splits;
   const unsigned grid = (unsigned)(units < 148 ? units : 148);
   lkh::launch_pdl(kern, dim3(grid), dim3(MX_THREADS), S::TOTAL, st, tmA, tmB, q);
   lkh::count_launch();

@@ -68,6 +68,14 @@ class Completion:
     figures: Optional[dict] = None
 
 
+class EmbedsPrompt(list):
+    """A prompt given as embedding rows: placeholder token ids (one per row) carrying the rows."""
+
+    def __init__(self, embeds):
+        super().__init__([0] * int(embeds.shape[0]))
+        self.embeds = embeds
+
+
 class _Ticket:
     def __init__(self, prompt_ids, params, salt):
         self.prompt_ids, self.params, self.salt = prompt_ids, params, salt

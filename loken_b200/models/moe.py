@@ -39,7 +39,12 @@ class MoeWeights:
     fmt: str = "bf16"
 
 
-def random_moe(cfg: ModelConfig, gen, device, std: float, ep_rank: int = 0, ep_size: int = 1) -> MoeWeights:
+def random_moe(cfg: ModelConfig, gen, device, std: float, ep_rank: int = 0, ep_size: int = 1, il: int = 0
+               ) -> MoeWeights:
+    """Random experts of one layer, holding only this rank's share.  Every expert has its own seed
+    (derived from the model seed, the layer and the expert id), so a rank draws and quantises only the
+    experts it holds, one at a time (a 120b-shaped layer is 3.2 G values), and the model is the same at
+    every expert-parallel degree."""
     from .weights import linear_format
 
     E, H, I = cfg.n_experts, cfg.hidden, cfg.expert_intermediate
@@ -50,24 +55,34 @@ def random_moe(cfg: ModelConfig, gen, device, std: float, ep_rank: int = 0, ep_s
     router_w = (rn(E, H) * 4).bfloat16()          # spread the logits so routing is not a coin toss
     router_b = rn(E) if cfg.expert_bias else None
     fmt = linear_format(cfg, "expert")
+    base = int(gen.initial_seed())
     gu_parts, dn_parts, gub, dnb = [], [], [], []
-    for e in range(E):                            # every rank draws every expert: same model at any degree
-        g, u, d = rn(I, H), rn(I, H), rn(H, I)
-        bg = rn(2 * I) if cfg.expert_bias else None
-        bd = rn(H) if cfg.expert_bias else None
-        if elo <= e < elo + ecnt:
-            gu_parts.append(torch.cat([g, u], 0))
-            dn_parts.append(d)
-            if cfg.expert_bias:
-                gub.append(bg)
-                dnb.append(bd)
-    gu = torch.cat(gu_parts, 0)
-    dn = torch.cat(dn_parts, 0)
+    for e in range(elo, elo + ecnt):
+        ge = torch.Generator(device=device)
+        ge.manual_seed((base * 1000003 + il * 4099 + e) & 0x7FFFFFFFFFFFFFFF)
+        re_ = lambda *s: torch.randn(*s, generator=ge, device=device, dtype=torch.float32) * std
+        gu = torch.cat([re_(I, H), re_(I, H)], 0)
+        dn = re_(H, I)
+        if cfg.expert_bias:
+            gub.append(re_(2 * I))
+            dnb.append(re_(H))
+        if fmt == "bf16":
+            gu_parts.append(gu.bfloat16())
+            dn_parts.append(dn.bfloat16())
+        else:
+            qz = quant.quantize_weight_torch if gu.is_cuda else quant.quantize_weight
+            gu_parts.append(qz(gu, fmt))
+            dn_parts.append(qz(dn, fmt))
+        del gu, dn
     if fmt == "bf16":
-        gu_w, dn_w = gu.bfloat16().contiguous(), dn.bfloat16().contiguous()
+        gu_w, dn_w = torch.cat(gu_parts, 0).contiguous(), torch.cat(dn_parts, 0).contiguous()
     else:
-        qz = quant.quantize_weight_torch if gu.is_cuda else quant.quantize_weight
-        gu_w, dn_w = qz(gu, fmt), qz(dn, fmt)
+        def stack(parts):
+            p0 = parts[0]
+            return quant.QuantWeight(p0.aq_fmt, p0.ggml_type, sum(p.rows for p in parts), p0.K,
+                                     torch.cat([p.codes for p in parts], 0).contiguous(),
+                                     torch.cat([p.scales for p in parts], 0).contiguous())
+        gu_w, dn_w = stack(gu_parts), stack(dn_parts)
     return MoeWeights(router_w, router_b, gu_w, dn_w,
                       torch.stack(gub).contiguous() if gub else None,
                       torch.stack(dnb).contiguous() if dnb else None, elo, ecnt, fmt)

@@ -48,6 +48,7 @@ class StepInputs:
     plan: Optional[attention.PrefillPlan] = None
     logit_rows: Optional[torch.Tensor] = None    # int64 rows that need logits (None: all T)
     n_logit_rows: int = 0
+    embed_overrides: Optional[list] = None       # [(first row, bf16 [n, H])]: rows given as embeddings (prompt_embeds)
 
 
 class Buffers:
@@ -181,6 +182,9 @@ class DecoderModel:
         T = inp.T
         assert T <= self.buf.cap
         rows.embed(inp.tokens[:T], self.w.embed, out=self.buf.x[:T], scale=self.cfg.embedding_scale)
+        for r0, t in (inp.embed_overrides or ()):
+            self.buf.x[r0:r0 + t.shape[0]].copy_(t)       # a prompt given as embedding rows takes the table's place
+        self._delta_local = False
 
     def sharded(self, T: int) -> bool:
         """True when this step keeps the residual stream sharded by rows over the tensor-parallel

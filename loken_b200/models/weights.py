@@ -171,7 +171,7 @@ def random_weights(cfg: ModelConfig, device, seed: int = 0, tp_rank: int = 0, tp
         if cfg.is_moe:
             from .moe import random_moe
 
-            lw.moe = random_moe(cfg, gen, device, std, ep_rank, ep_size)
+            lw.moe = random_moe(cfg, gen, device, std, ep_rank, ep_size, il=il)
         else:
             I = cfg.intermediate
             assert I % tp_size == 0

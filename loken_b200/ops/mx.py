@@ -25,6 +25,9 @@ def sf_pitch(K: int) -> int:
     return (K + 127) // 128 * 4
 
 
+assert sf_pitch(2880) == 92
+
+
 @dataclass
 class MxAct:
     """e4m3 rows [rows, K] + E8M0 exponents [rows, sf_pitch(K)] (bytes past K / 32 stay zero)."""
@@ -54,8 +57,12 @@ def mx_weight(q: QuantWeight) -> MxWeight:
     """The planes of an MXFP4 `QuantWeight` with the exponent rows padded to whole stages."""
     assert q.aq_fmt == AQ_MX4 and q.K % 32 == 0
     ld = sf_pitch(q.K)
+    if q.scales.dim() == 2 and q.scales.shape[1] == ld and q.codes.is_contiguous():
+        # the planes are shared, not copied: a slot cache that rewrites an expert's rows in place
+        # (models/expert_tier.py) is seen by the GEMM without further ado
+        return MxWeight(q.codes, q.scales, q.rows, q.K)
     sf = torch.zeros(q.rows, ld, dtype=torch.uint8, device=q.codes.device)
-    sf[:, :q.K // 32] = q.scales.view(q.rows, q.K // 32)
+    sf[:, :q.K // 32] = q.scales.reshape(q.rows, -1)[:, :q.K // 32]
     return MxWeight(q.codes.contiguous(), sf, q.rows, q.K)
 
 

@@ -45,7 +45,14 @@ class QuantWeight:
         return (self.rows, self.K)
 
     def nbytes(self) -> int:
+        if self.aq_fmt == AQ_MX4:
+            return self.codes.numel() + self.rows * (self.K // 32)       # without the pitch padding
         return self.codes.numel() + self.scales.numel()
+
+
+def mx_sf_pitch(K: int) -> int:
+    """Bytes per row of an MXFP4 exponent plane: four per 128 values of K."""
+    return (K + 127) // 128 * 4
 
 
 def _pack_nibbles(v: np.ndarray) -> np.ndarray:
@@ -63,7 +70,11 @@ def repack_blocks(raw: np.ndarray, ggml_type: int, rows: int, K: int):
         b = raw.reshape(rows, K // 32, 17)
         qs = b[:, :, 1:]
         v = np.concatenate([qs & 0xF, qs >> 4], axis=2)          # [rows, K/32, 32] in value order
-        return _pack_nibbles(v).reshape(rows, K // 2), b[:, :, 0].copy()
+        # exponent rows are padded with zeros to four per 128 values of K: the block-scaled GEMM reads one
+        # 32-bit word of exponents per row and stage
+        ex = np.zeros((rows, mx_sf_pitch(K)), dtype=np.uint8)
+        ex[:, :K // 32] = b[:, :, 0]
+        return _pack_nibbles(v).reshape(rows, K // 2), ex
     if ggml_type == gguf.Q4_K:
         b = raw.reshape(rows, K // 256, 144)
         sc12 = b[:, :, 4:16].astype(np.uint8)
@@ -134,7 +145,7 @@ def dequantize_weight(q: QuantWeight) -> torch.Tensor:
         return (d1 * v.float().view(rows, K // 256, 8, 32) - m1).view(rows, K)
     if q.aq_fmt == AQ_MX4:
         lut = torch.tensor([0, .5, 1, 1.5, 2, 3, 4, 6, 0, -.5, -1, -1.5, -2, -3, -4, -6], device=c.device)
-        e = s.to(torch.int32)
+        e = s[:, :K // 32].to(torch.int32)
         sc = torch.where(e == 0, torch.full_like(e, 0, dtype=torch.float32) + 2.0 ** -127,
                          torch.exp2((e - 127).float()))
         return (lut[v.long()].view(rows, K // 32, 32) * sc[:, :, None]).view(rows, K)
@@ -222,7 +233,9 @@ def quantize_weight_torch(w: torch.Tensor, fmt: str) -> QuantWeight:
         mag = (x.abs().unsqueeze(-1) - lut).abs().argmin(-1).to(torch.uint8)
         code = mag | ((x < 0).to(torch.uint8) << 3)
         codes = _nibble_pack_t(code.view(rows, K))
-        return QuantWeight(AQ_MX4, ty, rows, K, codes.contiguous(), (e + 127).to(torch.uint8).contiguous())
+        ex = torch.zeros(rows, mx_sf_pitch(K), dtype=torch.uint8, device=dev)
+        ex[:, :K // 32] = (e + 127).to(torch.uint8)
+        return QuantWeight(AQ_MX4, ty, rows, K, codes.contiguous(), ex)
     if fmt == "q4_k":
         g = w.view(rows, K // 256, 8, 32)
         mn = (-g.amin(3)).clamp_min(0.0)

@@ -116,8 +116,9 @@ class LockstepEngine:
     def add_request(self, prompt, params=None, salt: int = 0) -> int:
         if params is not None and params.seed is None:
             params = dataclasses.replace(params, seed=random.SystemRandom().getrandbits(62))
-        sid = self._e.add_request(prompt, params, salt)
-        self._ops.append(("add", list(prompt), params, salt))
+        embeds = getattr(prompt, "embeds", None)
+        sid = self._e.add_request(prompt, params, salt, **({"embeds": embeds} if embeds is not None else {}))
+        self._ops.append(("add", list(prompt), params, salt, embeds))
         return sid
 
     def abort(self, seq_id: int):
@@ -177,7 +178,8 @@ def follow(llm_or_engine, group=None, watchdog=None) -> int:
         for op in msg[1]:
             if op[0] == "add":
                 try:
-                    eng.add_request(op[1], op[2], salt=op[3])
+                    eng.add_request(op[1], op[2], salt=op[3],
+                                    **({"embeds": op[4]} if len(op) > 4 and op[4] is not None else {}))
                 except ValueError:
                     pass             # refused on rank 0 too (same allocator state): no sequence anywhere
             elif op[0] == "abort":

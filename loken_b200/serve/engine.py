@@ -111,8 +111,23 @@ class LLMEngine:
         self.grammar_factory = None  # callable((kind, source)) -> session; set by whoever owns the tokenizer
 
     # ---- requests ----
-    def add_request(self, prompt: Seq[int], params: Optional[SamplingParams] = None, salt: int = 0) -> int:
+    def add_request(self, prompt: Seq[int], params: Optional[SamplingParams] = None, salt: int = 0,
+                    embeds=None) -> int:
+        """`embeds` (or a `prompt` object carrying `.embeds`): float rows [len(prompt), hidden] that stand
+        in for the prompt's token embeddings (`prompt_embeds`); `prompt` then holds placeholder ids."""
         params = (params or SamplingParams()).validate()
+        embeds = embeds if embeds is not None else getattr(prompt, "embeds", None)
+        if embeds is not None:
+            import zlib
+
+            import numpy as np
+
+            arr = np.ascontiguousarray(np.asarray(embeds, dtype=np.float32))
+            if arr.ndim != 2 or arr.shape[1] != self.cfg.hidden:
+                raise ValueError(f"prompt embeddings must be [rows, {self.cfg.hidden}]")
+            prompt = [0] * arr.shape[0]
+            if not salt:
+                salt = (1 << 40) | zlib.crc32(arr.tobytes())     # equal embeddings share cached blocks, nothing else does
         if len(prompt) == 0:
             raise ValueError("empty prompt")
         if len(prompt) >= self.max_ctx:
@@ -124,6 +139,8 @@ class LLMEngine:
         sid = self.next_id
         self.next_id += 1
         seq = Sequence(sid, list(prompt), params, arrival=time.perf_counter(), salt=salt)
+        if embeds is not None:
+            seq.prompt_embeds = torch.from_numpy(arr).to(self.device).to(torch.bfloat16)
         if params.grammar is not None:
             if self.grammar_factory is None:
                 raise ValueError("structured output needs a tokenizer: load the model through LLM")

@@ -416,9 +416,14 @@ class ModelRunner:
         nr = self.n_rows
         T = 0
         q_lens, kv_lens, last_rows, done = [], [], [], []
+        overrides = []
         for j, it in enumerate(items):
             s, n = it.seq, it.end - it.start
             toks = s.tokens
+            pe = getattr(s, "prompt_embeds", None)
+            if pe is not None and it.start < len(s.prompt):
+                p_end = min(it.end, len(s.prompt))
+                overrides.append((T, pe[it.start:p_end]))
             nr[0, T:T + n] = toks[it.start:it.end]
             nr[1, T:T + n] = np.arange(it.start, it.end, dtype=np.int32)
             nr[2, T:T + n] = alloc.slots_for_range(s.seq_id, it.start, it.end)
@@ -440,7 +445,7 @@ class ModelRunner:
         n_l = len(last_rows)
         lr = torch.tensor(last_rows if last_rows else [0], dtype=torch.int64, device=self.device)
         inp = StepInputs(T=T, tokens=r[0], positions=r[1], slots=r[2], mode="prefill", block_table=self.d_bt,
-                         plan=plan, logit_rows=lr, n_logit_rows=max(n_l, 1))
+                         plan=plan, logit_rows=lr, n_logit_rows=max(n_l, 1), embed_overrides=overrides or None)
         logits = self.model.forward(inp)
         if not done:
             return {}

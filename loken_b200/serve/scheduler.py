@@ -44,6 +44,7 @@ class Sequence:
     rejected_drafts: int = 0
     logprobs: List[tuple] = field(default_factory=list)   # per output token: (logprob, [(id, logprob)...])
     grammar: Optional[object] = None     # a text.grammar.GrammarSession while the request is constrained
+    prompt_embeds: Optional[object] = None   # bf16 [len(prompt), hidden] on the device: the prompt as embedding rows
 
     @property
     def tokens(self) -> List[int]:

@@ -42,6 +42,7 @@ class FakeEngine:
         self.fail_steps = fail_steps
         self.step_delay = step_delay
         self.prompts: List[List[int]] = []
+        self.embeds: list = []
 
     def add_request(self, prompt, params: Optional[SamplingParams] = None, salt: int = 0) -> int:
         params = (params or SamplingParams()).validate()
@@ -51,6 +52,7 @@ class FakeEngine:
         self.next_id += 1
         self.seqs[sid] = FakeSeq(sid, prompt, params, list(self.reply.encode()) + [257])
         self.prompts.append(list(prompt))
+        self.embeds.append(getattr(prompt, "embeds", None))
         return sid
 
     def abort(self, sid):
