@@ -54,6 +54,8 @@ class ServerContext:
 
         self.handover = HandoverRate()
         self.fetch_prefill = _fetch_prefill      # replaceable (tests, another transport)
+        self.catalogue = None                    # store.catalogue.Catalogue when model stores are configured
+        self.opener = None                       # transport of pulls (store.download.Opener); None = requests
 
     def _prefill_on_peer(self, llm: LLM, ids: List[int], params: GenerationParams) -> bool:
         """Disaggregated prefill: a long prompt is read by the configured peer and its cache imported

@@ -31,6 +31,12 @@ def _details(llm) -> dict:
             "quantization_level": cfg.weight_format.upper()}
 
 
+def _default_opener():
+    from ..store.download import requests_opener
+
+    return requests_opener
+
+
 def router(ctx: ServerContext) -> APIRouter:
     r = APIRouter()
 
@@ -42,13 +48,27 @@ def router(ctx: ServerContext) -> APIRouter:
     async def version():
         return {"version": VERSION}
 
+    def _catalogue():
+        return getattr(ctx, "catalogue", None)
+
     @r.get("/api/tags")
     async def tags():
-        out = []
+        """Loaded models, then what the model stores hold (Ollama manifests, the Hugging Face cache,
+        bare GGUF files), each listed once."""
+        out, seen = [], set()
         for m in ctx.registry.list():
+            seen.add(m.model_id)
             out.append({"name": m.model_id, "model": m.model_id,
                         "modified_at": datetime.datetime.fromtimestamp(m.loaded_at, datetime.timezone.utc).isoformat(),
                         "size": int(m.cfg.param_count()), "digest": "", "details": _details(m)})
+        cat = _catalogue()
+        for e in (cat.list() if cat is not None else []):
+            if e.name in seen:
+                continue
+            out.append({"name": e.name, "model": e.name, "size": int(e.size), "digest": e.digest.split(":")[-1],
+                        "modified_at": datetime.datetime.fromtimestamp(e.modified or 0, datetime.timezone.utc).isoformat(),
+                        "details": {"format": "gguf" if e.source != "huggingface" else "safetensors",
+                                    "family": "", "parameter_size": "", "quantization_level": ""}})
         return {"models": out}
 
     @r.post("/api/show")
@@ -225,6 +245,10 @@ def router(ctx: ServerContext) -> APIRouter:
         src, dst = body.get("source"), body.get("destination")
         if not src or not dst:
             raise ApiError(400, "source and destination are required")
+        cat = _catalogue()
+        if cat is not None and cat.ollama.find(src) is not None:
+            cat.ollama.copy(src, dst)            # stays in the directory of its source, beside the blobs it shares
+            return JSONResponse({}, status_code=200)
         ctx.registry.alias(src, dst)
         return JSONResponse({}, status_code=200)
 
@@ -234,7 +258,10 @@ def router(ctx: ServerContext) -> APIRouter:
         name = body.get("model") or body.get("name")
         if not name:
             raise ApiError(400, "model is required")
-        if not ctx.registry.drop(name):
+        dropped = ctx.registry.drop(name)
+        cat = _catalogue()
+        removed = cat.delete(name) if cat is not None else 0         # every copy, in every store directory
+        if not dropped and not removed:
             raise ApiError(404, f"model '{name}' not found")
         return JSONResponse({}, status_code=200)
 
@@ -247,6 +274,14 @@ def router(ctx: ServerContext) -> APIRouter:
             raise ApiError(400, "model and from are required")
         if body.get("files") or body.get("adapters"):
             raise ApiError(400, "creating a model from uploaded blobs is not supported; load the file with POST /load")
+        cat = _catalogue()
+        src = cat.resolve(base) if cat is not None else None
+        if src is not None and src.source in ("ollama", "gguf"):
+            # a new manifest over the same weights blob, with its own template / system prompt / parameters
+            cat.ollama.create(name, src.path, template=body.get("template") or src.template,
+                              system=body.get("system") or src.system,
+                              params=body.get("parameters") or src.params or None, license=src.license)
+            return {"status": "success"}
         ctx.registry.alias(base, name)
         return {"status": "success"}
 
@@ -258,9 +293,24 @@ def router(ctx: ServerContext) -> APIRouter:
         if not name:
             raise ApiError(400, "model is required")
         known = {m.model_id for m in ctx.registry.list()} | set(ctx.registry.aliases)
-        if name in known:
+        cat = _catalogue()
+        if name in known or (cat is not None and cat.resolve(name) is not None):
             return {"status": "success"}
-        raise ApiError(404, f"model '{name}' is not on this server and no registry is reachable; "
-                            f"load a local file with POST /load")
+        if cat is None:
+            raise ApiError(404, f"model '{name}' is not on this server and no model store is configured; "
+                                f"load a local file with POST /load")
+        from ..store.download import pull_ollama
+
+        def fetch_all():
+            return [s for s in pull_ollama(cat.ollama, name, opener=getattr(ctx, "opener", None) or _default_opener())]
+
+        try:
+            states = await run_in_threadpool(fetch_all)
+        except (IOError, OSError) as e:
+            raise ApiError(502, f"pull of '{name}' failed: {e}")
+        if body.get("stream", True) is False:
+            return {"status": "success"}
+        body_text = "".join(json.dumps(s) + "\n" for s in states)
+        return PlainTextResponse(body_text, media_type="application/x-ndjson")
 
     return r

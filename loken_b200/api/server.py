@@ -184,6 +184,12 @@ def ops_router(ctx: ServerContext):
         if not path:
             raise ApiError(400, "model (a GGUF path or a built-in shape name) is required")
         kw = {k: body[k] for k in ("requant", "kv_format", "max_seqs", "max_ctx", "num_blocks", "lora") if k in body}
+        cat = getattr(ctx, "catalogue", None)
+        entry = cat.resolve(path) if cat is not None else None
+        if entry is not None:
+            # a store name (`name:tag`, `owner/repo`, a GGUF's file name): the files it resolves to
+            body.setdefault("id", entry.name)
+            path = entry.path
         loader = getattr(ctx, "loader", None) or LLM.load
         evicted = []
         while True:
@@ -365,13 +371,15 @@ def create_app(registry: ModelRegistry, settings: Optional[ServerSettings] = Non
     return app
 
 
-def serve(registry: ModelRegistry, settings: Optional[ServerSettings] = None, cluster=None):
+def serve(registry: ModelRegistry, settings: Optional[ServerSettings] = None, cluster=None, catalogue=None):
     """`cluster`: the configuration's [cluster] section; with peers listed, a gossip loop runs beside
-    the server (`cluster/gossip.py`)."""
+    the server (`cluster/gossip.py`).  `catalogue`: the model stores (`store/catalogue.py`) behind
+    listings, pulls, copies and deletes, and behind loads by name."""
     import uvicorn
 
     s = settings or ServerSettings()
     app = create_app(registry, s)
+    app.state.ctx.catalogue = catalogue
     loop = None
     if cluster is not None and getattr(cluster, "peers", None):
         import socket

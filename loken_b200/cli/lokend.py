@@ -81,6 +81,15 @@ def serve(cfg, requant=None) -> int:
         else:
             comm = SymmComm(torch.device("cuda", local), max_rows=max(i.max_seqs, 256), hidden=hidden)
             comm.fused_gemm = i.tp_sum == "fused"
+    import os as _os
+
+    if not _os.path.exists(i.model):
+        from ..store.catalogue import Catalogue as _Cat
+
+        hit = _Cat(cfg.ollama_models_dir, cfg.huggingface_models_dir).resolve(i.model)
+        if hit is not None:                   # `name:tag`, `owner/repo` or a GGUF's file name in a model store
+            i.model_id = i.model_id or hit.name
+            i.model = hit.path
     llm = LLM.load(i.model, model_id=i.model_id, requant=requant, kv_format=cfg.kv_format, tp_rank=rank,
                    tp_size=world, comm=comm, max_seqs=i.max_seqs, max_ctx=i.max_ctx,
                    max_prefill_tokens=i.max_prefill_tokens, lora=i.lora,
@@ -97,11 +106,14 @@ def serve(cfg, requant=None) -> int:
         return follow(llm, llm.control_group, llm.watchdog)
     reg = ModelRegistry()
     reg.add(llm, default=True)
+    from ..store.catalogue import Catalogue
+
+    catalogue = Catalogue(cfg.ollama_models_dir, cfg.huggingface_models_dir)
     http_serve(reg, ServerSettings(host=s.host, port=s.port, api_keys=s.api_keys, require_auth=s.require_auth,
                                    allowed_origins=s.allowed_origins, rate_limit_rps=s.rate_limit_rps,
                                    rate_limit_burst=s.rate_limit_burst, max_body_bytes=s.max_body_mb << 20,
                                    request_timeout_s=s.request_timeout_s, gate_slots=i.max_seqs,
-                                   prefill_peer=i.prefill_peer), cluster=cfg.cluster)
+                                   prefill_peer=i.prefill_peer), cluster=cfg.cluster, catalogue=catalogue)
     return 0
 
 

@@ -89,6 +89,9 @@ class ClusterSection:
 
 @dataclass
 class Config:
+    # top-level keys: the model stores, each a directory or a list of directories on several disks
+    ollama_models_dir: List[str] = field(default_factory=lambda: ["~/.ollama/models"])
+    huggingface_models_dir: List[str] = field(default_factory=lambda: ["~/.cache/huggingface/hub"])
     server: ServerSection = field(default_factory=ServerSection)
     inference: InferenceSection = field(default_factory=InferenceSection)
     energy: EnergySection = field(default_factory=EnergySection)
@@ -144,8 +147,12 @@ def load_config(path: Optional[str] = None, env: Optional[Dict[str, str]] = None
                 cfg.notes.append(f"[{section}] {k} is obsolete and ignored")
             else:
                 cfg.notes.append(f"[{section}] unknown key {k} ignored")
+    for key in ("ollama_models_dir", "huggingface_models_dir"):
+        if key in data:
+            v = data[key]
+            setattr(cfg, key, [v] if isinstance(v, str) else [str(x) for x in v])     # a single string reads as a list of 1
     for section in data:
-        if section not in ("server", "inference", "energy", "cluster"):
+        if section not in ("server", "inference", "energy", "cluster", "ollama_models_dir", "huggingface_models_dir"):
             cfg.notes.append(f"unknown section [{section}] ignored")
     key = env.get("LOKEN_API_KEY")
     if key and key not in cfg.server.api_keys:
