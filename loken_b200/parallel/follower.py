@@ -86,7 +86,17 @@ class LockstepEngine:
             if self._closed:
                 raise RankLeft("the tensor-parallel group was shut down")
             box = [msg]
-            dist.broadcast_object_list(box, src=0, group=self._group)
+            try:
+                dist.broadcast_object_list(box, src=0, group=self._group)
+            except Exception as e:
+                # a member left between the watchdog's last look and this send: the group is broken for good
+                self._closed = True
+                dead = []
+                if self._watchdog is not None:
+                    time.sleep(self._watchdog.interval * 2)
+                    dead = self._watchdog.check()
+                raise RankLeft(f"tensor-parallel rank(s) {dead or '?'} left or stopped beating "
+                               f"({type(e).__name__} on the control group)") from e
             self._last_send = time.monotonic()
 
     def _keepalive(self, period: float):
