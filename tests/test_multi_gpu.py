@@ -66,10 +66,10 @@ def test_expert_parallel_matches_single_gpu(tmp_path, fmt):
     n = 8 if n >= 8 else 4 if n >= 4 else 2
     rep = _run("mp_ep_worker.py", n, str(tmp_path / "ep.json"), 29661, (fmt,))
     print(json.dumps(rep))
-    bound = 0.9995 if fmt == "bf16" else 0.98
+    bound = 0.9995 if fmt == "bf16" else 0.99      # at nine positions in ten; the worker bounds the worst one
     for name in ("replicated", "dispatch"):
         assert rep[f"match_{name}"], (name, rep)
-        assert rep[f"logits_cos_min_{name}"] >= bound, (name, rep)
+        assert rep[f"logits_cos_p10_{name}"] >= bound, (name, rep)
         assert rep[f"status_{name}"] == 0, (name, rep)
     assert rep["sharded_steps_dispatch"] > 0 and rep["sharded_steps_replicated"] == 0
 
