@@ -57,6 +57,9 @@ struct GemmParams {
   int* status;                // error word
   int tiles_a, tiles_b, splits;   // output tiles and the K split of the tiles past n_full
   int n_full;                     // leading tiles that run as whole-K units (a multiple of the grid)
+  int nrem, rem_mt;               // gemm_mx: units past n_full and the weight tiles in each of them
+  int a_tiled;                    // gemm_mx: the weights are stored tile-major (16 KB per 128 x 128 tile)
+  long long* prof;                // gemm_mx: optional per-CTA wait counters
   // quantised A (AFMT != 0): code plane and scale plane, row pitches in bytes
   const uint8_t* aq;
   const uint8_t* aq_scale;
@@ -373,6 +376,98 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const TileCtx& 
         reinterpret_cast<float*>(p.out)[off] = x;
       else
         reinterpret_cast<__nv_bfloat16*>(p.out)[off] = __float2bfloat16(x);
+    }
+  }
+}
+
+// The same final stage for outputs whose contiguous dimension is the A row (weights on the MMA M side,
+// out[token][feature]): a thread holds one feature and CH tokens, so storing from registers writes two
+// bytes per lane into rows a whole pitch apart.  Here the four epilogue warps of a tile (128 features)
+// lay the chunk out in shared memory as [token][128 features] bf16 and then write every token's 256
+// bytes as sixteen 16-byte stores: whole 128-byte lines, two token rows per warp instruction.
+// `stage` holds 2 x CH x 128 bf16 (double buffered by `parity`: one barrier per chunk); `et` is the
+// thread's index among the 128 epilogue threads (= feature row of the tile).  All 128 threads call it.
+template <int CH>
+__device__ __forceinline__ bool store_t_ok(const GemmParams& p) {
+  return p.out_sa == 1 && !p.out_fp32 && !p.residual && (p.out_sb & 7) == 0 &&
+         (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
+}
+template <int CH>
+__device__ __forceinline__ void store_chunk_t(const GemmParams& p, const TileCtx& t, int i0, int et, int j0,
+                                              const float (&v)[CH], __nv_bfloat16* stage, int parity,
+                                              long long* tq = nullptr) {
+  const long long q0 = tq ? clock64() : 0;
+  // the staging tile in 32-bit words: [token][64 words = 128 features]; odd token rows are rotated by 16
+  // words so that the two rows a warp writes at once fall into different banks
+  uint32_t* sw = reinterpret_cast<uint32_t*>(stage) + parity * (CH * 64);
+  const uint32_t sw_s = smem_u32(sw);          // shared-window address: explicit st.shared / ld.shared below
+  const int lane = et & 31;
+  const int i = i0 + et;
+  float ba = 0.f;
+  if (p.bias && p.bias_on_a && i < t.ra_end) ba = p.bias[i];
+  // neighbouring lanes hold neighbouring features: they swap one value per token pair, so the even lane
+  // writes both features of the even token as one word and the odd lane those of the odd token
+  const int odd = lane & 1;
+  const int w = (et >> 1);                      // word of this lane pair within a token row
+  // in three sweeps (all swaps, all packs, all stores), so that the latencies of a sweep overlap
+  float mine[CH / 2], got[CH / 2];
+#pragma unroll
+  for (int e = 0; e < CH; e += 2) {
+    float x0 = v[e] + ba, x1 = v[e + 1] + ba;
+    if (p.bias && !p.bias_on_a) {
+      if (j0 + e < t.rb_end) x0 += p.bias[j0 + e];
+      if (j0 + e + 1 < t.rb_end) x1 += p.bias[j0 + e + 1];
+    }
+    mine[e / 2] = odd ? x1 : x0;
+    got[e / 2] = odd ? x0 : x1;
+  }
+#pragma unroll
+  for (int k = 0; k < CH / 2; ++k) got[k] = __shfl_xor_sync(0xffffffffu, got[k], 1);
+  uint32_t pk[CH / 2];
+#pragma unroll
+  for (int k = 0; k < CH / 2; ++k) {
+    const __nv_bfloat162 h = odd ? __floats2bfloat162_rn(got[k], mine[k]) : __floats2bfloat162_rn(mine[k], got[k]);
+    pk[k] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  const uint32_t sw_row = sw_s + 4u * (odd * 64 + ((w + 16 * odd) & 63));
+#pragma unroll
+  for (int k = 0; k < CH / 2; ++k)
+    asm volatile("st.shared.b32 [%0], %1;" ::"r"(sw_row + 4u * (2 * k * 64)), "r"(pk[k]) : "memory");
+  const long long q1 = tq ? clock64() : 0;
+  epi_bar(128);
+  const long long q2 = tq ? clock64() : 0;
+  const int f0 = (et & 15) * 8;                 // eight features = 16 bytes
+  const int io = i0 - t.a_base + f0;
+  if (i0 + f0 + 8 <= t.ra_end) {
+    // all reads from the staging tile first, then the global stores
+    constexpr int NR = CH / 8;
+    uint4 q[NR];
+#pragma unroll
+    for (int k = 0; k < NR; ++k) {
+      const int r = (et >> 4) + 8 * k;
+      asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(q[k].x), "=r"(q[k].y), "=r"(q[k].z), "=r"(q[k].w)
+                   : "r"(sw_s + 4u * (r * 64 + (((f0 >> 1) + 16 * (r & 1)) & 63))));
+    }
+#pragma unroll
+    for (int k = 0; k < NR; ++k) {
+      const int j = j0 + (et >> 4) + 8 * k;
+      if (j < t.rb_end)
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + (long long)j * p.out_sb + io) = q[k];
+    }
+    if (tq) {
+      tq[1] += q1 - q0;
+      tq[2] += q2 - q1;
+      tq[3] += clock64() - q2;
+    }
+  } else if (i0 + f0 < t.ra_end) {
+    // the last features of a matrix whose row count is not a multiple of eight
+    for (int r = et >> 4; r < CH; r += 8) {
+      const int j = j0 + r;
+      if (j < t.rb_end) {
+        const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(sw + r * 64 + (((f0 >> 1) + 16 * (r & 1)) & 63));
+        for (int e = 0; e < 8 && i0 + f0 + e < t.ra_end; ++e)
+          reinterpret_cast<__nv_bfloat16*>(p.out)[(long long)j * p.out_sb + io + e] = row[e];
+      }
     }
   }
 }

@@ -49,6 +49,17 @@ typedef struct LkGemmArgs {
   const int* g_tile_row0;
   const int* g_tile_rows;
   const int* g_ntiles;
+  // lk_gemm_mx, dense e4m3 weights: weight tiles per unit of work in the whole rounds / in the K-split
+  // remainder (0 = the launcher's cost model chooses; `splits` above likewise)
+  int mt, rem_mt;
+  // e4m3 weights stored tile-major: [ceil(Ra / 128)][ceil(K / 128)][128 rows][128 bytes], zero padded
+  int a_tiled;
+  // lk_gemm_mx, optional: int64 [296 x 8].  Row c < 148 (CTA c): cycles the producer waited for a free
+  // stage; cycles the MMA thread waited for operands; global-timer ns when the last unit's MMAs had
+  // completed; cycles of the MMA thread's whole loop; global-timer ns at the CTA's start, when the last
+  // unit's MMAs were issued, and at the end of the epilogue; cycles the epilogue waited for accumulators.
+  // Row 148 + c: cycles the epilogue spent in tensor-memory loads, staging, its barrier, global stores.
+  long long* prof;
 } LkGemmArgs;
 
 int lk_gemm_tc(const LkGemmArgs* args, void* stream);

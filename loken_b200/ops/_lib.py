@@ -65,7 +65,7 @@ class GemmArgs(C.Structure):
         ("status", vp), ("symm_view", vp),
         ("aq_fmt", C.c_int), ("aq", vp), ("aq_scale", vp), ("aq_ld", ll), ("aq_sld", ll),
         ("g_rows_per_expert", C.c_int), ("g_max_tiles", C.c_int), ("g_tile_expert", vp), ("g_tile_row0", vp),
-        ("g_tile_rows", vp), ("g_ntiles", vp),
+        ("g_tile_rows", vp), ("g_ntiles", vp), ("mt", C.c_int), ("rem_mt", C.c_int), ("a_tiled", C.c_int), ("prof", vp),
     ]
 
 

@@ -28,10 +28,23 @@ class Fp8Weight:
     data: torch.Tensor
     scale: torch.Tensor
     _pow2: Optional[bool] = None
+    tiled: Optional[torch.Tensor] = None     # the same values tile-major (`tile_major`), read by lk_gemm_mx
 
     @property
     def shape(self):
         return self.data.shape
+
+    def tile_major(self) -> torch.Tensor:
+        """[ceil(N/128), ceil(K/128), 128, 128]: every 128 x 128 tile is 16 KB in one piece, so the box a
+        CTA fetches per stage is one contiguous read instead of 128 pieces of 128 bytes a row pitch apart."""
+        if self.tiled is None:
+            N, K = self.data.shape
+            n128, k128 = (N + 127) // 128, (K + 127) // 128
+            raw = self.data.view(torch.uint8)
+            if N % 128 or K % 128:
+                raw = torch.nn.functional.pad(raw, (0, k128 * 128 - K, 0, n128 * 128 - N))
+            self.tiled = raw.view(n128, 128, k128, 128).permute(0, 2, 1, 3).contiguous()
+        return self.tiled
 
     @property
     def pow2(self) -> bool:
@@ -117,12 +130,19 @@ def gemm_raw(kind, A, B, out, out_sa, out_sb, *, bias=None, bias_on_a=False, res
 
 SWAP_MAX_M = 256
 FP8_MX = True           # block-fp8 weights with power-of-two scales run on the block-scaled MMA (lk_gemm_mx)
-# ... up to this many tokens (tokens on the MMA N side).  Measured on 57344 x 8192: 16 tokens 87 us against
-# 93 us for the fold kernel; at 64 tokens both are bound by what the SMs pull through L2 (the weight
-# stream plus the token tile re-read for every weight tile: 116 us against 105 us), and the fold kernel's
-# 128-wide weight tile re-reads the tokens half as often
+# ... up to this many tokens (tokens on the MMA N side).  Measured on 57344 x 8192 with three weight tiles
+# per token tile: 16 tokens 76 us against 90 us for the fold kernel, 64 tokens 97 against 105, 128 tokens 122
+# against 114.  The MMA loop itself ends after 64 - 70 us at every batch (6.7 - 7.3 TB/s of weights); what
+# follows is the epilogue (four warps move 128 x BN values through shared memory: memory instructions of one
+# warp per scheduler issue about twenty cycles apart) and the K-split remainder, both exposed when a CTA has
+# a single unit.  Matrices without whole rounds of three-tile units (fewer than 3 x 148 weight tiles) keep
+# the fold kernel above FP8_MX_MAX_M tokens.
 FP8_MX_MAX_M = 32
+FP8_MX_WIDE_MAX_M = 64  # ... and this many tokens when the matrix has at least 3 x 148 tiles of 128 rows
 FP8_MX_BN = 0           # measurement hook: N tile of that path (0 = the launcher's choice)
+FP8_MX_TILED = False    # measurement hook: read the weights tile-major (Fp8Weight.tile_major)
+FP8_MX_PROF = None      # measurement hook: int64 tensor [296, 8] that receives the kernel's per-CTA counters (loken_cuda.h)
+FP8_MX_PLAN = (0, 0, 0) # measurement hook: (weight tiles per unit, tiles per remainder unit, K splits); 0 = cost model
 # fp8 carries one activation scale per token in the swapped form: measured faster only for a handful of tokens
 FP8_BN_OVERRIDE = 0     # measurement hook: N-tile width of the tokens-on-M form (0 = the rule in linear_fp8)
 FP8_SWAP_MAX_M = 16     # measured: up to 16 tokens the weights-on-M form is faster (93 vs 107 us on 57344 x 8192)
@@ -158,7 +178,8 @@ def linear_fp8(x: Fp8Act, w: Fp8Weight, *, bias: Optional[torch.Tensor] = None,
         out = torch.empty(M, N, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=xd.device)
     ldo = out.stride(0)
     sld = x.scale_t.stride(0)
-    if FP8_MX and M <= FP8_MX_MAX_M and symm is None and not out_fp32 and residual is None and w.pow2:
+    mx_max_m = FP8_MX_WIDE_MAX_M if N >= 3 * NUM_SMS * 128 else FP8_MX_MAX_M
+    if FP8_MX and M <= max(FP8_MX_MAX_M, mx_max_m) and symm is None and not out_fp32 and residual is None and w.pow2:
         # power-of-two block scales: one accumulation over all of K on the block-scaled MMA (gemm_mx.cu)
         wsp = Workspace.get(xd.device)
         a = GemmArgs()
@@ -166,11 +187,15 @@ def linear_fp8(x: Fp8Act, w: Fp8Weight, *, bias: Optional[torch.Tensor] = None,
         a.A, a.B = ptr(w.data), ptr(xd)
         a.Ra, a.Rb, a.K = N, M, K
         a.lda, a.ldb = w.data.stride(0), xd.stride(0)
+        if FP8_MX_TILED or w.tiled is not None:
+            a.A, a.a_tiled, a.lda = ptr(w.tile_major()), 1, 128
         a.out, a.out_sa, a.out_sb = ptr(out), 1, ldo
         a.bias, a.bias_on_a = ptr(bias), 1
         a.a_scale, a.a_mode, a.a_ld = ptr(w.scale), SCALE_WBLOCK, w.scale.stride(0)
         a.b_scale, a.b_mode, a.b_ld = ptr(x.scale_t), SCALE_ACT_T, sld
-        a.bn, a.splits = FP8_MX_BN, splits
+        a.bn, a.splits = FP8_MX_BN, FP8_MX_PLAN[2] or splits
+        a.mt, a.rem_mt = FP8_MX_PLAN[0], FP8_MX_PLAN[1]
+        a.prof = ptr(FP8_MX_PROF)
         a.ws, a.ws_floats = ptr(wsp.ws), wsp.ws.numel()
         a.counters, a.n_counters = ptr(wsp.counters), wsp.counters.numel()
         a.status = ptr(wsp.status)

@@ -97,6 +97,70 @@ def gemm_case(kind: str, M: int, N: int, K: int, swap_max_m: int = -1, bn: int =
           f"{2 * M * N * K / ms / 1e9:.1f} TFLOP/s")
 
 
+def gemm_sweep_case(M: int, shapes, variants):
+    """Block-fp8 GEMMs of the given (N, K) shapes at M tokens, each under every variant
+    "name[:max_m[:mt[:rem_mt[:splits]]]]" ("fold" = the per-K-block fold kernel; "mx" = the block-scaled MMA
+    with its plan left to the cost model or forced).  Weights rotate through copies that together exceed
+    the L2, so every launch streams from HBM; times are CUDA-graph replays."""
+    from ..ops import gemm, rows
+
+    for (N, K) in shapes:
+        copies = max(2, (300 << 20) // (N * K) + 1)
+        ws = [gemm.quantize_weight_fp8(torch.randn(N, K, device="cuda") * 0.02) for _ in range(copies)]
+        x = torch.randn(M, K, device="cuda").bfloat16()
+        xq = rows.quant_fp8(x)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        ref = None
+        for v in variants:
+            f = v.split(":")
+            nums = [int(t) for t in f[1:]] + [0] * 4
+            gemm.FP8_MX_MAX_M = 0 if f[0] == "fold" else (nums[0] or 1 << 20)
+            gemm.FP8_MX_WIDE_MAX_M = gemm.FP8_MX_MAX_M
+            gemm.FP8_MX_PLAN = (nums[1], nums[2], nums[3])
+            for w in ws:                       # "mxt": the same weights read tile-major
+                w.tiled = None
+                if f[0] == "mxt":
+                    w.tile_major()
+
+            def fn():
+                for w in ws:
+                    gemm.linear_fp8(xq, w, out=out)
+
+            for _ in range(2):
+                fn()
+            got = out.float().clone()
+            if ref is None:
+                ref = got
+            err = ((got - ref).abs().max() / ref.abs().max()).item()
+            ms = _bracket(fn, 2) / copies
+            note = ""
+            if f[0] != "fold":
+                # one more launch with the kernel's own wait counters: median over the CTAs, in microseconds
+                # at the clock the SM ran (clock64 counts SM cycles; 1.9 GHz assumed for the printout)
+                prof = torch.zeros(296, 8, dtype=torch.int64, device="cuda")
+                gemm.FP8_MX_PROF = prof
+                gemm.linear_fp8(xq, ws[0], out=out)
+                torch.cuda.synchronize()
+                gemm.FP8_MX_PROF = None
+                live = prof[:148][prof[:148, 4] > 0]
+                ex = prof[148:][prof[:148, 4] > 0].float().median(dim=0).values / 1900.0
+                med = live[:, :4].float().median(dim=0).values / 1900.0
+                t0 = int(live[:, 4].min())
+                loop_end = (live[:, 5] - t0).float() / 1e3
+                epi_end = (live[:, 6] - t0).float() / 1e3
+                mma_done = (live[:, 2] - t0).float() / 1e3
+                accw = live[:, 7].float().median() / 1900.0
+                note = (f"; epilogue: tensor-memory loads {ex[0]:.2f}, staging {ex[1]:.2f}, barrier {ex[2]:.2f}, global stores {ex[3]:.2f}, waits for accumulators {accw:.1f}; per CTA (us at 1.9 GHz): loop {med[3]:.1f}, MMA thread waits for operands {med[1]:.1f}, "
+                        f"for an accumulator {med[2]:.1f}; producer waits for a free stage {med[0]:.1f}; global timer (us "
+                        f"after the first CTA's start): last start {float((live[:, 4] - t0).max()) / 1e3:.1f}, last unit's MMAs issued "
+                        f"{loop_end.median():.1f} median / {loop_end.max():.1f} last, completed {mma_done.median():.1f} / "
+                        f"{mma_done.max():.1f}, epilogues end "
+                        f"{epi_end.median():.1f} median / {epi_end.max():.1f} last")
+            print(f"gemm_fp8 M={M} N={N} K={K} {v}: {ms * 1e3:.1f} us/launch, {N * K / ms / 1e6:.0f} GB/s weights, "
+                  f"diff vs first variant {err:.2e}{note}")
+        del ws
+
+
 def decode_step_case(layers: int, batch: int, ctx: int, tp: int, model: str):
     from ..models.config import get_config
     from ..serve.engine import LLMEngine
@@ -266,7 +330,7 @@ def moe_case(T: int, fmt: str, experts: int, top_k: int, H: int, I: int):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm_fp8", "gemm_bf16", "gemm_q8_0", "gemm_q4_k", "gemm_q6_k", "gemm_mxfp4",
+    ap.add_argument("case", choices=["gemm_sweep", "gemm_fp8", "gemm_bf16", "gemm_q8_0", "gemm_q4_k", "gemm_q6_k", "gemm_mxfp4",
                                     "decode_step", "attn_decode", "sampler", "attn_prefill", "add_rmsnorm", "glu",
                                     "rope_kv", "embed", "moe"])
     ap.add_argument("--m", type=int, default=64)
@@ -290,8 +354,12 @@ def main(argv=None):
     ap.add_argument("--gemm-splits", type=int, default=0, help="K splits of a GEMM with fewer tiles than SMs (0 = the library's choice)")
     ap.add_argument("--bn", type=int, default=0, help="fp8 GEMM: N-tile width of the tokens-on-M form (0 = the library's choice)")
     ap.add_argument("--splits", type=int, default=0, help="kv splits of the decode kernel (0 = the library's choice)")
+    ap.add_argument("--shapes", default="57344x8192,8192x28672,10240x8192,8192x8192", help="gemm_sweep: N x K list")
+    ap.add_argument("--variants", default="fold,mx", help="gemm_sweep: name[:max_m[:mt[:rem_mt[:splits]]]] list")
     a = ap.parse_args(argv)
-    if a.case.startswith("gemm_"):
+    if a.case == "gemm_sweep":
+        gemm_sweep_case(a.m, [tuple(int(t) for t in sh.split("x")) for sh in a.shapes.split(",")], a.variants.split(","))
+    elif a.case.startswith("gemm_"):
         gemm_case(a.case[5:], a.m, a.n, a.k, a.swap_max_m, a.bn, a.gemm_splits)
     elif a.case == "decode_step":
         decode_step_case(a.layers, a.batch, a.ctx, a.tp, a.model)

@@ -88,6 +88,41 @@ def test_linear_fp8_block(M, N, K, ue8m0):
     assert rel_err(out2, ref) < 1e-2
 
 
+@pytest.mark.parametrize("tiled", [False, True])
+@pytest.mark.parametrize("M", [5, 64, 128])
+@pytest.mark.parametrize("N,K,plan", [
+    (1024, 1024, (2, 0, 0)), (1152, 2048, (3, 0, 0)),              # tile groups; 9 tiles: a group of 3 ends on the edge
+    (1000, 2048, (3, 2, 3)), (640, 4096, (2, 1, 4)),                 # ragged last tile; remainder units of 2 / 1 tiles, K split
+    (148 * 3 * 128 + 128 * 5, 1024, (3, 2, 2)),                      # whole rounds of 3-tile units, then 5 tiles as 2 + 2 + 1
+    (148 * 2 * 128 + 128, 1536, (2, 2, 0)), (1536, 8192, (0, 0, 0)), # the cost model's own choice
+])
+def test_linear_fp8_block_tile_groups(M, N, K, plan, tiled):
+    """The block-scaled path with several weight tiles per token tile and stage, whole and K-split units:
+    every plan gives the fp32 result of the same quantised operands."""
+    from loken_b200.ops import gemm
+
+    torch.manual_seed(M + N + K)
+    x = torch.randn(M, K, device=DEV) * torch.rand(M, 1, device=DEV) * 2
+    w = torch.randn(N, K, device=DEV) * 0.05
+    wq = gemm.quantize_weight_fp8(w, ue8m0=True)
+    xq = gemm.quantize_act_fp8_ref(x.bfloat16())
+    ref = gemm.dequantize_act_fp8(xq, M) @ gemm.dequantize_weight_fp8(wq).t()
+    if tiled:
+        wq.tile_major()                     # 16 KB per 128 x 128 tile in one piece
+    bias = torch.randn(N, device=DEV)
+    old = gemm.FP8_MX_MAX_M, gemm.FP8_MX_PLAN
+    try:
+        gemm.FP8_MX_MAX_M, gemm.FP8_MX_PLAN = 128, plan
+        out = gemm.linear_fp8(xq, wq, bias=bias)
+        again = gemm.linear_fp8(xq, wq, bias=bias)
+    finally:
+        gemm.FP8_MX_MAX_M, gemm.FP8_MX_PLAN = old
+    torch.cuda.synchronize()
+    assert _status() == 0
+    assert rel_err(out, ref + bias) < 1e-2
+    assert torch.equal(out, again)          # split partials are summed in split order
+
+
 # ------------------------------------------------------------------ row kernels
 def test_embed_add_rmsnorm_glu_quant():
     from loken_b200.ops import gemm, rows
