@@ -102,7 +102,7 @@ class ModelDrafter:
         blocks = max_seqs * ((max_ctx + DRAFT_MAX + block_size - 1) // block_size + 1) + 8
         self.alloc = PagedKvAllocator(blocks, block_size, enable_prefix_cache=False)
         self.runner = ModelRunner(cfg, weights, num_blocks=blocks, block_size=block_size, max_seqs=max_seqs,
-                                  max_tokens=max(max_seqs * (DRAFT_MAX + 2), 2048), max_ctx=max_ctx + DRAFT_MAX,
+                                  max_tokens=max(max_seqs * (DRAFT_MAX + 2), 8192), max_ctx=max_ctx + DRAFT_MAX,
                                   comm=comm, use_graphs=False)
         self.known: Dict[int, List[int]] = {}      # tokens whose K/V the draft cache holds, per sequence
         self.shadow: Dict[int, Sequence] = {}
@@ -112,6 +112,8 @@ class ModelDrafter:
     def _sync(self, s: Sequence) -> int:
         """Brings the draft cache's view of `s` to a prefix of its real tokens; returns its length."""
         toks = s.tokens
+        if getattr(s, "prompt_embeds", None) is not None:
+            return -1                            # embeddings of the target's width: the drafter cannot read them
         have = self.known.get(s.seq_id)
         if have is None:
             if not self.alloc.allocate(s.seq_id, len(toks) + DRAFT_MAX):
@@ -129,6 +131,37 @@ class ModelDrafter:
             return -1
         return n
 
+    CATCH_UP_ROWS = 16      # more pending tokens than this go through the prefill kernels, not as verify rows
+
+    def _catch_up(self, items):
+        """A sequence the drafter meets for the first time (or after a long gap) has its whole prompt
+        pending.  All but its last token are written to the draft cache by variable-length prefill
+        forwards, as many chunks per forward as the runner's row budget holds; what is left (the
+        last token, whose logits start the draft) goes on as verify rows."""
+        from .scheduler import PrefillItem
+
+        budget = self.runner.d_rows.shape[1]
+        max_items = self.runner.d_bt.shape[0]
+        out, todo = [], []
+        for s, toks, start in items:
+            if len(toks) > self.CATCH_UP_ROWS:
+                todo.append((s, start, start + len(toks) - 1))
+                out.append((s, toks[-1:], start + len(toks) - 1))
+            else:
+                out.append((s, toks, start))
+        batch, used = [], 0
+        while todo:
+            s, a, b = todo.pop(0)
+            n = min(b - a, budget - used)
+            batch.append(PrefillItem(s, a, a + n, False))
+            used += n
+            if a + n < b:
+                todo.insert(0, (s, a + n, b))
+            if used >= budget or len(batch) >= max_items or not todo:
+                self.runner.prefill(batch, self.alloc, None)
+                batch, used = [], 0
+        return out
+
     def propose(self, seqs: Seq[Sequence], k: int) -> List[List[int]]:
         t0 = time.perf_counter()
         items, live = [], []
@@ -142,6 +175,7 @@ class ModelDrafter:
         drafts: Dict[int, List[int]] = {s.seq_id: [] for s in seqs}
         if not live or k <= 0:
             return [drafts[s.seq_id] for s in seqs]
+        items = self._catch_up(items)
         logits = self.runner.forward_rows(items, self.alloc, last_only=True)
         views = [_RowView(_greedy_twin(s), []) for s in live]
         first = self.runner.sample_rows(logits, views, [0.0] * len(live))

@@ -44,8 +44,11 @@ def test_prefill_logits_match_oracle(arch, fmt, kw):
     # e4m3 activations carry ~3% rounding per element into every product of the fp8 model, and into the
     # expert products of an MXFP4 model (block-scaled MMA: weights as stored, activations e4m3)
     assert _cos(got, ref[-1]) > (0.99 if fmt in ("fp8_block", "mxfp4") else 0.998)
+    # the greedy token must agree wherever the oracle's lead over the runner-up is clear of the measured
+    # noise (six times the rms difference: a difference of two elements has sqrt(2) of it)
     gap = torch.topk(ref[-1], 2).values
-    if (gap[0] - gap[1]) > 0.05 * ref[-1].abs().max():
+    noise = (got.float() - ref[-1].float().to(got.device)).pow(2).mean().sqrt()
+    if (gap[0] - gap[1]) > max(0.05 * float(ref[-1].abs().max()), 6.0 * float(noise)):
         assert int(got.argmax()) == int(ref[-1].argmax())
 
 
