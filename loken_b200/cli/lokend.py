@@ -31,7 +31,11 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--draft-model")
     s.add_argument("--draft-k", type=int)
     s.add_argument("--lora", help="PEFT adapter directory merged into a bf16 / block-fp8 checkpoint at load")
-    s.add_argument("--tp-sum", choices=["push", "fused", "nccl"], help="how tensor-parallel layers are summed")
+    s.add_argument("--tp-sum", choices=["boundary", "push", "fused", "nccl"],
+                   help="how tensor-parallel layers are summed (boundary = one kernel per layer boundary: "
+                        "reduce-scatter + residual + norm + all-gather)")
+    s.add_argument("--expert-slots", type=int,
+                   help="mixture models larger than the card: experts per layer kept resident, the rest streamed from host memory")
     s.add_argument("--requant", choices=["fp8_block", "bf16"], help="re-encode float tensors at load")
     sub.add_parser("check-config", help="parse the configuration and print what was ignored").add_argument(
         "--config", required=True)
@@ -43,7 +47,8 @@ def apply_flags(cfg, args):
     for name, target, attr in (("model", i, "model"), ("model_id", i, "model_id"), ("host", s, "host"),
                                ("port", s, "port"), ("tp", i, "tp"), ("max_seqs", i, "max_seqs"),
                                ("max_ctx", i, "max_ctx"), ("draft_model", i, "draft_model"),
-                               ("draft_k", i, "draft_k"), ("lora", i, "lora"), ("tp_sum", i, "tp_sum")):
+                               ("draft_k", i, "draft_k"), ("lora", i, "lora"), ("tp_sum", i, "tp_sum"),
+                               ("expert_slots", i, "expert_slots")):
         v = getattr(args, name, None)
         if v is not None:
             setattr(target, attr, v)
@@ -60,6 +65,15 @@ def serve(cfg, requant=None) -> int:
     if not i.model:
         print("lokend: no model configured ([inference] model or --model)", file=sys.stderr)
         return 2
+    import os as _os
+
+    if not _os.path.exists(i.model):
+        from ..store.catalogue import Catalogue as _Cat
+
+        hit = _Cat(cfg.ollama_models_dir, cfg.huggingface_models_dir).resolve(i.model)
+        if hit is not None:                   # `name:tag`, `owner/repo` or a GGUF's file name in a model store
+            i.model_id = i.model_id or hit.name
+            i.model = hit.path
     comm, rank, world = None, 0, 1
     if i.tp > 1:
         from ..parallel.comm import init_distributed
@@ -71,28 +85,21 @@ def serve(cfg, requant=None) -> int:
             return 2
         import torch
 
-        from ..models.config import get_config
+        from ..models.loader import peek_config
 
-        hidden = get_config(i.model).hidden if not i.model.endswith(".gguf") else 8192
+        shape = peek_config(i.model)          # the symmetric heap is sized from the model's own shape
         if i.tp_sum == "nccl":
             from ..parallel.comm import NcclComm
 
             comm = NcclComm()
         else:
-            comm = SymmComm(torch.device("cuda", local), max_rows=max(i.max_seqs, 256), hidden=hidden)
+            comm = SymmComm(torch.device("cuda", local), max_rows=max(i.max_seqs, 256), hidden=shape.hidden,
+                            top_k=shape.top_k if shape.is_moe else 0)
+            comm.fused_norm = i.tp_sum == "boundary"
             comm.fused_gemm = i.tp_sum == "fused"
-    import os as _os
-
-    if not _os.path.exists(i.model):
-        from ..store.catalogue import Catalogue as _Cat
-
-        hit = _Cat(cfg.ollama_models_dir, cfg.huggingface_models_dir).resolve(i.model)
-        if hit is not None:                   # `name:tag`, `owner/repo` or a GGUF's file name in a model store
-            i.model_id = i.model_id or hit.name
-            i.model = hit.path
     llm = LLM.load(i.model, model_id=i.model_id, requant=requant, kv_format=cfg.kv_format, tp_rank=rank,
                    tp_size=world, comm=comm, max_seqs=i.max_seqs, max_ctx=i.max_ctx,
-                   max_prefill_tokens=i.max_prefill_tokens, lora=i.lora,
+                   max_prefill_tokens=i.max_prefill_tokens, lora=i.lora, expert_slots=i.expert_slots,
                    **({"draft": (i.draft_model, i.draft_k)} if (i.draft_model and world > 1) else {}))
     if i.draft_model and world == 1:
         from ..serve.speculative import attach_draft

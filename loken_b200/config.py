@@ -7,7 +7,7 @@ the reference derives from measurement and a B200 node wants stated):
                  max_body_mb, request_timeout_s
     [inference]  model_id, model (GGUF path or built-in shape), replicas, tp, tp_sum, ep, pp, dp, fidelity
                  (reference | balanced | fast), kv_format, max_seqs, max_ctx, max_prefill_tokens,
-                 kv_disk_dir, prefill_peer, draft_model, draft_k, lora, models_dir
+                 kv_disk_dir, prefill_peer, draft_model, draft_k, lora, models_dir, expert_slots
     [energy]     enabled, grid_g_co2_per_kwh
     [cluster]    node_id, listen, peers, heartbeat_ms, suspect_phi
 
@@ -54,7 +54,10 @@ class InferenceSection:
     model: Optional[str] = None
     replicas: int = 1
     tp: int = 1
-    tp_sum: str = "push"        # push (peer-memory all-reduce kernel) | fused (GEMM epilogue) | nccl
+    tp_sum: str = "boundary"    # boundary (one kernel per layer boundary: reduce-scatter + residual + norm +
+                                # all-gather over peer memory) | push (peer-memory all-reduce kernel) |
+                                # fused (GEMM epilogue) | nccl
+    expert_slots: int = 0       # mixture models: experts per layer resident on the card, the rest streamed (0 = all resident)
     ep: int = 1
     pp: int = 1
     dp: int = 1
@@ -109,8 +112,8 @@ class Config:
         for k in ("tp", "ep", "pp", "dp", "replicas"):
             if getattr(i, k) < 1:
                 raise ValueError(f"[inference] {k} must be >= 1")
-        if i.tp_sum not in ("push", "fused", "nccl"):
-            raise ValueError("[inference] tp_sum must be push, fused or nccl")
+        if i.tp_sum not in ("boundary", "push", "fused", "nccl"):
+            raise ValueError("[inference] tp_sum must be boundary, push, fused or nccl")
         if not (0 < self.server.port < 65536):
             raise ValueError("[server] port out of range")
         if self.server.require_auth and not self.server.api_keys:

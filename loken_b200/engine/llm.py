@@ -278,6 +278,13 @@ class LLM:
         group = None
         watchdog = None
         draft = engine_kw.pop("draft", None)       # (model, k): a drafter attached on every rank before wrapping
+        slots = int(engine_kw.pop("expert_slots", 0) or 0)
+        if slots > 0:
+            # a mixture model larger than the card: `slots` experts per layer stay resident, the rest stream
+            # from pinned host memory as the router asks for them (models/expert_tier.py)
+            from ..models.expert_tier import TieredMoeRunner
+
+            engine_kw["moe_runner_factory"] = lambda c, w, cap, cm: TieredMoeRunner(c, w, cap, cm, slots=slots)
         if tp_size > 1:
             import torch.distributed as dist
 

@@ -317,3 +317,25 @@ class _ShapeOnly:
 
     def __init__(self, shape):
         self.shape = tuple(shape)
+
+
+def peek_config(model: str) -> ModelConfig:
+    """The shape of `model` (a Hugging Face checkpoint directory, a GGUF file or the name of a built-in
+    shape) without reading a tensor: what has to be known before the weights load, e.g. to size the
+    symmetric heap of a tensor-parallel group."""
+    import json
+    import os
+
+    if os.path.isdir(model) and os.path.exists(os.path.join(model, "config.json")):
+        from .loader_hf import config_from_hf
+
+        with open(os.path.join(model, "config.json")) as f:
+            return config_from_hf(json.load(f), os.path.basename(os.path.normpath(model)))
+    if os.path.exists(model):
+        from ..formats.gguf import GGUFReader
+
+        meta = GGUFReader(model).meta
+        return ModelConfig.from_gguf_meta(meta, meta.get("general.name", "gguf"))
+    from .config import get_config
+
+    return get_config(model)
