@@ -383,28 +383,41 @@ def create_app(registry: ModelRegistry, settings: Optional[ServerSettings] = Non
 
 
 def serve(registry: ModelRegistry, settings: Optional[ServerSettings] = None, cluster=None, catalogue=None):
-    """`cluster`: the configuration's [cluster] section; with peers listed, a gossip loop runs beside
-    the server (`cluster/gossip.py`).  `catalogue`: the model stores (`store/catalogue.py`) behind
+    """`cluster`: the configuration's [cluster] section; with peers listed or discovery on, a gossip loop
+    runs beside the server (`cluster/gossip.py`, `cluster/discovery.py`).  `catalogue`: the model stores (`store/catalogue.py`) behind
     listings, pulls, copies and deletes, and behind loads by name."""
     import uvicorn
 
     s = settings or ServerSettings()
     app = create_app(registry, s)
     app.state.ctx.catalogue = catalogue
-    loop = None
-    if cluster is not None and getattr(cluster, "peers", None):
+    loop, disco = None, None
+    if cluster is not None and (getattr(cluster, "peers", None) or getattr(cluster, "discovery", False)):
         import socket
 
         from ..cluster.gossip import GossipLoop
         from ..cluster.membership import Membership
 
         ctx = app.state.ctx
-        ctx.membership = Membership(cluster.node_id or socket.gethostname(), suspect_phi=cluster.suspect_phi)
-        loop = GossipLoop(ctx.membership, cluster.listen or f"http://{s.host}:{s.port}", list(cluster.peers),
-                          ctx.describe, interval_s=cluster.heartbeat_ms / 1000.0)
+        node_id = cluster.node_id or socket.gethostname()
+        me = cluster.listen or f"http://{s.host}:{s.port}"
+        ctx.membership = Membership(node_id, suspect_phi=cluster.suspect_phi)
+        loop = GossipLoop(ctx.membership, me, list(cluster.peers), ctx.describe,
+                          interval_s=cluster.heartbeat_ms / 1000.0)
+        if getattr(cluster, "discovery", False):
+            # nodes heard on the multicast group join the gossip's address book beside the seeds
+            from ..cluster.discovery import Announcement, Discovery
+
+            try:
+                disco = Discovery(Announcement(cluster.name, node_id, me),
+                                  on_peer=lambda nid, ep: loop.addrs.setdefault(ep, ep)).start()
+            except OSError as e:
+                print(f"loken: multicast discovery is off ({e}); the seed list still applies", flush=True)
         loop.start()
     try:
         uvicorn.run(app, host=s.host, port=s.port, log_level="info")
     finally:
         if loop is not None:
             loop.stop()
+        if disco is not None:
+            disco.stop()

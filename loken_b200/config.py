@@ -9,7 +9,7 @@ the reference derives from measurement and a B200 node wants stated):
                  (reference | balanced | fast), kv_format, max_seqs, max_ctx, max_prefill_tokens,
                  kv_disk_dir, prefill_peer, draft_model, draft_k, lora, models_dir, expert_slots
     [energy]     enabled, grid_g_co2_per_kwh
-    [cluster]    node_id, listen, peers, heartbeat_ms, suspect_phi
+    [cluster]    node_id, listen, peers, heartbeat_ms, suspect_phi, name, discovery
 
 Keys that older files carry and that no longer mean anything load fine and are reported
 (`config.rs:134`); unknown keys are reported as well, never fatal.  `LOKEN_API_KEY` adds an API key,
@@ -88,6 +88,8 @@ class ClusterSection:
     peers: List[str] = field(default_factory=list)
     heartbeat_ms: int = 500
     suspect_phi: float = 8.0
+    name: str = "loken"         # discovery ignores announcements that name another cluster
+    discovery: bool = False     # announce on, and listen to, the multicast group (cluster/discovery.py)
 
 
 @dataclass
