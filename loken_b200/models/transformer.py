@@ -25,6 +25,7 @@ from typing import List, Optional
 
 import torch
 
+from ..utils import nvtx
 from ..ops import attention, gemm, rows
 from ..ops.gemm import Fp8Act
 from ..ops.rows import KVCacheLayer
@@ -220,6 +221,7 @@ class DecoderModel:
         self.sharded_steps += int(shard)
         for il in range(lo, hi):
             lw = w.layers[il]
+            nvtx.mark(f"layer {il}", level=2)
             # attention block
             self._norm(b.x, lw.attn_norm, delta, T, lw.wqkv.wants_fp8, shard, local=self._delta_local)
             self._delta_local = False

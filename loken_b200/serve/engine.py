@@ -20,6 +20,7 @@ import torch
 
 from ..models.config import ModelConfig, get_config
 from ..models.weights import ModelWeights, random_weights
+from ..utils import nvtx
 from .kv_manager import PagedKvAllocator
 from .params import SamplingParams
 from .runner import ModelRunner
@@ -262,7 +263,8 @@ class LLMEngine:
                 self.sched.finish(seq, "cancelled")
                 outs[sid] = StepOutput(sid, [], True, "cancelled")
         self.cancelled.clear()
-        plan = self.sched.schedule()
+        with nvtx.span("schedule"):
+            plan = self.sched.schedule()
         self.stats.preemptions += len(plan.preempted)
         for seq in plan.rejected:
             outs[seq.seq_id] = StepOutput(seq.seq_id, [], True, "error")
@@ -270,17 +272,20 @@ class LLMEngine:
             return list(outs.values())
         lps: Dict[int, tuple] = {}
         try:
-            first = self.runner.prefill(plan.prefills, self.alloc, self.rngs) if plan.prefills else {}
+            with nvtx.span("prefill"):
+                first = self.runner.prefill(plan.prefills, self.alloc, self.rngs) if plan.prefills else {}
             if first:
                 done = [it.seq for it in plan.prefills if it.seq.seq_id in first]
                 self._logprobs(done, [first[s.seq_id] for s in done], lps)
             spec = self.spec
             commits = None
             if plan.decodes and spec is not None and not any(s.grammar is not None for s in plan.decodes):
-                commits = spec.step(self, list(plan.decodes))
+                with nvtx.span("verify"):
+                    commits = spec.step(self, list(plan.decodes))
                 toks = []
             else:
-                toks = self.runner.decode(plan.decodes, self.alloc, self.rngs) if plan.decodes else []
+                with nvtx.span("decode"):
+                    toks = self.runner.decode(plan.decodes, self.alloc, self.rngs) if plan.decodes else []
                 if plan.decodes:
                     self._logprobs(list(plan.decodes), toks, lps)
             self.runner.check_status()
