@@ -79,6 +79,12 @@ class LLMEngine:
             weights = random_weights(self.cfg, self.device, seed=seed, tp_rank=tp_rank, tp_size=tp_size,
                                      ep_rank=tp_rank, ep_size=tp_size)
         self.weights = weights
+        if self.cfg.kv_format == "q8" and self.cfg.qk_norm:
+            # keys are stored as int8 with one step per 32 lanes: fold a per-lane scale into the Q / K norm
+            # weights so the lanes of a block carry comparable magnitudes (scores are unchanged)
+            from ..models.key_scale import apply_key_scale
+
+            apply_key_scale(weights)
         if num_blocks is None:
             free, _total = torch.cuda.mem_get_info(self.device)
             reserve = 6 << 30     # activations, graphs, workspaces
