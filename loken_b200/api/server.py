@@ -221,6 +221,35 @@ def ops_router(ctx: ServerContext):
         ctx.registry.add(llm, default=bool(body.get("default")))
         return {"status": "loaded", "model": llm.info(), "evicted": evicted}
 
+    @r.post("/api/swap")
+    async def swap(req: Request):
+        """Replace the resident model: the named one (or every resident language model when none is
+        named) is unloaded first, so the new model has the card to itself, then the new one is loaded as
+        the default.  A load that fails leaves the server without the old model: the reply says so."""
+        import json as _json
+
+        body = await req.json()
+        if not (body.get("model") or body.get("path")):
+            raise ApiError(400, "model (what to load) is required")
+        names = [body["replace"]] if body.get("replace") else [m.model_id for m in ctx.registry.list()]
+        gone = [n for n in names if ctx.registry.remove(n)]
+        from ..place.vram import authority
+
+        authority().residency_epoch += len(gone)
+        body["default"] = True
+
+        class _Again:
+            async def json(self_inner):
+                return body
+
+        try:
+            out = await load(_Again())
+        except ApiError as e:
+            raise ApiError(e.status, f"{e.message} (unloaded: {_json.dumps(gone)})")
+        out["status"] = "swapped"
+        out["unloaded"] = gone
+        return out
+
     @r.delete("/api/models/{model_id:path}")
     async def unload(model_id: str):
         if not ctx.registry.remove(model_id):

@@ -450,6 +450,32 @@ def test_devices_route_version_stamp_and_load_eviction():
     assert c.post("/load", json={"model": "x.gguf"}).status_code == 507
 
 
+def test_swap_replaces_the_resident_model():
+    c, reg = client()
+    app = c.app
+    seen = []
+
+    def loader(path, model_id=None, **kw):
+        seen.append(([m.model_id for m in reg.list()], path))       # what was resident when the load began
+        return fake_llm("new", model_id=model_id or "new")
+
+    app.state.ctx.loader = loader
+    assert c.post("/api/swap", json={}).status_code == 400
+    r = c.post("/api/swap", json={"model": "next.gguf", "id": "new"})
+    assert r.status_code == 200, r.text
+    j = r.json()
+    assert j["status"] == "swapped" and j["unloaded"] == ["fake-model"] and j["model"]["id"] == "new"
+    assert seen == [([], "next.gguf")]                               # the old model left before the new one loaded
+    assert [m.model_id for m in reg.list()] == ["new"] and reg.default == "new"
+
+    def broken(path, model_id=None, **kw):
+        raise FileNotFoundError(path)
+
+    app.state.ctx.loader = broken
+    r = c.post("/api/swap", json={"model": "gone.gguf"})
+    assert r.status_code == 400 and "unloaded" in r.text and reg.list() == []
+
+
 def test_prefill_peer_is_asked_for_long_prompts_and_failures_fall_back():
     settings = ServerSettings(prefill_peer="http://peer:11434", prefill_peer_min_tokens=8)
     c, reg = client(settings=settings)
