@@ -8,8 +8,10 @@
     loken validate FILE.gguf              check a GGUF file: header, tensor table, payload sizes
     loken convert --shape NAME --format q8_0 -o out.gguf     write a random-init model file
     loken draft attach|detach|status
-Commands that need weights from a hub (pull, popular, draft-head) report that this build has no
-network access.
+    loken pull NAME                       fetch a model into the daemon's stores (streams progress; resumable)
+    loken swap PATH [--id NAME]           replace the resident model
+    loken launch AGENT [-m MODEL] [--config] [-- ARGS]      run a coding agent against the daemon
+Commands that need a hub catalogue (popular, draft-head, calibrate) say that this build has none.
 """
 from __future__ import annotations
 
@@ -125,7 +127,18 @@ def build_parser() -> argparse.ArgumentParser:
     d.add_argument("--draft")
     d.add_argument("-k", type=int, default=4)
     d.add_argument("--method", default="model", choices=["model", "prompt_lookup"])
-    for name in ("pull", "popular", "draft-head", "calibrate", "launch"):
+    pl = sub.add_parser("pull")
+    pl.add_argument("name", help="name:tag of an Ollama registry model, or owner/repo[:file] on the Hugging Face hub")
+    pl.add_argument("--insecure", action="store_true")
+    sw = sub.add_parser("swap")
+    sw.add_argument("path")
+    sw.add_argument("--id")
+    la = sub.add_parser("launch")
+    la.add_argument("agent", choices=["claude", "cline"])
+    la.add_argument("-m", "--model")
+    la.add_argument("--config", action="store_true", help="print or write the configuration and start nothing")
+    la.add_argument("args", nargs="*", help="arguments handed to the agent, after --")
+    for name in ("popular", "draft-head", "calibrate"):
         sub.add_parser(name).add_argument("args", nargs="*")
     return ap
 
@@ -189,6 +202,42 @@ def main(argv=None, out=sys.stdout) -> int:
             cfg = dataclasses.replace(cfg, n_layers=args.layers)
         export_random_gguf(args.output, cfg, seed=args.seed)
         p(f"wrote {args.output}")
+    elif args.cmd == "swap":
+        p(json.dumps(cl.json("POST", "/api/swap", {"model": args.path, "id": args.id}), indent=1))
+    elif args.cmd == "pull":
+        # a pull is stalled when no progress line arrives for 8 times the longest gap seen so far
+        import time
+
+        last, longest, status = time.monotonic(), 5.0, None
+        for ev in cl.ndjson("/api/pull", {"model": args.name, "insecure": args.insecure}):
+            now = time.monotonic()
+            longest, last = max(longest, now - last), now
+            if ev.get("error"):
+                p(f"loken: {ev['error']}")
+                return 1
+            if ev.get("total"):
+                out.write(f"\r{ev.get('status', '')}: {100.0 * ev.get('completed', 0) / ev['total']:5.1f} %")
+                out.flush()
+            elif ev.get("status") != status:
+                status = ev.get("status")
+                p(f"\n{status}" if status else "")
+        p()
+    elif args.cmd == "launch":
+        import os
+
+        from . import launch as L
+
+        loaded = [m["name"] for m in cl.json("GET", "/api/ps").get("models", [])]
+        held = [m["name"] for m in cl.json("GET", "/api/tags").get("models", [])]
+        try:
+            model = L.pick_model(args.model, loaded, held)
+            info = cl.json("POST", "/api/show", {"model": model}).get("model_info") or {}
+            window = next((int(v) for k, v in info.items() if k.endswith(".context_length")), None)
+            key = os.environ.get("LOKEN_API_KEY") or args.api_key or None
+            return L.launch(args.agent, L.Launch(args.server, model, key, window), args.config, args.args, out)
+        except ValueError as e:
+            p(f"loken: {e}")
+            return 1
     elif args.cmd == "draft":
         if args.action == "status":
             p(json.dumps(cl.json("GET", "/api/draft/status"), indent=1))
@@ -198,8 +247,8 @@ def main(argv=None, out=sys.stdout) -> int:
         else:
             p(json.dumps(cl.json("POST", "/api/draft/detach", {"model": args.model})))
     else:
-        p(f"loken {args.cmd}: this build has no network access to a model hub; place GGUF files on disk and use "
-          f"`loken load`")
+        p(f"loken {args.cmd}: this build has no hub catalogue; `loken pull NAME` fetches a named model and "
+          f"`loken load PATH` loads a file")
         return 1
     return 0
 
