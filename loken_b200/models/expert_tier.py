@@ -112,6 +112,7 @@ class TieredLayer:
 
 class TieredMoeRunner(MoeRunner):
     """`MoeRunner` whose expert stacks are slot caches over host memory."""
+    plans_on_host = True        # the round plan reads the router's choices on the host: no CUDA-graph capture
 
     def __init__(self, cfg, weights, cap: int, comm=None, slots: int = 8):
         super().__init__(cfg, weights, cap, comm)

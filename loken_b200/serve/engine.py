@@ -102,7 +102,10 @@ class LLMEngine:
             moe_runner = MoeRunner(self.cfg, weights, max(max_prefill_tokens, max_seqs), comm)
         self.runner = ModelRunner(self.cfg, weights, num_blocks=num_blocks, block_size=block_size,
                                   max_seqs=max_seqs, max_tokens=max_prefill_tokens, max_ctx=max_ctx, comm=comm,
-                                  moe_runner=moe_runner, use_graphs=use_graphs, device=self.device,
+                                  moe_runner=moe_runner,
+                                  # a runner that plans on the host inside the step (host-streamed experts) cannot be captured
+                                  use_graphs=use_graphs and not getattr(moe_runner, "plans_on_host", False),
+                                  device=self.device,
                                   pipeline=pipeline)
         self.eos = set(eos_token_ids or [])
         self.runner.end_ids = sorted(self.eos)
