@@ -36,8 +36,7 @@ using namespace lk;
 
 namespace {
 
-constexpr int NT = 256;
-constexpr int MAX_IT = 8;      // 8 iterations x 256 threads x 8 values = 16384 columns at most
+constexpr int MAX_CHUNKS = 256 * 8;      // 8 chunks x 256 threads x 8 values = 16384 columns at most
 
 struct TpNormParams {
   SymmView sv;
@@ -79,43 +78,8 @@ __device__ __forceinline__ uint2 ld_ll8(const void* p) {
   return v;
 }
 
-// Bounded polls.  `ab` is the CTA's abort word: once one thread has given up, the others stop
-// waiting too (their results are garbage; the status word says so).
-__device__ __forceinline__ bool ll_wait16(const void* p, unsigned epoch, uint4& v, volatile int* ab, int* status,
-                                          int src) {
-  v = ld_ll16(p);
-  if (v.y == epoch && v.w == epoch) return true;
-  const long long t0 = clock64();
-  for (unsigned it = 1;; ++it) {
-    v = ld_ll16(p);
-    if (v.y == epoch && v.w == epoch) return true;
-    if ((it & 63u) == 0u) {
-      if (*ab) return false;
-      if (clock64() - t0 > LK_PEER_WAIT_CYCLES) break;
-    }
-  }
-  *ab = 1;
-  if (status) atomicCAS(status, 0, LK_ERR_PEER_TIMEOUT | (src << 8));
-  return false;
-}
-__device__ __forceinline__ bool ll_wait8(const void* p, unsigned epoch, uint2& v, volatile int* ab, int* status,
-                                         int src) {
-  v = ld_ll8(p);
-  if (v.y == epoch) return true;
-  const long long t0 = clock64();
-  for (unsigned it = 1;; ++it) {
-    v = ld_ll8(p);
-    if (v.y == epoch) return true;
-    if ((it & 63u) == 0u) {
-      if (*ab) return false;
-      if (clock64() - t0 > LK_PEER_WAIT_CYCLES) break;
-    }
-  }
-  *ab = 1;
-  if (status) atomicCAS(status, 0, LK_ERR_PEER_TIMEOUT | (src << 8));
-  return false;
-}
-
+// `ab` (below) is the CTA's abort word: once one thread has given up on a wait, the others stop waiting
+// too (their results are garbage; the status word says so).
 __device__ __forceinline__ void add_bf16x2(uint32_t w, float& a, float& b) {
   const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
   a += f.x;
@@ -131,7 +95,27 @@ __device__ __forceinline__ long long hop2_row_bytes(int H, bool f8) {
   return (data + sc + 15) & ~15ll;
 }
 
-template <int W>
+__device__ __forceinline__ bool ll_ok(const uint4& v, unsigned epoch) { return v.y == epoch && v.w == epoch; }
+
+// One bounded step of a batched poll: called when some word of the batch was not valid yet.  Returns
+// false when the wait is over (a thread of the CTA gave up, or this one ran out of time).
+__device__ __forceinline__ bool poll_again(unsigned& spins, long long& t0, volatile int* ab, int* status, int src) {
+  if (spins == 0) t0 = clock64();
+  if ((++spins & 15u) == 0u) {
+    if (*ab) return false;
+    if (clock64() - t0 > LK_PEER_WAIT_CYCLES) {
+      *ab = 1;
+      if (status) atomicCAS(status, 0, LK_ERR_PEER_TIMEOUT | (src << 8));
+      return false;
+    }
+  }
+  return true;
+}
+
+// NT threads per CTA, IT chunks of eight values per thread: NT * IT * 8 >= H.  Every wait is a batched
+// poll: all the words a thread needs in a step are requested together, and the ones that have not
+// arrived are requested again together, so a late peer costs one round trip per retry, not one per word.
+template <int W, int NT, int IT>
 __global__ void __launch_bounds__(NT)
 tp_sum_norm_kernel(const TpNormParams p) {
   pdl_wait();
@@ -172,36 +156,54 @@ tp_sum_norm_kernel(const TpNormParams p) {
   for (int r = blockIdx.x; r < T; r += gridDim.x) {
     if (r / rpr != me) continue;
     const int rl = r - me * rpr;
-    float v[MAX_IT][8];
+    float v[IT][8];
     float ss = 0.f;
 #pragma unroll
-    for (int it = 0; it < MAX_IT; ++it) {
+    for (int it = 0; it < IT; ++it) {
       const int c = it * NT + threadIdx.x;
       if (c < nchunk) {
-        // every peer's two words of this chunk are requested before the first is examined
         uint4 q[W][2];
+        const uint4 own_q = *reinterpret_cast<const uint4*>(p.partial + (long long)r * p.ld_p + c * 8);
+        if (!local) {
+          const char* src0 = mine + (long long)rl * hop1_row + (long long)c * 32;
+          const long long sstep = (long long)rpr * hop1_row;
 #pragma unroll
-        for (int s = 0; s < W; ++s) {
-          if (s == me) {
-            q[s][0] = *reinterpret_cast<const uint4*>(p.partial + (long long)r * p.ld_p + c * 8);
-          } else if (!local) {
-            const char* src = mine + ((long long)s * rpr + rl) * hop1_row + (long long)c * 32;
-            q[s][0] = ld_ll16(src);
-            q[s][1] = ld_ll16(src + 16);
+          for (int s = 0; s < W; ++s) {
+            if (s != me) {
+              q[s][0] = ld_ll16(src0 + s * sstep);
+              q[s][1] = ld_ll16(src0 + s * sstep + 16);
+            }
+          }
+          unsigned spins = 0;
+          long long t0 = 0;
+          while (true) {
+            bool all = true;
+            int late = 0;
+#pragma unroll
+            for (int s = 0; s < W; ++s)
+              if (s != me && !(ll_ok(q[s][0], epoch) && ll_ok(q[s][1], epoch))) {
+                all = false;
+                late = s;
+              }
+            if (all || !poll_again(spins, t0, ab, p.status, late)) break;
+#pragma unroll
+            for (int s = 0; s < W; ++s) {
+              if (s != me) {
+                if (!ll_ok(q[s][0], epoch)) q[s][0] = ld_ll16(src0 + s * sstep);
+                if (!ll_ok(q[s][1], epoch)) q[s][1] = ld_ll16(src0 + s * sstep + 16);
+              }
+            }
           }
         }
         float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int s = 0; s < W; ++s) {       // rank order: the same bits whichever peer arrives first
           if (s == me) {
-            add_bf16x2(q[s][0].x, a[0], a[1]);
-            add_bf16x2(q[s][0].y, a[2], a[3]);
-            add_bf16x2(q[s][0].z, a[4], a[5]);
-            add_bf16x2(q[s][0].w, a[6], a[7]);
+            add_bf16x2(own_q.x, a[0], a[1]);
+            add_bf16x2(own_q.y, a[2], a[3]);
+            add_bf16x2(own_q.z, a[4], a[5]);
+            add_bf16x2(own_q.w, a[6], a[7]);
           } else if (!local) {
-            const char* src = mine + ((long long)s * rpr + rl) * hop1_row + (long long)c * 32;
-            if (!(q[s][0].y == epoch && q[s][0].w == epoch)) ll_wait16(src, epoch, q[s][0], ab, p.status, s);
-            if (!(q[s][1].y == epoch && q[s][1].w == epoch)) ll_wait16(src + 16, epoch, q[s][1], ab, p.status, s);
             add_bf16x2(q[s][0].x, a[0], a[1]);
             add_bf16x2(q[s][0].z, a[2], a[3]);
             add_bf16x2(q[s][1].x, a[4], a[5]);
@@ -231,7 +233,7 @@ tp_sum_norm_kernel(const TpNormParams p) {
     ss = block_sum(ss, red);
     const float rinv = rsqrtf(ss / (float)H + p.eps);
 #pragma unroll
-    for (int it = 0; it < MAX_IT; ++it) {
+    for (int it = 0; it < IT; ++it) {
       const int c = it * NT + threadIdx.x;
       if (c < nchunk) {
         const float4* w4 = reinterpret_cast<const float4*>(p.w + c * 8);
@@ -295,34 +297,84 @@ tp_sum_norm_kernel(const TpNormParams p) {
       if (own == me) continue;
       const char* src = mine + p.sv.ll_hop2_off + (long long)r * hop2_row;
       if (f8) {
-        // two chunks per thread in flight
-        for (int c0 = threadIdx.x; c0 < nchunk; c0 += 2 * NT) {
-          const int c1 = c0 + NT;
-          uint4 a = ld_ll16(src + (long long)c0 * 16), b = make_uint4(0, epoch, 0, epoch);
-          if (c1 < nchunk) b = ld_ll16(src + (long long)c1 * 16);
-          if (!(a.y == epoch && a.w == epoch)) ll_wait16(src + (long long)c0 * 16, epoch, a, ab, p.status, own);
-          *reinterpret_cast<uint2*>(p.out_fp8 + (long long)r * H + c0 * 8) = make_uint2(a.x, a.z);
-          if (c1 < nchunk) {
-            if (!(b.y == epoch && b.w == epoch)) ll_wait16(src + (long long)c1 * 16, epoch, b, ab, p.status, own);
-            *reinterpret_cast<uint2*>(p.out_fp8 + (long long)r * H + c1 * 8) = make_uint2(b.x, b.z);
+        // a thread's IT payload words and (the first H / 128 threads) one scale word, all in one batch
+        uint4 a[IT];
+        const bool has_sc = threadIdx.x < (H >> 7);
+        uint2 sc = make_uint2(0u, epoch);
+#pragma unroll
+        for (int it = 0; it < IT; ++it) {
+          const int c = it * NT + threadIdx.x;
+          a[it] = c < nchunk ? ld_ll16(src + (long long)c * 16) : make_uint4(0u, epoch, 0u, epoch);
+        }
+        if (has_sc) sc = ld_ll8(src + hop2_data + (long long)threadIdx.x * 8);
+        unsigned spins = 0;
+        long long t0 = 0;
+        while (true) {
+          bool all = sc.y == epoch;
+#pragma unroll
+          for (int it = 0; it < IT; ++it) all = all && ll_ok(a[it], epoch);
+          if (all || !poll_again(spins, t0, ab, p.status, own)) break;
+#pragma unroll
+          for (int it = 0; it < IT; ++it)
+            if (!ll_ok(a[it], epoch)) a[it] = ld_ll16(src + (long long)(it * NT + threadIdx.x) * 16);
+          if (sc.y != epoch) sc = ld_ll8(src + hop2_data + (long long)threadIdx.x * 8);
+        }
+#pragma unroll
+        for (int it = 0; it < IT; ++it) {
+          const int c = it * NT + threadIdx.x;
+          if (c < nchunk) *reinterpret_cast<uint2*>(p.out_fp8 + (long long)r * H + c * 8) = make_uint2(a[it].x, a[it].z);
+        }
+        if (has_sc) p.scales_t[(long long)threadIdx.x * p.scale_ld + r] = __uint_as_float(sc.x);
+      } else {
+        uint4 a[IT][2];
+#pragma unroll
+        for (int it = 0; it < IT; ++it) {
+          const int c = it * NT + threadIdx.x;
+          if (c < nchunk) {
+            a[it][0] = ld_ll16(src + (long long)c * 32);
+            a[it][1] = ld_ll16(src + (long long)c * 32 + 16);
+          } else {
+            a[it][0] = a[it][1] = make_uint4(0u, epoch, 0u, epoch);
           }
         }
-        for (int g = threadIdx.x; g < (H >> 7); g += NT) {
-          uint2 s;
-          ll_wait8(src + hop2_data + (long long)g * 8, epoch, s, ab, p.status, own);
-          p.scales_t[(long long)g * p.scale_ld + r] = __uint_as_float(s.x);
+        unsigned spins = 0;
+        long long t0 = 0;
+        while (true) {
+          bool all = true;
+#pragma unroll
+          for (int it = 0; it < IT; ++it) all = all && ll_ok(a[it][0], epoch) && ll_ok(a[it][1], epoch);
+          if (all || !poll_again(spins, t0, ab, p.status, own)) break;
+#pragma unroll
+          for (int it = 0; it < IT; ++it) {
+            const long long off = (long long)(it * NT + threadIdx.x) * 32;
+            if (!ll_ok(a[it][0], epoch)) a[it][0] = ld_ll16(src + off);
+            if (!ll_ok(a[it][1], epoch)) a[it][1] = ld_ll16(src + off + 16);
+          }
         }
-      } else {
-        for (int c = threadIdx.x; c < nchunk; c += NT) {
-          uint4 a = ld_ll16(src + (long long)c * 32), b = ld_ll16(src + (long long)c * 32 + 16);
-          if (!(a.y == epoch && a.w == epoch)) ll_wait16(src + (long long)c * 32, epoch, a, ab, p.status, own);
-          if (!(b.y == epoch && b.w == epoch)) ll_wait16(src + (long long)c * 32 + 16, epoch, b, ab, p.status, own);
-          *reinterpret_cast<uint4*>(p.out_bf16 + (long long)r * p.ld_o + c * 8) = make_uint4(a.x, a.z, b.x, b.z);
+#pragma unroll
+        for (int it = 0; it < IT; ++it) {
+          const int c = it * NT + threadIdx.x;
+          if (c < nchunk)
+            *reinterpret_cast<uint4*>(p.out_bf16 + (long long)r * p.ld_o + c * 8) =
+                make_uint4(a[it][0].x, a[it][0].z, a[it][1].x, a[it][1].z);
         }
       }
     }
   }
   symm_epoch_end(p.sv);
+}
+
+template <int W>
+void launch_sum_norm(const TpNormParams& p, int grid, cudaStream_t st) {
+  const int nchunk = p.H >> 3;
+  // more ranks mean more words per chunk in flight: more threads with fewer chunks each keep the
+  // sequential steps of an owned row few
+  if (W >= 4 && nchunk <= 512 * 2)
+    lkh::launch_pdl(tp_sum_norm_kernel<W, 512, 2>, dim3(grid), dim3(512), 0, st, p);
+  else if (nchunk <= 256 * 4)
+    lkh::launch_pdl(tp_sum_norm_kernel<W, 256, 4>, dim3(grid), dim3(256), 0, st, p);
+  else
+    lkh::launch_pdl(tp_sum_norm_kernel<W, 256, 8>, dim3(grid), dim3(256), 0, st, p);
 }
 
 }  // namespace
@@ -339,7 +391,7 @@ LK_API int lk_tp_sum_norm(const void* view, const void* partial, long long ld_p,
   TpNormParams p;
   p.sv = *reinterpret_cast<const SymmView*>(view);
   const int W = p.sv.world;
-  if (H % 8 || (out_fp8 && (H % 128 || !scales_t)) || (H >> 3) > MAX_IT * NT) return LKH_BAD_ARG;
+  if (H % 8 || (out_fp8 && (H % 128 || !scales_t)) || (H >> 3) > MAX_CHUNKS) return LKH_BAD_ARG;
   if ((ld_p & 7) || (ld_x & 7) || (out_bf16 && (ld_o & 7))) return LKH_BAD_ARG;
   if (out_bf16 && out_fp8 && gather) return LKH_BAD_ARG;      // one payload format per call travels
   const long long rpr = (T + W - 1) / W;
@@ -367,10 +419,10 @@ LK_API int lk_tp_sum_norm(const void* view, const void* partial, long long ld_p,
   const int grid = T < 148 ? T : 148;        // every CTA waits on peers: all of them resident at once
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   switch (W) {
-    case 1: lkh::launch_pdl(tp_sum_norm_kernel<1>, dim3(grid), dim3(NT), 0, st, p); break;
-    case 2: lkh::launch_pdl(tp_sum_norm_kernel<2>, dim3(grid), dim3(NT), 0, st, p); break;
-    case 4: lkh::launch_pdl(tp_sum_norm_kernel<4>, dim3(grid), dim3(NT), 0, st, p); break;
-    case 8: lkh::launch_pdl(tp_sum_norm_kernel<8>, dim3(grid), dim3(NT), 0, st, p); break;
+    case 1: launch_sum_norm<1>(p, grid, st); break;
+    case 2: launch_sum_norm<2>(p, grid, st); break;
+    case 4: launch_sum_norm<4>(p, grid, st); break;
+    case 8: launch_sum_norm<8>(p, grid, st); break;
     default: return LKH_BAD_ARG;
   }
   lkh::count_launch();

@@ -61,4 +61,6 @@ def test_loken_convert_and_validate(tmp_path):
     with pytest.raises((IOError, OSError, SystemExit)):
         loken.validate_gguf(bad)
     out2 = io.StringIO()
-    assert loken.main(["pull", "whatever"], out=out2) == 1 and "no network" in out2.getvalue()
+    assert loken.main(["popular"], out=out2) == 1 and "no hub catalogue" in out2.getvalue()
+    with pytest.raises(SystemExit, match="cannot reach"):       # a pull goes through the daemon, which is not running
+        loken.main(["--server", "http://127.0.0.1:9", "pull", "whatever"], out=out2)

@@ -53,7 +53,8 @@ def test_tensor_parallel_matches_single_gpu(tmp_path, fmt):
         assert rep[f"logits_cos_min_{name}"] >= bound, (name, rep)
         assert rep[f"status_{name}"] == 0, (name, rep)
         assert rep[f"cos_vs_nccl_{name}"] >= bound, (name, rep)
-    assert rep["cos_vs_nccl_push"] >= 0.99999 and rep["cos_vs_nccl_fused"] >= 0.99999     # same rounding places as NCCL
+    if rep["world"] == 2:      # a sum of two has one order: the same rounding places as NCCL
+        assert rep["cos_vs_nccl_push"] >= 0.99999 and rep["cos_vs_nccl_fused"] >= 0.99999
     assert rep["sharded_steps_sum_norm"] > 0 and rep["sharded_steps_push"] == 0
 
 
