@@ -197,6 +197,8 @@ def params_from_openai(body: dict, llm: LLM, chat: bool) -> GenerationParams:
         thinking_token_budget=body.get("thinking_token_budget"),
         truncate_prompt_tokens=body.get("truncate_prompt_tokens"),
         cache_salt=body.get("cache_salt"),
+        context_shift=bool(body.get("context_shift", False)),
+        num_keep=max(0, int(body.get("num_keep", 1))),
     )
     if p.max_tokens is not None:
         p.max_tokens = int(p.max_tokens)
@@ -223,6 +225,9 @@ def params_from_ollama(options: dict, body: dict, llm: LLM) -> GenerationParams:
         repeat_penalty=float(o.get("repeat_penalty", 1.0)), repeat_last_n=int(o.get("repeat_last_n", 64)),
         max_tokens=int(num_predict) if num_predict is not None and int(num_predict) > 0 else None,
         seed=o.get("seed"), stop=_stops(o.get("stop")),
+        # a generation that reaches the window slides it (the first num_keep tokens and the newer half stay)
+        # unless `shift` is false; an unbounded num_predict is what makes that matter
+        context_shift=bool(o.get("shift", True)), num_keep=max(0, int(o.get("num_keep", 1))),
     )
     fmt = body.get("format")
     if fmt == "json":

@@ -89,6 +89,11 @@ int lk_rope_kv(const void* qkv, long long ld, const int* pos, const int* slots, 
                const float* q_norm_w, const float* k_norm_w, float eps, const float* inv_freq, int rope_dim,
                int pairing, float mscale, void* q_out, void* k_cache, void* v_cache, void* k_scale, void* v_scale,
                long long num_slots, int kv_q8, int* status, void* stream);
+// Context shift: cache positions move from `src` to `dst` slots (no overlap); key i is turned by delta[i]
+// positions on the way, values are copied.
+int lk_kv_shift(void* k_cache, void* v_cache, void* k_scale, void* v_scale, const int* src, const int* dst,
+                const int* delta, int n, int n_kv, int hd, const float* inv_freq, int rope_dim, int pairing,
+                long long num_slots, int kv_q8, int* status, void* stream);
 int lk_kv_gather(const void* k_cache, const void* v_cache, const void* k_scale, const void* v_scale, int kv_q8,
                  int n_kv, int hd, const int* block_table, int max_blocks, int block_size, const int* seq_of_tile,
                  const int* tile_tok0, int n_tiles, const int* kv_len, const int* dst_off, void* k_out,

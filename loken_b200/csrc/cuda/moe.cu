@@ -120,6 +120,10 @@ moe_route_kernel(const float* __restrict__ logits, long long ld, int T, int E, i
 // stays in L2), then the top-k of `route_warp`.  For the decode-size steps of a mixture layer this
 // replaces a GEMM launch whose single output tile cannot occupy the chip, plus the routing launch.
 constexpr int RT_WARPS = 8;
+constexpr int RT_EG = 4;       // experts a warp works on at once: four independent load streams per lane
+// TT tokens per CTA share every load of the router matrix (L2 traffic and time per token fall with TT;
+// the number of CTAs falls too, so small steps use TT = 1).
+template <int TT>
 __global__ void __launch_bounds__(RT_WARPS * 32)
 moe_router_kernel(const __nv_bfloat16* __restrict__ h, long long ldh, const __nv_bfloat16* __restrict__ w,
                   const float* __restrict__ bias, int T, int H, int E, int k, int mode, int renorm,
@@ -127,44 +131,75 @@ moe_router_kernel(const __nv_bfloat16* __restrict__ h, long long ldh, const __nv
   pdl_wait();
   pdl_launch();
   extern __shared__ __align__(16) uint8_t rt_smem[];
-  __nv_bfloat16* hs = reinterpret_cast<__nv_bfloat16*>(rt_smem);            // [H]
-  float* sc = reinterpret_cast<float*>(rt_smem + (((size_t)H * 2 + 15) & ~size_t(15)));   // [MAX_E]
-  const int t = blockIdx.x;
+  const size_t row_bytes = ((size_t)H * 2 + 15) & ~size_t(15);
+  float* sc = reinterpret_cast<float*>(rt_smem + TT * row_bytes);           // [TT][MAX_E]
+  const int t0 = blockIdx.x * TT;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nchunk = H >> 3;
-  for (int c = threadIdx.x; c < nchunk; c += RT_WARPS * 32)
-    reinterpret_cast<uint4*>(hs)[c] = *reinterpret_cast<const uint4*>(h + (long long)t * ldh + c * 8);
-  __syncthreads();
-  for (int e = warp; e < E; e += RT_WARPS) {
-    const __nv_bfloat16* wr = w + (long long)e * H;
-    float acc = 0.f;
-    for (int c = lane; c < nchunk; c += 32) {
-      const uint4 a = __ldg(reinterpret_cast<const uint4*>(wr) + c);
-      const uint4 b = reinterpret_cast<const uint4*>(hs)[c];
-      const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
-      const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const float2 x = __bfloat1622float2(a2[q]), y = __bfloat1622float2(b2[q]);
-        acc = fmaf(x.x, y.x, acc);
-        acc = fmaf(x.y, y.y, acc);
+  for (int tt = 0; tt < TT; ++tt) {
+    uint4* hs = reinterpret_cast<uint4*>(rt_smem + tt * row_bytes);
+    const int t = min(t0 + tt, T - 1);
+    for (int c = threadIdx.x; c < nchunk; c += RT_WARPS * 32)
+      hs[c] = *reinterpret_cast<const uint4*>(h + (long long)t * ldh + c * 8);
+  }
+  __syncthreads();
+  for (int e0 = warp * RT_EG; e0 < E; e0 += RT_WARPS * RT_EG) {
+    float acc[RT_EG][TT];
+#pragma unroll
+    for (int g = 0; g < RT_EG; ++g)
+#pragma unroll
+      for (int tt = 0; tt < TT; ++tt) acc[g][tt] = 0.f;
+    const uint4* wr[RT_EG];
+#pragma unroll
+    for (int g = 0; g < RT_EG; ++g) wr[g] = reinterpret_cast<const uint4*>(w + (long long)min(e0 + g, E - 1) * H);
+#pragma unroll 2
+    for (int c = lane; c < nchunk; c += 32) {
+      uint4 a[RT_EG];
+#pragma unroll
+      for (int g = 0; g < RT_EG; ++g) a[g] = __ldg(wr[g] + c);
+#pragma unroll
+      for (int tt = 0; tt < TT; ++tt) {
+        const uint4 b = reinterpret_cast<const uint4*>(rt_smem + tt * row_bytes)[c];
+        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
+        float2 y[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) y[q] = __bfloat1622float2(b2[q]);
+#pragma unroll
+        for (int g = 0; g < RT_EG; ++g) {
+          const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a[g]);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 x = __bfloat1622float2(a2[q]);
+            acc[g][tt] = fmaf(x.x, y[q].x, acc[g][tt]);
+            acc[g][tt] = fmaf(x.y, y[q].y, acc[g][tt]);
+          }
+        }
       }
     }
-    acc = warp_sum(acc);
-    if (lane == 0) sc[e] = acc + (bias ? bias[e] : 0.f);
+#pragma unroll
+    for (int g = 0; g < RT_EG; ++g)
+#pragma unroll
+      for (int tt = 0; tt < TT; ++tt) {
+        const float v = warp_sum(acc[g][tt]);
+        if (lane == 0 && e0 + g < E) sc[tt * MAX_E + e0 + g] = v + (bias ? bias[e0 + g] : 0.f);
+      }
   }
   __syncthreads();
   if (logits_out)
-    for (int e = threadIdx.x; e < E; e += RT_WARPS * 32) logits_out[(long long)t * ldl + e] = sc[e];
-  if (warp == 0) {
+    for (int i = threadIdx.x; i < TT * E; i += RT_WARPS * 32) {
+      const int tt = i / E, e = i % E;
+      if (t0 + tt < T) logits_out[(long long)(t0 + tt) * ldl + e] = sc[tt * MAX_E + e];
+    }
+  if (warp < TT && t0 + warp < T) {
     constexpr int PER = MAX_E / 32;
     float v[PER];
 #pragma unroll
     for (int j = 0; j < PER; ++j) {
       const int e = j * 32 + lane;
-      v[j] = e < E ? sc[e] : -INFINITY;
+      v[j] = e < E ? sc[warp * MAX_E + e] : -INFINITY;
     }
-    route_warp(v, lane, E, k, mode, renorm, ids + (long long)t * k, wts + (long long)t * k);
+    route_warp(v, lane, E, k, mode, renorm, ids + (long long)(t0 + warp) * k, wts + (long long)(t0 + warp) * k);
   }
 }
 
@@ -290,11 +325,20 @@ LK_API int lk_moe_router(const void* h, long long ldh, const void* w, const floa
                          int mode, int renorm, int* ids, float* wts, float* logits_out, long long ldl, void* stream) {
   if (T <= 0) return LKH_OK;
   if (E > MAX_E || k > MAX_K || k > E || k < 1 || (H & 7) || (ldh & 7)) return LKH_BAD_ARG;
-  const size_t smem = (((size_t)H * 2 + 15) & ~size_t(15)) + MAX_E * sizeof(float);
+  const size_t row = ((size_t)H * 2 + 15) & ~size_t(15);
+  // tokens per CTA: more of them share each load of the router matrix, fewer CTAs result
+  int tt = T <= 32 ? 1 : T <= 256 ? 2 : 4;
+  while (tt > 1 && tt * (row + MAX_E * sizeof(float)) > 48 * 1024) tt >>= 1;
+  const size_t smem = tt * (row + MAX_E * sizeof(float));
   if (smem > 48 * 1024) return LKH_TOO_LARGE;
-  lkh::launch_pdl(moe_router_kernel, dim3(T), dim3(RT_WARPS * 32), smem, (cudaStream_t)stream,
-                  (const __nv_bfloat16*)h, ldh, (const __nv_bfloat16*)w, bias, T, H, E, k, mode, renorm, ids, wts,
-                  logits_out, ldl);
+  const dim3 grid((T + tt - 1) / tt), block(RT_WARPS * 32);
+#define LK_ROUTER(TT)                                                                                              \
+  lkh::launch_pdl(moe_router_kernel<TT>, grid, block, smem, (cudaStream_t)stream, (const __nv_bfloat16*)h, ldh,    \
+                  (const __nv_bfloat16*)w, bias, T, H, E, k, mode, renorm, ids, wts, logits_out, ldl)
+  if (tt == 4) LK_ROUTER(4);
+  else if (tt == 2) LK_ROUTER(2);
+  else LK_ROUTER(1);
+#undef LK_ROUTER
   lkh::count_launch();
   return lkh::launch_status();
 }

@@ -202,7 +202,124 @@ kv_gather_kernel(const void* __restrict__ k_cache, const void* __restrict__ v_ca
   }
 }
 
+// Context shift: the keys and values of n cache positions move from `src` slots to `dst` slots, and
+// every key is turned by `delta[i]` positions on the way (negative when the window slides down after
+// older tokens were discarded; zero for positions that only move).  A stored key already carries its
+// rotation and the attention factor, so a pure rotation by delta * inv_freq re-phases it: dequantise
+// the row, rotate its pairs, requantise with a fresh step.  Values are copied as stored.  One warp per
+// (position, kv head).  src and dst must not overlap (the caller writes into fresh blocks).
+template <int HD>
+__global__ void __launch_bounds__(128)
+kv_shift_kernel(void* __restrict__ k_cache, void* __restrict__ v_cache, __half* __restrict__ k_scale,
+                __half* __restrict__ v_scale, const int* __restrict__ src, const int* __restrict__ dst,
+                const int* __restrict__ delta, int n, int n_kv, const float* __restrict__ inv_freq, int rope_dim,
+                int pairing, long long num_slots, int kv_q8, int* __restrict__ status) {
+  constexpr int EPL = HD / 32;
+  __shared__ float sh[4][HD];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long unit = (long long)blockIdx.x * 4 + warp;
+  if (unit >= (long long)n * n_kv) return;
+  const int t = (int)(unit / n_kv), h = (int)(unit % n_kv);
+  const long long so = src[t], dn = dst[t];
+  if (so < 0 || dn < 0 || so >= num_slots || dn >= num_slots) {
+    if (status && lane == 0) atomicCAS(status, 0, LK_ERR_BOUNDS | (2 << 8));
+    return;
+  }
+  const long long srow = (so * n_kv + h) * HD + lane * EPL, drow = (dn * n_kv + h) * HD + lane * EPL;
+  constexpr int LPB = 32 / EPL;      // lanes per 32-value block
+  float v[EPL];
+  if (kv_q8) {
+    const float d = __half2float(k_scale[(so * n_kv + h) * (HD / 32) + lane / LPB]);
+    const int8_t* c = reinterpret_cast<const int8_t*>(k_cache) + srow;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) v[e] = (float)c[e] * d;
+  } else {
+    const __nv_bfloat16* c = reinterpret_cast<const __nv_bfloat16*>(k_cache) + srow;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) v[e] = bf2f(c[e]);
+  }
+  const float p = (float)delta[t];
+  if (p != 0.f) {
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) sh[warp][lane * EPL + e] = v[e];
+    __syncwarp();
+    const int half = rope_dim >> 1;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+      const int dd = lane * EPL + e;
+      if (dd < rope_dim) {
+        int fi, partner;
+        bool first;
+        if (pairing == 0) {
+          fi = dd >> 1;
+          partner = dd ^ 1;
+          first = (dd & 1) == 0;
+        } else {
+          first = dd < half;
+          fi = first ? dd : dd - half;
+          partner = first ? dd + half : dd - half;
+        }
+        float sn, cs;
+        sincosf(p * inv_freq[fi], &sn, &cs);
+        const float a = sh[warp][dd], b = sh[warp][partner];
+        v[e] = first ? (a * cs - b * sn) : (a * cs + b * sn);
+      }
+    }
+  }
+  if (kv_q8) {
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) v[e] = bf2f(f2bf(v[e]));
+    float amax = 0.f;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) amax = fmaxf(amax, fabsf(v[e]));
+#pragma unroll
+    for (int o = LPB / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const __half dh = __float2half(amax * (1.f / 127.f));
+    const float d = __half2float(dh);
+    const float id = d > 0.f ? 1.f / d : 0.f;
+    int8_t* c = reinterpret_cast<int8_t*>(k_cache) + drow;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) c[e] = (int8_t)__float2int_rn(v[e] * id);
+    if ((lane % LPB) == 0) k_scale[(dn * n_kv + h) * (HD / 32) + lane / LPB] = dh;
+    // values: codes and steps as they are
+    const int8_t* vs = reinterpret_cast<const int8_t*>(v_cache) + srow;
+    int8_t* vd = reinterpret_cast<int8_t*>(v_cache) + drow;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) vd[e] = vs[e];
+    if ((lane % LPB) == 0)
+      v_scale[(dn * n_kv + h) * (HD / 32) + lane / LPB] = v_scale[(so * n_kv + h) * (HD / 32) + lane / LPB];
+  } else {
+    __nv_bfloat16* c = reinterpret_cast<__nv_bfloat16*>(k_cache) + drow;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) c[e] = f2bf(v[e]);
+    const __nv_bfloat16* vs = reinterpret_cast<const __nv_bfloat16*>(v_cache) + srow;
+    __nv_bfloat16* vd = reinterpret_cast<__nv_bfloat16*>(v_cache) + drow;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) vd[e] = vs[e];
+  }
+}
+
 }  // namespace
+
+LK_API int lk_kv_shift(void* k_cache, void* v_cache, void* k_scale, void* v_scale, const int* src, const int* dst,
+                       const int* delta, int n, int n_kv, int hd, const float* inv_freq, int rope_dim, int pairing,
+                       long long num_slots, int kv_q8, int* status, void* stream) {
+  if (n <= 0) return LKH_OK;
+  if (!k_cache || !v_cache || !src || !dst || !delta || !inv_freq || (kv_q8 && (!k_scale || !v_scale))) return LKH_BAD_ARG;
+  const long long units = (long long)n * n_kv;
+  const unsigned grid = (unsigned)((units + 3) / 4);
+  cudaStream_t st = (cudaStream_t)stream;
+#define LK_SHIFT(HD)                                                                                          \
+  kv_shift_kernel<HD><<<grid, 128, 0, st>>>(k_cache, v_cache, (__half*)k_scale, (__half*)v_scale, src, dst, delta, \
+                                            n, n_kv, inv_freq, rope_dim, pairing, num_slots, kv_q8, status)
+  if (hd == 128) LK_SHIFT(128);
+  else if (hd == 64) LK_SHIFT(64);
+  else if (hd == 256) LK_SHIFT(256);
+  else return LKH_BAD_ARG;
+#undef LK_SHIFT
+  lkh::count_launch();
+  return lkh::launch_status();
+}
 
 LK_API int lk_rope_kv(const void* qkv, long long ld, const int* pos, const int* slots, int T, int n_q, int n_kv,
                       int hd, const float* q_norm_w, const float* k_norm_w, float eps, const float* inv_freq,

@@ -98,6 +98,18 @@ class KVCacheLayer:
         return self.k.float() * ks, self.v.float() * vs
 
 
+def kv_shift(cache: KVCacheLayer, src: torch.Tensor, dst: torch.Tensor, delta: torch.Tensor, inv_freq: torch.Tensor, *,
+             rope_dim: Optional[int] = None, pairing: int = 1):
+    """Context shift on one layer's cache: position i moves from slot src[i] to slot dst[i] (int32, no
+    overlap between the two sets) and its key is turned by delta[i] positions; values are copied."""
+    n = src.numel()
+    wsp = Workspace.get(cache.k.device)
+    check(cuda_lib().lk_kv_shift(ptr(cache.k), ptr(cache.v), ptr(cache.k_scale), ptr(cache.v_scale), ptr(src), ptr(dst),
+                                 ptr(delta), n, cache.n_kv, cache.hd, ptr(inv_freq),
+                                 rope_dim if rope_dim is not None else cache.hd, pairing,
+                                 C.c_longlong(cache.num_slots), int(cache.q8), ptr(wsp.status), stream()), "lk_kv_shift")
+
+
 def rope_kv(qkv: torch.Tensor, pos: torch.Tensor, slots: torch.Tensor, cache: KVCacheLayer, n_q: int,
             inv_freq: torch.Tensor, *, rope_dim: Optional[int] = None, pairing: int = 1, mscale: float = 1.0,
             q_norm_w: Optional[torch.Tensor] = None, k_norm_w: Optional[torch.Tensor] = None, eps: float = 1e-6,

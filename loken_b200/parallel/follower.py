@@ -42,7 +42,8 @@ READ_ONLY = frozenset({
     "cancelled", "has_work", "grammar_factory", "next_id",
 })
 # engine methods that every rank has to execute at the same point between two steps
-MIRRORED = frozenset({"embed", "layer_perf", "import_prefix", "reset_prefix_cache", "detach_speculator"})
+MIRRORED = frozenset({"embed", "layer_perf", "import_prefix", "reset_prefix_cache", "detach_speculator",
+                      "context_shift"})
 
 
 class RankLeft(RuntimeError):

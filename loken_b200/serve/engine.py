@@ -59,6 +59,7 @@ class EngineStats:
     preemptions: int = 0
     step_errors: int = 0
     consecutive_errors: int = 0
+    context_shifts: int = 0
 
 
 def kv_bytes_per_token(cfg: ModelConfig, n_kv_local: int) -> int:
@@ -236,9 +237,46 @@ class LLMEngine:
             return "stop"
         if p.max_tokens is not None and n_out >= p.max_tokens:
             return "length"
-        if seq.total_len >= self.max_ctx:
+        if seq.total_len >= self.max_ctx and not self._can_shift(seq):
             return "length"
         return None
+
+    # ---- context shift ----
+    def _can_shift(self, seq: Sequence) -> bool:
+        cfg = self.cfg
+        return bool(seq.params.context_shift and seq.prompt_embeds is None and self.spec is None
+                    and getattr(self.runner, "pipeline", None) is None and not cfg.sliding_window)
+
+    def context_shift(self, seq_id: int, n_keep: Optional[int] = None, n_discard: Optional[int] = None) -> int:
+        """Makes room in a running sequence's window: cache positions [n_keep, n_keep + n_discard) are
+        dropped, the later ones move down and their keys are turned back by n_discard positions (the
+        rotary phase comes from the layer's own frequency table, so scaled and factored frequencies need
+        nothing special).  Defaults: keep `params.num_keep` tokens, drop the older half of the rest.
+        Returns the number of positions dropped (0 when the pool has no room for the copy).  A re-phased
+        key is not bit for bit the key a fresh prefill of the shorter text would produce.  Sliding-window
+        layers, prompts given as embeddings, pipelines and speculative decoding do not shift
+        (the reference lists the same exclusions, `docs/STATUS.md:111-123`)."""
+        seq = self.seqs[seq_id]
+        if seq.state != "running" or seq.computed < seq.total_len - 1:
+            raise ValueError("only a sequence that is decoding can shift its context")
+        if self.cfg.sliding_window or seq.prompt_embeds is not None:
+            raise ValueError("this sequence's cache cannot be shifted")
+        have = seq.computed                                   # cache positions that hold K/V
+        n_keep = max(0, min(seq.params.num_keep if n_keep is None else n_keep, have - 2))
+        if n_discard is None:
+            n_discard = (have - n_keep) // 2
+        n_discard = min(n_discard, have - n_keep - 1)
+        if n_discard <= 0:
+            return 0
+        self.alloc.trim(seq_id, have)                         # lookahead slots go back first
+        moved = self.alloc.shift(seq_id, n_keep, n_discard)
+        if moved is None:
+            return 0
+        self.runner.kv_shift(*moved)
+        seq.drop_positions(n_keep, n_discard)
+        seq.computed = have - n_discard
+        self.stats.context_shifts += 1
+        return n_discard
 
     def _emit(self, seq: Sequence, tok: int, outs: Dict[int, StepOutput], lp: Optional[tuple] = None):
         if seq.first_token_time is None:
@@ -272,6 +310,13 @@ class LLMEngine:
                 self.sched.finish(seq, "cancelled")
                 outs[sid] = StepOutput(sid, [], True, "cancelled")
         self.cancelled.clear()
+        for seq in list(self.sched.running):
+            # a generation at the end of its window slides it before the scheduler asks for the next slot
+            if seq.state == "running" and seq.total_len + 1 + self.sched.lookahead > self.max_ctx \
+                    and seq.computed >= seq.total_len - 1 and self._can_shift(seq):
+                if self.context_shift(seq.seq_id) == 0:
+                    self.sched.finish(seq, "length")
+                    outs[seq.seq_id] = StepOutput(seq.seq_id, [], True, "length")
         with nvtx.span("schedule"):
             plan = self.sched.schedule()
         self.stats.preemptions += len(plan.preempted)

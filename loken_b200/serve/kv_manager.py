@@ -47,6 +47,7 @@ class _Seq:
     blocks: List[int] = field(default_factory=list)
     length: int = 0                 # tokens whose KV the sequence owns
     hashes: List[int] = field(default_factory=list)   # hash of each committed (cached) leading block
+    publish_limit: Optional[int] = None   # after a context shift: only blocks below this index may be published
 
 
 class PagedKvAllocator:
@@ -170,7 +171,8 @@ class PagedKvAllocator:
             return
         s = self.seqs[seq_id]
         hs = block_hashes(tokens[:s.length], self.block_size, salt)
-        for i in range(len(s.hashes), min(len(hs), len(s.blocks))):
+        top = min(len(hs), len(s.blocks)) if s.publish_limit is None else min(len(hs), len(s.blocks), s.publish_limit)
+        for i in range(len(s.hashes), top):
             h, b = hs[i], s.blocks[i]
             if h in self.cached and self.cached[h] != b:
                 pass    # an equal block is already published; keep ours private
@@ -187,6 +189,45 @@ class PagedKvAllocator:
             self._release(s.blocks.pop())
         s.hashes = s.hashes[:min(len(s.hashes), new_len // self.block_size)]
         s.length = new_len
+
+    def shift(self, seq_id: int, n_keep: int, n_discard: int):
+        """Context shift: positions [n_keep, n_keep + n_discard) leave the sequence and everything after
+        them moves down by n_discard.  Whole blocks inside the kept head stay as they are (they may be
+        shared); the rest of the sequence moves into fresh blocks, so nothing shared is written and the
+        copy never overlaps its source.  Returns (src slots, dst slots, deltas) for the positions that
+        move, new position order, or None when the pool has no room for the copy.  The old blocks are
+        released here: the caller enqueues the copy on the stream before anything else can reuse them.
+        Blocks past the kept head are never published: their keys were computed in a context that no
+        longer exists."""
+        s = self.seqs[seq_id]
+        bs = self.block_size
+        L = s.length
+        assert 0 <= n_keep and n_discard > 0 and n_keep + n_discard <= L
+        new_len = L - n_discard
+        kb = n_keep // bs
+        need = self.blocks_needed(new_len) - kb
+        if need > self.free_blocks():
+            return None
+        old = s.blocks
+        fresh = []
+        for _ in range(need):
+            b = self._take()
+            self.ref[b] = 1
+            fresh.append(b)
+        new = old[:kb] + fresh
+        src, dst, delta = [], [], []
+        for p in range(kb * bs, new_len):
+            q = p if p < n_keep else p + n_discard
+            src.append(old[q // bs] * bs + q % bs)
+            dst.append(new[p // bs] * bs + p % bs)
+            delta.append(0 if p < n_keep else -n_discard)
+        for b in reversed(old[kb:]):
+            self._release(b)
+        s.blocks = new
+        s.length = new_len
+        s.hashes = s.hashes[:min(len(s.hashes), kb)]
+        s.publish_limit = kb
+        return src, dst, delta
 
     def free(self, seq_id: int):
         s = self.seqs.pop(seq_id, None)

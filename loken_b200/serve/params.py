@@ -47,6 +47,10 @@ class SamplingParams:
     min_tokens: int = 0
     n: int = 1
     grammar: Optional[tuple] = None      # (kind, source): json_schema | regex | lark | choice
+    # a generation that reaches the window keeps its first `num_keep` tokens and the newer half of the rest
+    # (the cache is shifted and its keys re-phased) instead of ending with "length"
+    context_shift: bool = False
+    num_keep: int = 1
 
     @property
     def greedy(self) -> bool:

@@ -457,6 +457,20 @@ class ModelRunner:
         out = self.h_sampled[:n_l].tolist()
         return {s.seq_id: t for s, t in zip(done, out)}
 
+    def kv_shift(self, src: Seq[int], dst: Seq[int], delta: Seq[int]):
+        """Moves cache positions `src` -> `dst` on every layer this rank holds, turning key i by delta[i]
+        positions (`ops/rows.py:kv_shift`)."""
+        from ..ops import rows
+
+        dev = self.device
+        t = torch.tensor([list(src), list(dst), list(delta)], dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
+        m = self.model
+        for cache in m.kv:
+            if cache is not None:
+                rows.kv_shift(cache, t[0], t[1], t[2], m.w.inv_freq, rope_dim=self.cfg.rope_dim or self.cfg.head_dim,
+                              pairing=self.cfg.rope_pairing)
+        self.h2d_bytes += 12 * len(src)
+
     def layer_perf(self, alloc, n_tokens: int = 1):
         sid = -1 - len(alloc.seqs)
         n = max(1, min(n_tokens, self.max_seqs))

@@ -45,14 +45,30 @@ class Sequence:
     logprobs: List[tuple] = field(default_factory=list)   # per output token: (logprob, [(id, logprob)...])
     grammar: Optional[object] = None     # a text.grammar.GrammarSession while the request is constrained
     prompt_embeds: Optional[object] = None   # bf16 [len(prompt), hidden] on the device: the prompt as embedding rows
+    # after a context shift: the tokens the cache still stands for, as of `kv_out0` output tokens (`prompt` and
+    # `output` stay whole: they are what the client sent and what it was sent)
+    kv_head: Optional[List[int]] = None
+    kv_out0: int = 0
+    shifts: int = 0
 
     @property
     def tokens(self) -> List[int]:
-        return self.prompt + self.output
+        """Token i is the token at cache position i."""
+        if self.kv_head is None:
+            return self.prompt + self.output
+        return self.kv_head + self.output[self.kv_out0:]
 
     @property
     def total_len(self) -> int:
-        return len(self.prompt) + len(self.output)
+        if self.kv_head is None:
+            return len(self.prompt) + len(self.output)
+        return len(self.kv_head) + len(self.output) - self.kv_out0
+
+    def drop_positions(self, n_keep: int, n_discard: int):
+        toks = self.tokens
+        self.kv_head = toks[:n_keep] + toks[n_keep + n_discard:]
+        self.kv_out0 = len(self.output)
+        self.shifts += 1
 
 
 @dataclass
