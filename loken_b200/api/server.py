@@ -221,6 +221,144 @@ def ops_router(ctx: ServerContext):
         ctx.registry.add(llm, default=bool(body.get("default")))
         return {"status": "loaded", "model": llm.info(), "evicted": evicted}
 
+    def _calibration_dir() -> str:
+        import os as _os
+
+        cat = getattr(ctx, "catalogue", None)
+        base = cat.ollama.dirs[0] if cat is not None and cat.ollama.dirs else _os.path.expanduser("~/.loken")
+        return _os.path.join(base, "calibrations")
+
+    def _ndjson_job(job, stream: bool):
+        """Runs `job(emit)` in a worker thread; with `stream` every emitted dict is one NDJSON line as it
+        happens, otherwise the last one is the JSON reply.  A failure is the last line, with `error`."""
+        import json as _json
+        import queue
+        import threading
+
+        from starlette.concurrency import iterate_in_threadpool
+        from starlette.responses import JSONResponse, StreamingResponse
+
+        q: "queue.Queue" = queue.Queue()
+
+        def run():
+            try:
+                job(q.put)
+            except Exception as e:              # the reason travels to the client, not to a log
+                q.put({"error": f"{type(e).__name__}: {e}"})
+            q.put(None)
+
+        threading.Thread(target=run, daemon=True).start()
+
+        def lines():
+            while True:
+                ev = q.get()
+                if ev is None:
+                    return
+                yield ev
+
+        if stream:
+            return StreamingResponse(iterate_in_threadpool((_json.dumps(ev) + "\n").encode() for ev in lines()),
+                                     media_type="application/x-ndjson")
+        last = {}
+        for ev in lines():
+            last = ev
+        return JSONResponse(last, status_code=400 if "error" in last else 200)
+
+    @r.post("/api/calibrate")
+    async def calibrate(req: Request):
+        """Records what the matrices of a checkpoint see on the given `texts` as the calibration `name`:
+        per tensor, the mean square of the activations it multiplies and of its own values (the fp32
+        forward of `models/reference.py`).  `model` is a path or a store name; `tokens` bounds the pass
+        (default 4096), `excerpt` the characters taken from each text."""
+        from starlette.concurrency import run_in_threadpool
+
+        body = await req.json()
+        name, model, texts = body.get("name"), body.get("model"), body.get("texts") or []
+        if not name or not model or not texts or not all(isinstance(t, str) for t in texts):
+            raise ApiError(400, "name, model and texts (a list of strings) are required")
+        if "/" in name or name.startswith("."):
+            raise ApiError(400, "a calibration name is a plain file name")
+        cat = getattr(ctx, "catalogue", None)
+        entry = cat.resolve(model) if cat is not None else None
+        path = entry.path if entry is not None else model
+        excerpt, budget = int(body.get("excerpt") or 4000), int(body.get("tokens") or 4096)
+
+        def job(emit):
+            import os as _os
+
+            import torch as _torch
+
+            from ..formats.requant import calibrate as _cal, write_calibration
+            from ..models.loader import load_gguf
+            from ..text.tokenizer import from_gguf_meta
+
+            emit({"status": "loading"})
+            w, meta = load_gguf(path, _torch.device("cuda" if _torch.cuda.is_available() else "cpu"), requant="bf16")
+            tk = from_gguf_meta(meta)
+            lists = [tk.encode(t[:excerpt], True) for t in texts]
+            emit({"status": "recording", "texts": len(lists), "tokens": min(budget, sum(len(x) for x in lists))})
+            stats = _cal(w, lists, max_tokens=budget)
+            out = _os.path.join(_calibration_dir(), name + ".json")
+            rec = write_calibration(out, name, model, stats, len(lists), min(budget, sum(len(x) for x in lists)))
+            emit({"status": "success", "calibration": name, "path": out, "tensors": len(rec["stats"])})
+
+        return await run_in_threadpool(_ndjson_job, job, body.get("stream", True) is not False)
+
+    @r.post("/api/convert")
+    async def convert(req: Request):
+        """Converts a checkpoint (`model`: a GGUF path or a store name) into the model `name` (`name:tag`) of
+        the first Ollama store, re-encoded as `format` (q8_0, q4_k_m, q4_k, q6_k, mxfp4, bf16, f16); a
+        `calibration` recorded by /api/calibrate lifts the most sensitive tensors one step.  `complete`
+        finishes a conversion whose file was written but never registered."""
+        import os as _os
+
+        from starlette.concurrency import run_in_threadpool
+
+        body = await req.json()
+        name, model, fmt = body.get("name"), body.get("model"), (body.get("format") or "q4_k_m").lower()
+        cat = getattr(ctx, "catalogue", None)
+        if not name or (not model and not body.get("complete")):
+            raise ApiError(400, "name (the model to create) and model (the checkpoint to convert) are required")
+        if cat is None or not cat.ollama.dirs:
+            raise ApiError(400, "no ollama_models_dir is configured to hold the converted model")
+        from ..formats.requant import FORMATS
+
+        if fmt not in FORMATS:
+            raise ApiError(400, f"format must be one of {', '.join(FORMATS)}")
+        work = _os.path.join(cat.ollama.dirs[0], "conversions")
+        out = _os.path.join(work, name.replace("/", "_").replace(":", "_") + f".{fmt}.gguf")
+        cal = body.get("calibration")
+        cal_path = _os.path.join(_calibration_dir(), cal + ".json") if cal else None
+        if cal_path and not _os.path.exists(cal_path):
+            raise ApiError(404, f"no calibration named {cal}")
+        entry = cat.resolve(model) if model else None
+        src = entry.path if entry is not None else model
+
+        def job(emit):
+            from ..formats.requant import requantize_gguf
+
+            _os.makedirs(work, exist_ok=True)
+            if not (body.get("complete") and _os.path.exists(out)):
+                if not src or not _os.path.isfile(src):
+                    raise FileNotFoundError(f"{model}: not a GGUF file or a store name that resolves to one")
+                emit({"status": "converting", "format": fmt})
+                state = {"last": 0}
+
+                def progress(tensor, done, total):
+                    if done == total or done - state["last"] >= max(1, total // 50):
+                        state["last"] = done
+                        emit({"status": "converting", "completed": done, "total": total})
+
+                rep = requantize_gguf(src, out, fmt, calibration=cal_path, progress=progress)
+            else:
+                rep = {"output": out, "format": fmt, "resumed": True}
+            emit({"status": "registering"})
+            e = cat.ollama.create(name, out)
+            _os.remove(out)                       # the store holds the blob (hard link or copy)
+            emit(dict(rep, status="success", model=e.name, size=e.size))
+
+        return await run_in_threadpool(_ndjson_job, job, body.get("stream", True) is not False)
+
     @r.post("/api/swap")
     async def swap(req: Request):
         """Replace the resident model: the named one (or every resident language model when none is

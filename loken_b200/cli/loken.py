@@ -6,6 +6,7 @@
     loken load PATH [--id NAME]           ask the server to load a model
     loken delete MODEL                    unload it
     loken validate FILE.gguf              check a GGUF file: header, tensor table, payload sizes
+    loken convert --from in.gguf --format q4_k_m -o out.gguf [--calibration rec.json]     re-encode a model
     loken convert --shape NAME --format q8_0 -o out.gguf     write a random-init model file
     loken draft attach|detach|status
     loken pull NAME                       fetch a model into the daemon's stores (streams progress; resumable)
@@ -116,8 +117,10 @@ def build_parser() -> argparse.ArgumentParser:
     sub.add_parser("validate").add_argument("file")
     sub.add_parser("repair").add_argument("file")
     cv = sub.add_parser("convert")
-    cv.add_argument("--shape", required=True, help="built-in shape name, e.g. qwen3-1.7b")
-    cv.add_argument("--format", default="q8_0", choices=["q8_0", "q4_k_m", "q4_k", "q6_k", "bf16", "mxfp4"])
+    cv.add_argument("--shape", help="built-in shape name, e.g. qwen3-1.7b: write a random-init model file")
+    cv.add_argument("--from", dest="source", help="a GGUF file to re-encode in --format")
+    cv.add_argument("--calibration", help="a calibration record (JSON) that lifts the most sensitive tensors one step")
+    cv.add_argument("--format", default="q8_0", choices=["q8_0", "q4_k_m", "q4_k", "q6_k", "bf16", "f16", "mxfp4"])
     cv.add_argument("--layers", type=int, help="write only the first N layers")
     cv.add_argument("-o", "--output", required=True)
     cv.add_argument("--seed", type=int, default=0)
@@ -197,6 +200,15 @@ def main(argv=None, out=sys.stdout) -> int:
         from ..models.config import get_config
         from ..models.loader import export_random_gguf
 
+        if args.source:
+            from ..formats.requant import requantize_gguf
+
+            rep = requantize_gguf(args.source, args.output, args.format, calibration=args.calibration)
+            p(json.dumps(rep, indent=1))
+            return 0
+        if not args.shape:
+            p("loken convert: give --from FILE.gguf (re-encode a model) or --shape NAME (write a random-init one)")
+            return 2
         cfg = dataclasses.replace(get_config(args.shape), weight_format=args.format)
         if args.layers:
             cfg = dataclasses.replace(cfg, n_layers=args.layers)

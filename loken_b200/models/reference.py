@@ -89,9 +89,11 @@ def moe_ref(x: torch.Tensor, moe, cfg: ModelConfig) -> torch.Tensor:
 
 
 @torch.no_grad()
-def forward_ref(w: ModelWeights, tokens: Sequence[int], *, bf16_stream: bool = True) -> torch.Tensor:
+def forward_ref(w: ModelWeights, tokens: Sequence[int], *, bf16_stream: bool = True, probe=None) -> torch.Tensor:
     """Full causal forward over `tokens`; returns fp32 logits [T, vocab] (single rank only).
-    With `bf16_stream` the residual stream is rounded to bf16 where the kernels round it."""
+    With `bf16_stream` the residual stream is rounded to bf16 where the kernels round it.
+    `probe(layer, role, x)` is called with the input rows of every dense linear layer (roles qkv, o,
+    gate_up, down): what a calibration pass records."""
     cfg = w.cfg
     assert w.tp_size == 1
     dev = w.embed.device
@@ -104,6 +106,8 @@ def forward_ref(w: ModelWeights, tokens: Sequence[int], *, bf16_stream: bool = T
     rope_dim = cfg.rope_dim or hd
     for il, lw in enumerate(w.layers):
         h = rd(_rms(x, lw.attn_norm, cfg.rms_eps))
+        if probe is not None:
+            probe(il, "qkv", h)
         qkv = h @ dequant_linear(lw.wqkv).t()
         if lw.wqkv.bias is not None:
             qkv = qkv + lw.wqkv.bias
@@ -115,17 +119,23 @@ def forward_ref(w: ModelWeights, tokens: Sequence[int], *, bf16_stream: bool = T
         q = rd(_rope(q, pos, w.inv_freq, cfg.rope_pairing, rope_dim, w.rope_mscale))
         k = rd(_rope(k, pos, w.inv_freq, cfg.rope_pairing, rope_dim, w.rope_mscale))
         a = attention_ref(q, k, v, 0, scale=cfg.softmax_scale(), window=lw.window, sinks=lw.sinks)
+        if probe is not None:
+            probe(il, "o", rd(a))
         d = rd(a) @ dequant_linear(lw.wo).t()
         if lw.wo.bias is not None:
             d = d + lw.wo.bias
         x = rd(x + rd(d))
         h = rd(_rms(x, lw.ffn_norm, cfg.rms_eps))
+        if probe is not None:
+            probe(il, "gate_up", h)
         if cfg.is_moe:
             d = moe_ref(h, lw.moe, cfg)
         else:
             gu = rd(h @ dequant_linear(lw.w_gate_up).t())
             I = gu.shape[1] // 2
             act = rd(glu_ref(gu[:, :I], gu[:, I:], cfg))
+            if probe is not None:
+                probe(il, "down", act)
             d = act @ dequant_linear(lw.w_down).t()
         x = rd(x + rd(d))
     h = rd(_rms(x, w.out_norm, cfg.rms_eps))
