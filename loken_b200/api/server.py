@@ -359,6 +359,65 @@ def ops_router(ctx: ServerContext):
 
         return await run_in_threadpool(_ndjson_job, job, body.get("stream", True) is not False)
 
+    @r.post("/api/pipeline/tail")
+    async def pipeline_tail(req: Request):
+        """Runs this node as one segment of a pipeline across nodes: layers `from` .. `to` of `model`,
+        relaying to `next` ("host:port" of the following segment) unless this is the last one.  Answers
+        the wire port the upstream segment (or the head) connects to.  A head calls this, not an
+        operator.  A second call for the same model and range answers the segment that already runs."""
+        from starlette.concurrency import run_in_threadpool
+
+        body = await req.json()
+        model, lo, hi = body.get("model"), body.get("from"), body.get("to")
+        if not model or lo is None or hi is None or int(lo) < 0 or int(hi) <= int(lo):
+            raise ApiError(400, "model, from and to (a non-empty layer range) are required")
+        lo, hi = int(lo), int(hi)
+        key = (model, lo, hi, body.get("next"))
+        segs = ctx.__dict__.setdefault("segments", {})
+        if key in segs:
+            srv, run = segs[key]
+            return {"status": "running", "port": srv.addr[1], "host": srv.addr[0], **run.status()}
+
+        def start():
+            import torch as _torch
+
+            from ..cluster.pipeline import SegmentLink, SegmentServer
+            from ..cluster.segment import SegmentRunner
+            from ..models.loader import load_gguf, peek_config
+
+            cat = getattr(ctx, "catalogue", None)
+            entry = cat.resolve(model) if cat is not None else None
+            path = entry.path if entry is not None else model
+            shape = peek_config(path)
+            if hi > shape.n_layers:
+                raise ValueError(f"{model} has {shape.n_layers} layers; the range ends at {hi}")
+            last = hi == shape.n_layers and not body.get("next")
+            dev = _torch.device("cuda", _torch.cuda.current_device())
+            import os as _os
+
+            if _os.path.exists(path):
+                w, _meta = load_gguf(path, dev, layer_range=(lo, hi), kv_format=body.get("kv_format"))
+            else:
+                from ..models.weights import random_weights
+
+                w = random_weights(shape, dev, seed=int(body.get("seed", 0)), layer_range=(lo, hi))
+            run = SegmentRunner(w.cfg, w, lo, hi, last=last, device=dev, max_ctx=int(body.get("max_ctx", 8192)),
+                                max_requests=int(body.get("max_requests", 16)))
+            nxt = None
+            if body.get("next"):
+                h, _, pt = str(body["next"]).rpartition(":")
+                nxt = SegmentLink(h or "127.0.0.1", int(pt))
+            srv = SegmentServer(run.run, cut=run.cut, host=body.get("listen", "0.0.0.0"), port=int(body.get("port", 0)),
+                                next_hop=nxt).start()
+            segs[key] = (srv, run)
+            return srv, run
+
+        try:
+            srv, run = await run_in_threadpool(start)
+        except (ValueError, FileNotFoundError, KeyError) as e:
+            raise ApiError(400, f"cannot start the segment: {e}")
+        return {"status": "started", "port": srv.addr[1], "host": srv.addr[0], **run.status()}
+
     @r.post("/api/swap")
     async def swap(req: Request):
         """Replace the resident model: the named one (or every resident language model when none is

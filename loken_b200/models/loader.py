@@ -108,8 +108,10 @@ def _vec(r: G.GGUFReader, name: str, device, sl: Optional[slice] = None) -> Opti
 
 
 def load_gguf(path: str, device, *, tp_rank: int = 0, tp_size: int = 1, ep_rank: int = 0, ep_size: int = 1,
-              requant: Optional[str] = None, kv_format: Optional[str] = None, name: Optional[str] = None):
-    """-> (ModelWeights, meta dict).  The caller builds the tokenizer from `meta`."""
+              requant: Optional[str] = None, kv_format: Optional[str] = None, name: Optional[str] = None,
+              layer_range: Optional[Tuple[int, int]] = None):
+    """-> (ModelWeights, meta dict).  The caller builds the tokenizer from `meta`.  With `layer_range`
+    only layers [lo, hi) are read (a pipeline segment); the others are None."""
     r = G.GGUFReader(path)
     meta = dict(r.meta)
     if "token_embd.weight" in r.tensors:
@@ -154,7 +156,11 @@ def load_gguf(path: str, device, *, tp_rank: int = 0, tp_size: int = 1, ep_rank:
     mw = ModelWeights(cfg, embed, _vec(r, "output_norm.weight", device), lm_head, [],
                       torch.tensor(inv, dtype=torch.float32, device=device), mscale, tp_rank, tp_size, nql, nkvl, vl,
                       tp_rank * vl if tp_size > 1 else 0)
+    mw.layer_range = tuple(layer_range) if layer_range is not None else None
     for il in range(cfg.n_layers):
+        if layer_range is not None and not (layer_range[0] <= il < layer_range[1]):
+            mw.layers.append(None)
+            continue
         p = f"blk.{il}."
         if has(p + "attn_qkv.weight"):
             s = T(p + "attn_qkv.weight")

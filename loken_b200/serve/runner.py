@@ -363,6 +363,41 @@ class ModelRunner:
                          seq_lens=r[3], nsplit=nsplit, row_seq=self.d_row_seq, logit_rows=lr, n_logit_rows=n_l)
         return self.model.forward(inp)
 
+    def forward_hidden(self, seq_id: int, hidden: torch.Tensor, pos0: int, alloc, lo: int, hi: int,
+                       last: bool) -> torch.Tensor:
+        """A pipeline segment's forward: `hidden` [T, H] bf16 is the residual stream of positions
+        pos0 .. pos0 + T of one sequence as the previous segment left it; layers [lo, hi) run over it (every
+        row attends to the cached keys of earlier positions and to the rows before it).  Returns the
+        residual stream after layer hi - 1, or, with `last`, the fp32 logits of the final row."""
+        T = hidden.shape[0]
+        assert T <= self.d_rows.shape[1], "more rows than the runner's max_tokens"
+        nr = self.n_rows
+        nr[0, :T] = 0
+        nr[1, :T] = np.arange(pos0, pos0 + T, dtype=np.int32)
+        nr[2, :T] = alloc.slots_for_range(seq_id, pos0, pos0 + T)
+        nr[3, :T] = np.arange(pos0 + 1, pos0 + T + 1, dtype=np.int32)
+        self.n_row_seq[:T] = 0
+        bt = alloc.block_table(seq_id)
+        self.n_bt[0, :len(bt)] = bt
+        self.d_rows[:, :T].copy_(self.h_rows[:, :T], non_blocking=True)
+        self.d_row_seq[:T].copy_(self.h_row_seq[:T], non_blocking=True)
+        self.d_bt[:1].copy_(self.h_bt[:1], non_blocking=True)
+        self.h2d_bytes += 20 * T + self.max_blocks * 4 + hidden.numel() * 2
+        ctx_bucket = (pos0 + T + 1023) // 1024 * 1024
+        nsplit = attention.pick_decode_splits(T, self.w.n_kv_local, ctx_bucket)
+        r = self.d_rows
+        lr = torch.tensor([T - 1], dtype=torch.int64, device=self.device) if last else None
+        inp = StepInputs(T=T, tokens=r[0], positions=r[1], slots=r[2], mode="decode", block_table=self.d_bt,
+                         seq_lens=r[3], nsplit=nsplit, row_seq=self.d_row_seq, logit_rows=lr,
+                         n_logit_rows=1 if last else 0)
+        m = self.model
+        m.buf.x[:T].copy_(hidden)
+        m._delta_local = False
+        delta = m.run_layers(inp, lo, hi)
+        if last:
+            return m.head(inp, delta).clone()
+        return m.fold_residual(inp, delta).clone()
+
     def sample_rows(self, logits: torch.Tensor, views, uniforms: Seq[float]) -> List[int]:
         """Samples one token per logits row.  `views[i]` looks like a Sequence (params, tokens,
         output) and describes the history row i is sampled after."""
