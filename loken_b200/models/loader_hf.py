@@ -21,7 +21,7 @@ from .config import ARCH_FACTS, ModelConfig, RopeScaling
 from .weights import LayerWeights, Linear, ModelWeights, make_linear
 
 HF_ARCH = {"LlamaForCausalLM": "llama", "MistralForCausalLM": "mistral", "Qwen2ForCausalLM": "qwen2",
-           "Qwen3ForCausalLM": "qwen3"}
+           "Qwen3ForCausalLM": "qwen3", "GptOssForCausalLM": "gpt-oss"}
 
 
 def config_from_hf(cfg: dict, name: str = "hf") -> ModelConfig:
@@ -36,6 +36,31 @@ def config_from_hf(cfg: dict, name: str = "hf") -> ModelConfig:
                          original_context=int(rs.get("original_max_position_embeddings", 8192)))
     qc = cfg.get("quantization_config") or {}
     fmt = "fp8_block" if qc.get("quant_method") == "fp8" and qc.get("weight_block_size") else "bf16"
+    if arch == "gpt-oss":
+        # mixture of experts with MXFP4 expert matrices (`*_blocks` / `*_scales`), attention sinks, a sliding
+        # window on alternate layers, YaRN, biases everywhere, the clamped SwiGLU
+        if rs.get("rope_type", rs.get("type")) == "yarn":
+            sc = RopeScaling(kind="yarn", factor=float(rs.get("factor", 32.0)),
+                             original_context=int(rs.get("original_max_position_embeddings", 4096)),
+                             beta_fast=float(rs.get("beta_fast", 32.0)), beta_slow=float(rs.get("beta_slow", 1.0)))
+        out = ModelConfig(name=name, arch=arch, n_layers=int(cfg["num_hidden_layers"]), hidden=hidden, n_q=n_q,
+                          n_kv=int(cfg.get("num_key_value_heads", n_q)), head_dim=int(cfg.get("head_dim") or hidden // n_q),
+                          intermediate=int(cfg["intermediate_size"]), vocab=int(cfg["vocab_size"]),
+                          rope_theta=float(cfg.get("rope_theta", 150000.0)), rope_pairing=1, rope_scaling=sc,
+                          rms_eps=float(cfg.get("rms_norm_eps", 1e-5)), attn_bias=True,
+                          context_length=int(cfg.get("max_position_embeddings", 131072)),
+                          tie_embeddings=bool(cfg.get("tie_word_embeddings", False)),
+                          sliding_window=int(cfg.get("sliding_window") or 128), swa_period=facts.get("swa_period", 2),
+                          sinks=True, n_experts=int(cfg.get("num_local_experts") or cfg.get("num_experts")),
+                          top_k=int(cfg.get("num_experts_per_tok") or cfg.get("experts_per_token") or 4),
+                          expert_intermediate=int(cfg["intermediate_size"]), router=facts.get("router", "softmax_topk"),
+                          expert_bias=True, glu_mode=1, glu_alpha=facts.get("glu_alpha", 1.702),
+                          glu_limit=float(cfg.get("swiglu_limit", facts.get("glu_limit", 7.0))),
+                          weight_format="mxfp4" if qc.get("quant_method") == "mxfp4" else "bf16")
+        kinds = cfg.get("layer_types")
+        if isinstance(kinds, list) and len(kinds) == out.n_layers:
+            out.swa_layers = [k == "sliding_attention" for k in kinds]
+        return out
     # HF checkpoints store q/k in the half-split (NeoX) layout whatever the family
     return ModelConfig(name=name, arch=arch, n_layers=int(cfg["num_hidden_layers"]), hidden=hidden, n_q=n_q,
                        n_kv=int(cfg.get("num_key_value_heads", n_q)),
@@ -131,15 +156,63 @@ def _float_rows(sh: _Shards, stem: str, sl, col=None) -> torch.Tensor:
     return w[:, col] if col is not None else w
 
 
+def _oss_experts(sh: _Shards, stem: str, what: str, cfg: ModelConfig, elo: int, ecnt: int, device, requant):
+    """One stacked expert matrix of a gpt-oss checkpoint -> (weight, bias) in this library's layout.
+
+    `what` = "gate_up" ([E, 2I, H]: rows alternate gate_0, up_0, gate_1, ...; here every expert's gate rows
+    come first, then its up rows) or "down" ([E, H, I]).  MXFP4 files hold `<name>_blocks` uint8
+    [E, rows, K / 32, 16] (two values per byte, the even one in the low nibble: this library's own nibble
+    plane) and `<name>_scales` uint8 [E, rows, K / 32] (E8M0); bf16 files hold `<name>` as [E, K, rows]."""
+    from ..ops import quant as Q
+
+    name = stem + ("gate_up_proj" if what == "gate_up" else "down_proj")
+    E, H, I = cfg.n_experts, cfg.hidden, cfg.expert_intermediate
+    rows, K = (2 * I, H) if what == "gate_up" else (H, I)
+    bias = sh.get(name + "_bias")[elo:elo + ecnt].float() if sh.has(name + "_bias") else None
+    if what == "gate_up" and bias is not None:
+        bias = torch.cat([bias[:, 0::2], bias[:, 1::2]], 1)
+    if sh.has(name + "_blocks"):
+        blocks = sh.get(name + "_blocks")[elo:elo + ecnt]                 # [e, rows, K/32, 16]
+        scales = sh.get(name + "_scales")[elo:elo + ecnt]                 # [e, rows, K/32]
+        if tuple(blocks.shape[1:]) != (rows, K // 32, 16):
+            raise ValueError(f"{name}_blocks has shape {tuple(blocks.shape)}, expected [E, {rows}, {K // 32}, 16]")
+        codes = blocks.reshape(ecnt, rows, K // 2)
+        if what == "gate_up":
+            codes = torch.cat([codes[:, 0::2], codes[:, 1::2]], 1)
+            scales = torch.cat([scales[:, 0::2], scales[:, 1::2]], 1)
+        if requant in (None, "mxfp4") and K % 32 == 0:
+            ex = torch.zeros(ecnt * rows, Q.mx_sf_pitch(K), dtype=torch.uint8)
+            ex[:, :K // 32] = scales.reshape(ecnt * rows, K // 32)
+            from ..formats import gguf as G
+
+            w = Q.QuantWeight(Q.AQ_MX4, G.MXFP4, ecnt * rows, K, codes.reshape(ecnt * rows, K // 2).contiguous().to(device),
+                              ex.to(device))
+            return w, (bias.to(device).contiguous() if bias is not None else None), "mxfp4"
+        # another target format: decode the nibbles (E2M1 values times 2^(e - 127)) and re-encode
+        lut = torch.tensor([0, .5, 1, 1.5, 2, 3, 4, 6, -0., -.5, -1, -1.5, -2, -3, -4, -6])
+        c = codes.reshape(ecnt * rows, K // 2)
+        vals = torch.stack([lut[(c & 0xF).long()], lut[(c >> 4).long()]], -1).reshape(ecnt * rows, K)
+        dense = vals * torch.exp2(scales.reshape(ecnt * rows, K // 32).float() - 127.0).repeat_interleave(32, 1)
+    else:
+        dense = sh.get(name)[elo:elo + ecnt].float().transpose(1, 2)     # [e, rows, K]
+        if what == "gate_up":
+            dense = torch.cat([dense[:, 0::2], dense[:, 1::2]], 1)
+        dense = dense.reshape(ecnt * rows, K)
+    fmt = requant or "bf16"
+    w = dense.to(device).bfloat16() if fmt == "bf16" else Q.quantize_weight(dense.to(device), fmt)
+    return w, (bias.to(device).contiguous() if bias is not None else None), fmt
+
+
 def load_hf(directory: str, device, *, tp_rank: int = 0, tp_size: int = 1, requant: Optional[str] = None,
             kv_format: Optional[str] = None):
-    """-> (ModelWeights, hf config dict)."""
+    """-> (ModelWeights, hf config dict).  Under tensor parallelism a mixture model's experts are split
+    over the same ranks (expert-parallel degree = tensor-parallel degree)."""
     with open(os.path.join(directory, "config.json")) as f:
         hf = json.load(f)
     cfg = config_from_hf(hf, os.path.basename(os.path.normpath(directory)))
     if kv_format:
         cfg.kv_format = kv_format
-    if requant:
+    if requant and not cfg.is_moe:
         cfg.weight_format = requant
     sh = _Shards(directory)
     hd, H = cfg.head_dim, cfg.hidden
@@ -190,10 +263,83 @@ def load_hf(directory: str, device, *, tp_rank: int = 0, tp_size: int = 1, requa
         if sh.has(a + "q_norm.weight"):
             lw.q_norm, lw.k_norm = vec(a + "q_norm.weight"), vec(a + "k_norm.weight")
         m = p + "mlp."
-        lw.w_gate_up = linear([m + "gate_proj", m + "up_proj"], [i_sl, i_sl])
-        lw.w_down = linear([m + "down_proj"], [None], col=i_sl if tp_size > 1 else None)
+        if sh.has(a + "sinks"):
+            lw.sinks = vec(a + "sinks")[tp_rank * nql:(tp_rank + 1) * nql].contiguous()
+        if cfg.is_moe and sh.has(m + "router.weight"):
+            from .moe import MoeWeights
+
+            ecnt = cfg.n_experts // tp_size
+            elo = tp_rank * ecnt
+            mreq = requant if requant in ("mxfp4", "bf16", "q8_0") else None
+            gu, gub, fmt = _oss_experts(sh, m + "experts.", "gate_up", cfg, elo, ecnt, device, mreq)
+            dn, dnb, _ = _oss_experts(sh, m + "experts.", "down", cfg, elo, ecnt, device, mreq)
+            lw.moe = MoeWeights(sh.get(m + "router.weight").to(device).bfloat16(),
+                                vec(m + "router.bias") if sh.has(m + "router.bias") else None,
+                                gu, dn, gub, dnb, elo, ecnt, fmt)
+        else:
+            lw.w_gate_up = linear([m + "gate_proj", m + "up_proj"], [i_sl, i_sl])
+            lw.w_down = linear([m + "down_proj"], [None], col=i_sl if tp_size > 1 else None)
         mw.layers.append(lw)
     return mw, hf
+
+
+def save_hf_gpt_oss(directory: str, cfg: ModelConfig, mw: ModelWeights) -> None:
+    """Writes a one-rank gpt-oss-shaped model in the checkpoint layout `load_hf` reads: MXFP4 experts as
+    `*_blocks` / `*_scales` with interleaved gate / up rows, bf16 attention, sinks, biases (test files)."""
+    from safetensors.torch import save_file
+
+    from ..ops import quant as Q
+
+    os.makedirs(directory, exist_ok=True)
+    hd, H, I, E = cfg.head_dim, cfg.hidden, cfg.expert_intermediate, cfg.n_experts
+    t: Dict[str, torch.Tensor] = {"model.embed_tokens.weight": mw.embed.cpu(), "model.norm.weight": mw.out_norm.cpu(),
+                                  "lm_head.weight": mw.lm_head.cpu()}
+    nq, nk = cfg.n_q * hd, cfg.n_kv * hd
+
+    def inter(x):            # [E, 2I, ...] gate rows then up rows -> rows alternating gate_i, up_i
+        g, u = x[:, :I], x[:, I:]
+        return torch.stack([g, u], 2).reshape(x.shape)
+
+    for il, lw in enumerate(mw.layers):
+        p = f"model.layers.{il}."
+        t[p + "input_layernorm.weight"] = lw.attn_norm.cpu()
+        t[p + "post_attention_layernorm.weight"] = lw.ffn_norm.cpu()
+        w = lw.wqkv.weight.cpu()
+        b = lw.wqkv.bias.cpu()
+        for nm, r0, r1 in (("q_proj", 0, nq), ("k_proj", nq, nq + nk), ("v_proj", nq + nk, nq + 2 * nk)):
+            t[p + f"self_attn.{nm}.weight"] = w[r0:r1].contiguous()
+            t[p + f"self_attn.{nm}.bias"] = b[r0:r1].contiguous()
+        t[p + "self_attn.o_proj.weight"] = lw.wo.weight.cpu().contiguous()
+        t[p + "self_attn.o_proj.bias"] = lw.wo.bias.cpu()
+        t[p + "self_attn.sinks"] = lw.sinks.cpu()
+        moe = lw.moe
+        t[p + "mlp.router.weight"] = moe.router_w.cpu()
+        t[p + "mlp.router.bias"] = moe.router_b.cpu()
+        for nm, qw, bias, rows, K in (("gate_up_proj", moe.gate_up, moe.gate_up_b, 2 * I, H),
+                                      ("down_proj", moe.down, moe.down_b, H, I)):
+            assert isinstance(qw, Q.QuantWeight) and qw.aq_fmt == Q.AQ_MX4
+            codes = qw.codes.cpu().reshape(E, rows, K // 32, 16)
+            sc = qw.scales.cpu()[:, :K // 32].reshape(E, rows, K // 32)
+            bias = bias.cpu()
+            if nm == "gate_up_proj":
+                codes, sc, bias = inter(codes), inter(sc), inter(bias)
+            t[p + f"mlp.experts.{nm}_blocks"] = codes.contiguous()
+            t[p + f"mlp.experts.{nm}_scales"] = sc.contiguous()
+            t[p + f"mlp.experts.{nm}_bias"] = bias.contiguous()
+    save_file(t, os.path.join(directory, "model.safetensors"))
+    hf = {"architectures": ["GptOssForCausalLM"], "num_hidden_layers": cfg.n_layers, "hidden_size": H,
+          "num_attention_heads": cfg.n_q, "num_key_value_heads": cfg.n_kv, "head_dim": hd, "intermediate_size": I,
+          "vocab_size": cfg.vocab, "rope_theta": cfg.rope_theta, "rms_norm_eps": cfg.rms_eps,
+          "max_position_embeddings": cfg.context_length, "sliding_window": cfg.sliding_window,
+          "layer_types": ["sliding_attention" if cfg.layer_window(i) else "full_attention" for i in range(cfg.n_layers)],
+          "num_local_experts": E, "num_experts_per_tok": cfg.top_k, "swiglu_limit": cfg.glu_limit,
+          "quantization_config": {"quant_method": "mxfp4"},
+          "rope_scaling": {"rope_type": "yarn", "factor": cfg.rope_scaling.factor,
+                           "original_max_position_embeddings": cfg.rope_scaling.original_context,
+                           "beta_fast": getattr(cfg.rope_scaling, "beta_fast", 32.0),
+                           "beta_slow": getattr(cfg.rope_scaling, "beta_slow", 1.0)}}
+    with open(os.path.join(directory, "config.json"), "w") as f:
+        json.dump(hf, f)
 
 
 def save_hf_fp8(directory: str, cfg: ModelConfig, mw: ModelWeights) -> None:
