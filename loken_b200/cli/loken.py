@@ -129,7 +129,8 @@ def build_parser() -> argparse.ArgumentParser:
     d.add_argument("--model")
     d.add_argument("--draft")
     d.add_argument("-k", type=int, default=4)
-    d.add_argument("--method", default="model", choices=["model", "prompt_lookup"])
+    d.add_argument("--method", default="model", choices=["model", "prompt_lookup", "head"],
+                   help="head: --draft names a directory with an EAGLE or MTP head, or random:eagle / random:mtp")
     pl = sub.add_parser("pull")
     pl.add_argument("name", help="name:tag of an Ollama registry model, or owner/repo[:file] on the Hugging Face hub")
     pl.add_argument("--insecure", action="store_true")

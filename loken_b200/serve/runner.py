@@ -327,11 +327,12 @@ class ModelRunner:
         return self.h_hist[:B, :steps].tolist()
 
     # ---- several rows per sequence through the decode kernels (verification, draft catch-up) ----
-    def forward_rows(self, items, alloc, last_only: bool = False) -> torch.Tensor:
+    def forward_rows(self, items, alloc, last_only: bool = False, embeds: Optional[torch.Tensor] = None) -> torch.Tensor:
         """items: (seq, tokens, start) — feed `tokens` at positions start.. of `seq`, whose cache
         already holds positions < start and has blocks for the new rows.  Every row attends to
         the keys at or before its own position (rows of one sequence see the rows before them:
-        all K/V are written before any attention runs).  Returns logits [rows or items, vocab]."""
+        all K/V are written before any attention runs).  Returns logits [rows or items, vocab].
+        `embeds` [rows, hidden] bf16 takes the embedding table's place for every row (a draft head's input)."""
         nr, nbt = self.n_rows, self.n_bt
         T, max_len, last = 0, 1, []
         for j, (s, toks, start) in enumerate(items):
@@ -360,7 +361,8 @@ class ModelRunner:
             lr = torch.tensor(last, dtype=torch.int64, device=self.device)
             n_l = len(last)
         inp = StepInputs(T=T, tokens=r[0], positions=r[1], slots=r[2], mode="decode", block_table=self.d_bt,
-                         seq_lens=r[3], nsplit=nsplit, row_seq=self.d_row_seq, logit_rows=lr, n_logit_rows=n_l)
+                         seq_lens=r[3], nsplit=nsplit, row_seq=self.d_row_seq, logit_rows=lr, n_logit_rows=n_l,
+                         embed_overrides=[(0, embeds[:T])] if embeds is not None else None)
         return self.model.forward(inp)
 
     def forward_hidden(self, seq_id: int, hidden: torch.Tensor, pos0: int, alloc, lo: int, hi: int,

@@ -314,12 +314,16 @@ class Speculator:
             states.append((rng, st, d))
         logits = engine.runner.forward_rows(items, engine.alloc)
         sampled = engine.runner.sample_rows(logits, views, uniforms)
+        # a draft head reads the target's final hidden states of the rows that are about to be committed
+        watch = getattr(self.drafter, "observe", None)
+        hidden = engine.runner.model.buf.x if watch is not None else None
         out: Dict[int, List[int]] = {}
         row = 0
         n_acc_total = 0
         for s, (rng, st, d) in zip(seqs, states):
             n = len(d) + 1
             mine = sampled[row:row + n]
+            row0 = row
             row += n
             commit: List[int] = []
             acc = 0
@@ -340,6 +344,8 @@ class Speculator:
             self.rejected += len(d) - acc
             n_acc_total += acc
             out[s.seq_id] = commit
+            if watch is not None:
+                watch(s, len(s.tokens) - 1, hidden[row0:row0 + len(commit)], commit)
         self.cycles += 1
         dt = time.perf_counter() - t0
         if k > 0:
@@ -371,8 +377,23 @@ def attach_draft_engine(eng, draft: Optional[str], k: int = 4, method: str = "mo
     """The same on a bare engine.  Every tensor-parallel rank holds a whole copy of the (small)
     drafter and runs it redundantly, so all ranks propose the same tokens without a collective."""
     del tp_rank, tp_size, comm
-    if method == "prompt_lookup" or not draft:
+    if method == "prompt_lookup" or (not draft and method != "head"):
         drafter = PromptLookupDrafter()
+    elif method == "head":
+        # a draft head on the target's own hidden states: a directory with an EAGLE or MTP head in safetensors,
+        # or "random:eagle" / "random:mtp" for a random-init head of the target's width
+        import os
+
+        from .draft_head import HeadDrafter, load_draft_head, random_draft_head
+
+        if eng.weights.tp_size > 1:
+            raise ValueError("a draft head reads the whole residual stream: not available under tensor parallelism")
+        if draft and os.path.isdir(draft):
+            head = load_draft_head(draft, eng.cfg, eng.device)
+        else:
+            head = random_draft_head(eng.cfg, eng.device, kind=(draft or "random:eagle").split(":")[-1])
+        drafter = HeadDrafter(eng.weights, head, max_seqs=eng.sched.max_running, max_ctx=eng.max_ctx,
+                              model_id=os.path.basename(os.path.normpath(draft)) if draft else "random")
     else:
         import os
 

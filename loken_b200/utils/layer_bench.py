@@ -29,13 +29,17 @@ def layer_times(model: str, layers: int, batch: int, ctx: int, weight_format=Non
     eng = LLMEngine(cfg, max_seqs=max(batch, 8), max_prefill_tokens=8192, max_ctx=ctx + 256,
                     num_blocks=batch * ((ctx + 256) // 16) + 64, use_graphs=False)
     g = torch.Generator().manual_seed(0)
-    sp = SamplingParams(temperature=0.7, top_k=0, top_p=0.9, ignore_eos=True, seed=1, max_tokens=8)
+    sp = SamplingParams(temperature=0.7, top_k=0, top_p=0.9, ignore_eos=True, seed=1, max_tokens=4096)
     ids = [eng.add_request(torch.randint(0, cfg.vocab, (ctx,), generator=g).tolist(), sp) for _ in range(batch)]
     while any(len(eng.seqs[i].output) == 0 for i in ids):
         eng.step()
     # one decode step's inputs, staged the way the runner stages them, then the profiling pass over them
     r = eng.runner
     seqs = [eng.seqs[i] for i in ids]
+    for s in seqs:                            # the slot of the token a decode step would write
+        short = s.total_len - eng.alloc.length(s.seq_id)
+        if short > 0 and not eng.alloc.append(s.seq_id, short):
+            raise MemoryError("no cache block for the profiled step")
     B, nsplit = r._stage_decode(seqs, eng.alloc)
     inp = r._decode_inputs(B, nsplit)
     r.model.profile_layers(inp)
