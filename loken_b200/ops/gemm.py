@@ -75,7 +75,7 @@ SPLIT_OVERRIDE = 0      # measurement hook: K splits of GEMMs with fewer tiles t
 
 def _pick_splits(tiles: int, nkb: int) -> int:
     if SPLIT_OVERRIDE:
-        return max(1, min(SPLIT_OVERRIDE, nkb, NUM_SMS // max(1, tiles)))
+        return max(1, min(SPLIT_OVERRIDE, nkb))
     # up to eight K blocks the split's hand-over (workspace, counter, owner sum: ~5 us) costs more than
     # the K loop it saves (measured 9.0 vs 10.8 us on 8192 x 1024)
     if tiles >= NUM_SMS or nkb <= 8:

@@ -114,6 +114,7 @@ def gemm_sweep_case(M: int, shapes, variants):
         for v in variants:
             f = v.split(":")
             nums = [int(t) for t in f[1:]] + [0] * 4
+            gemm.SPLIT_OVERRIDE = nums[0] if f[0] == "fold" else 0        # "fold:S": S K-splits of every tile
             gemm.FP8_MX_MAX_M = 0 if f[0] == "fold" else (nums[0] or 1 << 20)
             gemm.FP8_MX_WIDE_MAX_M = gemm.FP8_MX_MAX_M
             gemm.FP8_MX_PLAN = (nums[1], nums[2], nums[3])
