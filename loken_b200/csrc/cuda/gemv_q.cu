@@ -1,0 +1,278 @@
+// Quantised GEMV for decode-size batches (1..8 token rows): out[m, n] = sum_k W[n, k] x[m, k] with W in a
+// GGUF block format held as device planes (ops/quant.py: codes + scale records) and the activations
+// quantised to int8 per 32 values on the fly, so the inner product is `dp4a` on the stored integer codes:
+// nothing is expanded to bf16 and the weights are read exactly once.  This is the single-stream decode
+// path of quantised models; from nine token rows up the tensor-core GEMM with dequantising warps
+// (gemm_tc.cuh, dequant.cuh) takes over.
+//
+//   Q8_0   int8 codes, one f16 scale per 32 values
+//   Q6_K   int8 codes (already centred), per 256 values: f16 d + sixteen int8 sub-scales (one per 16)
+//   Q4_K   nibbles (value k in byte k / 2, low nibble for even k), per 256 values: f16 d, f16 dmin,
+//          eight 6-bit sub-scales and eight 6-bit minima as bytes (one of each per 32 values)
+//
+// Layout of the work: a CTA first quantises the M activation rows into shared memory, once (int8 codes,
+// one f32 scale and, for Q4_K, one f32 sum per 32 values: the minimum term needs sum(x)); from there on it
+// has no barrier.  It then walks row groups (8 warps x RW rows) strided over the grid: a lane owns every
+// 32nd group of 32 values of K, takes the M groups of activation codes from shared memory and reads 32
+// weight codes per row (16 or 32 bytes) plus the group's scale fields; floats accumulate per (row, token),
+// one butterfly per (row, token) ends a row group.  A first form that quantised 1024 values of K per
+// step between two barriers spent most of its time in those steps (Q8_0, 57344 x 8192: 134 us at one
+// token, 380 us at eight).
+//
+// The reference's quantised decode is the same idea with its own block layouts: int8 activations (q8_1) and
+// dp4a over the codes (cuda/moe/moe_gguf.cu:405-1340, src/inference/cuda/quantized/); its accuracy bar for
+// 8-bit activations is 2e-2 of the largest expected output.
+#include "common.cuh"
+#include "host_common.h"
+#include "loken_cuda.h"
+
+using namespace lk;
+
+namespace {
+
+constexpr int GV_WARPS = 8;
+enum { GV_W8 = 1, GV_W8G16 = 2, GV_W4 = 3 };
+
+__device__ __forceinline__ int dp4a_s8(uint32_t a, uint32_t b, int c) {
+  int d;
+  asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ int dp4a_u8s8(uint32_t a, uint32_t b, int c) {
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ float h2f(const uint8_t* p) {
+  return __half2float(*reinterpret_cast<const __half*>(p));
+}
+
+struct GvParams {
+  const uint8_t* codes;       // [N, code bytes per row]
+  const uint8_t* scales;      // [N, scale bytes per row]
+  long long c_ld, s_ld;       // row pitches in bytes
+  const __nv_bfloat16* x;     // [M, K]
+  long long ldx;
+  const float* bias;          // [N] or null
+  __nv_bfloat16* out;         // [M, N]
+  long long ldo;
+  int M, N, K;
+};
+
+// FMT: block format; MT: token rows (1, 2, 4 or 8); RW: output rows per warp and pass
+template <int FMT, int MT, int RW>
+__global__ void __launch_bounds__(GV_WARPS * 32)
+gemv_q_kernel(const GvParams p) {
+  pdl_wait();
+  pdl_launch();
+  // the activations of the whole row, quantised once per CTA: codes as words (for Q4_K de-interleaved per 8
+  // values, even values then odd ones, to line up with the nibble planes), scale and sum per 32-value group
+  extern __shared__ __align__(16) uint8_t gv_smem[];
+  const int ngroups = p.K >> 5;
+  uint32_t* xq = reinterpret_cast<uint32_t*>(gv_smem);                         // [MT][K / 4]
+  float* xd = reinterpret_cast<float*>(gv_smem + (size_t)MT * p.K);            // [MT][K / 32]
+  float* xs = xd + MT * ngroups;                                               // [MT][K / 32]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int g = threadIdx.x; g < MT * ngroups; g += GV_WARPS * 32) {
+    const int m = g / ngroups, gi = g % ngroups;
+    float v[32];
+    if (m < p.M) {
+      const uint4* src = reinterpret_cast<const uint4*>(p.x + (long long)m * p.ldx + gi * 32);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint4 u = src[q];
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h[e]);
+          v[q * 8 + 2 * e] = f.x;
+          v[q * 8 + 2 * e + 1] = f.y;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 32; ++e) v[e] = 0.f;
+    }
+    float amax = 0.f, sum = 0.f;
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+      amax = fmaxf(amax, fabsf(v[e]));
+      sum += v[e];
+    }
+    const float d = amax * (1.f / 127.f);
+    const float id = d > 0.f ? 1.f / d : 0.f;
+    uint32_t wq[8];
+#pragma unroll
+    for (int w8 = 0; w8 < 4; ++w8) {
+      int q8[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) q8[e] = __float2int_rn(v[w8 * 8 + e] * id) & 0xFF;
+      if (FMT == GV_W4) {
+        wq[2 * w8] = q8[0] | (q8[2] << 8) | (q8[4] << 16) | (q8[6] << 24);
+        wq[2 * w8 + 1] = q8[1] | (q8[3] << 8) | (q8[5] << 16) | (q8[7] << 24);
+      } else {
+        wq[2 * w8] = q8[0] | (q8[1] << 8) | (q8[2] << 16) | (q8[3] << 24);
+        wq[2 * w8 + 1] = q8[4] | (q8[5] << 8) | (q8[6] << 16) | (q8[7] << 24);
+      }
+    }
+    uint4* dst = reinterpret_cast<uint4*>(xq + (size_t)m * (p.K >> 2) + gi * 8);
+    dst[0] = make_uint4(wq[0], wq[1], wq[2], wq[3]);
+    dst[1] = make_uint4(wq[4], wq[5], wq[6], wq[7]);
+    xd[m * ngroups + gi] = d;
+    xs[m * ngroups + gi] = sum;
+  }
+  __syncthreads();
+
+  // row groups of RW rows per warp, strided over the grid; no barrier from here on
+  const int n_rg = (p.N + GV_WARPS * RW - 1) / (GV_WARPS * RW);
+  for (int rg = blockIdx.x; rg < n_rg; rg += gridDim.x) {
+    const int row0 = (rg * GV_WARPS + warp) * RW;
+    if (row0 >= p.N) continue;
+    float acc[RW][MT];
+#pragma unroll
+    for (int r = 0; r < RW; ++r)
+#pragma unroll
+      for (int m = 0; m < MT; ++m) acc[r][m] = 0.f;
+    for (int gi = lane; gi < ngroups; gi += 32) {      // this lane's 32-value group of every chunk
+      const int k = gi << 5;
+      uint32_t xw[MT][8];
+      float dx[MT], sx[MT];
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        const uint4* src = reinterpret_cast<const uint4*>(xq + (size_t)m * (p.K >> 2) + gi * 8);
+        const uint4 a = src[0], b = src[1];
+        xw[m][0] = a.x; xw[m][1] = a.y; xw[m][2] = a.z; xw[m][3] = a.w;
+        xw[m][4] = b.x; xw[m][5] = b.y; xw[m][6] = b.z; xw[m][7] = b.w;
+        dx[m] = xd[m * ngroups + gi];
+        sx[m] = xs[m * ngroups + gi];
+      }
+#pragma unroll
+      for (int r = 0; r < RW; ++r) {
+        const int n = min(row0 + r, p.N - 1);          // rows past the end repeat the last one; never stored
+        if (FMT == GV_W8) {
+          const uint4* c = reinterpret_cast<const uint4*>(p.codes + (long long)n * p.c_ld + k);
+          const uint4 c0 = __ldg(c), c1 = __ldg(c + 1);
+          const float dw = h2f(p.scales + (long long)n * p.s_ld + (k >> 5) * 2);
+          const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+          for (int m = 0; m < MT; ++m) {
+            int s = 0;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) s = dp4a_s8(cw[q], xw[m][q], s);
+            acc[r][m] = fmaf(dw * dx[m], (float)s, acc[r][m]);
+          }
+        } else if (FMT == GV_W8G16) {
+          const uint4* c = reinterpret_cast<const uint4*>(p.codes + (long long)n * p.c_ld + k);
+          const uint4 c0 = __ldg(c), c1 = __ldg(c + 1);
+          const uint8_t* rec = p.scales + (long long)n * p.s_ld + (k >> 8) * 18;
+          const float d = h2f(rec);
+          const int j = (k & 255) >> 4;                  // first of this group's two sub-scales
+          const uint32_t two = *reinterpret_cast<const uint16_t*>(rec + 2 + j);      // j is even: 2-byte aligned
+          const float s0 = d * (float)(int8_t)(two & 0xFF), s1 = d * (float)(int8_t)(two >> 8);
+          const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+          for (int m = 0; m < MT; ++m) {
+            int a = 0, b = 0;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              a = dp4a_s8(cw[q], xw[m][q], a);
+              b = dp4a_s8(cw[4 + q], xw[m][4 + q], b);
+            }
+            acc[r][m] = fmaf(dx[m], s0 * (float)a + s1 * (float)b, acc[r][m]);
+          }
+        } else {
+          const uint4 c0 = __ldg(reinterpret_cast<const uint4*>(p.codes + (long long)n * p.c_ld + (k >> 1)));
+          const uint8_t* rec = p.scales + (long long)n * p.s_ld + (k >> 8) * 20;
+          const int j = (k & 255) >> 5;
+          const uint32_t dd = *reinterpret_cast<const uint32_t*>(rec);          // d and dmin: records are 4-byte aligned
+          const float d = __half2float(__ushort_as_half((unsigned short)(dd & 0xFFFF))) * (float)rec[4 + j];
+          const float mn = __half2float(__ushort_as_half((unsigned short)(dd >> 16))) * (float)rec[12 + j];
+          const uint32_t cw[4] = {c0.x, c0.y, c0.z, c0.w};
+#pragma unroll
+          for (int m = 0; m < MT; ++m) {
+            int s = 0;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              s = dp4a_u8s8(cw[q] & 0x0F0F0F0Fu, xw[m][2 * q], s);              // even values
+              s = dp4a_u8s8((cw[q] >> 4) & 0x0F0F0F0Fu, xw[m][2 * q + 1], s);   // odd values
+            }
+            acc[r][m] += d * dx[m] * (float)s - mn * sx[m];
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < RW; ++r) {
+      const int n = row0 + r;
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        const float v = warp_sum(acc[r][m]);
+        if (lane == 0 && n < p.N && m < p.M) p.out[(long long)m * p.ldo + n] = f2bf(v + (p.bias ? p.bias[n] : 0.f));
+      }
+    }
+  }
+}
+
+template <int FMT, int MT>
+int launch_gv(const GvParams& p, cudaStream_t st) {
+  constexpr int RW = MT <= 2 ? 4 : 2;
+  const size_t smem = (size_t)MT * p.K + (size_t)MT * (p.K >> 5) * 8;
+  if (smem > 200 * 1024) return LKH_TOO_LARGE;
+  auto kern = gemv_q_kernel<FMT, MT, RW>;
+  static size_t granted = 48 * 1024;
+  if (smem > granted) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    granted = 200 * 1024;
+  }
+  // every CTA quantises the activations once, then walks row groups: a few CTAs per SM, not one per group
+  const int n_rg = (p.N + GV_WARPS * RW - 1) / (GV_WARPS * RW);
+  const int per_sm = smem > 100 * 1024 ? 1 : smem > 48 * 1024 ? 2 : 3;
+  const int grid = n_rg < 148 * per_sm ? n_rg : 148 * per_sm;
+  lkh::launch_pdl(kern, dim3(grid), dim3(GV_WARPS * 32), smem, st, p);
+  return 0;
+}
+
+template <int FMT>
+int dispatch_gv(const GvParams& p, int M, cudaStream_t st) {
+  if (M == 1) return launch_gv<FMT, 1>(p, st);
+  if (M == 2) return launch_gv<FMT, 2>(p, st);
+  if (M <= 4) return launch_gv<FMT, 4>(p, st);
+  return launch_gv<FMT, 8>(p, st);
+}
+
+}  // namespace
+
+// x [M <= 8, K] bf16 (row pitch ldx elements), W as device planes of format `fmt` (1 Q8_0, 2 Q6_K, 3 Q4_K),
+// out [M, N] bf16 (row pitch ldo).  K a multiple of 32 (256 for the K formats).
+LK_API int lk_gemv_q(int fmt, const void* codes, long long c_ld, const void* scales, long long s_ld, const void* x,
+                     long long ldx, int M, int N, int K, const float* bias, void* out, long long ldo, void* stream) {
+  if (M <= 0 || N <= 0) return LKH_OK;
+  if (M > 8 || !codes || !scales || !x || !out || (K & 31) || (ldx & 7)) return LKH_BAD_ARG;
+  if ((fmt == GV_W8G16 || fmt == GV_W4) && (K & 255)) return LKH_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(codes) & 15) || (c_ld & 15) || (reinterpret_cast<uintptr_t>(x) & 15)) return LKH_BAD_ARG;
+  GvParams p;
+  p.codes = reinterpret_cast<const uint8_t*>(codes);
+  p.scales = reinterpret_cast<const uint8_t*>(scales);
+  p.c_ld = c_ld;
+  p.s_ld = s_ld;
+  p.x = reinterpret_cast<const __nv_bfloat16*>(x);
+  p.ldx = ldx;
+  p.bias = bias;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.ldo = ldo;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int rc;
+  switch (fmt) {
+    case GV_W8: rc = dispatch_gv<GV_W8>(p, M, st); break;
+    case GV_W8G16: rc = dispatch_gv<GV_W8G16>(p, M, st); break;
+    case GV_W4: rc = dispatch_gv<GV_W4>(p, M, st); break;
+    default: return LKH_BAD_ARG;
+  }
+  if (rc) return rc;
+  lkh::count_launch();
+  return lkh::launch_status();
+}

@@ -156,6 +156,9 @@ def _pick_bn(rows: int) -> int:
     return 16 if rows <= 16 else 64 if rows <= 64 else 128
 
 
+GEMV_MAX_M = 8          # up to this many token rows the dp4a GEMV runs (gemv_q.cu); 0 turns it off
+
+
 def linear_gguf(x: torch.Tensor, w: QuantWeight, *, bias: Optional[torch.Tensor] = None,
                 out: Optional[torch.Tensor] = None, splits: int = 0) -> torch.Tensor:
     """x bf16 [M, K] @ W.T -> bf16 [M, N].  Tokens ride the MMA N dimension in tiles of
@@ -174,6 +177,13 @@ def linear_gguf(x: torch.Tensor, w: QuantWeight, *, bias: Optional[torch.Tensor]
             w._mx = mx.mx_weight(w)
         xa = mx.quant_mx8(x, rows=M)
         return mx.linear_mx(xa, w._mx, bias=bias, out=out, rows=M)
+    if M <= GEMV_MAX_M and w.aq_fmt in (AQ_W8, AQ_W8G16, AQ_W4) and x.stride(0) % 8 == 0 \
+            and (1 if M == 1 else 2 if M == 2 else 4 if M <= 4 else 8) * K * 1.25 <= 200 * 1024:
+        # a handful of token rows: int8 activations and dp4a over the stored codes, every weight byte read once
+        check(cuda_lib().lk_gemv_q(w.aq_fmt, ptr(w.codes), C.c_longlong(w.codes.stride(0)), ptr(w.scales),
+                                   C.c_longlong(w.scales.stride(0)), ptr(x), C.c_longlong(x.stride(0)), M, N, K,
+                                   ptr(bias), ptr(out), C.c_longlong(out.stride(0)), stream()), "lk_gemv_q")
+        return out
     wsp = Workspace.get(x.device)
     bn = _pick_bn(M)
     tiles = ((N + 127) // 128) * ((M + bn - 1) // bn)

@@ -44,3 +44,39 @@ def test_linear_gguf(fmt, M, N, K):
         assert rel_err(out2, ref) < 1e-2
     finally:
         quant.MX_NATIVE = True
+
+
+@pytest.mark.parametrize("fmt", ["q8_0", "q4_k", "q6_k"])
+@pytest.mark.parametrize("M", [1, 2, 3, 8])
+@pytest.mark.parametrize("N,K", [(300, 2048), (4096, 1280), (1234, 256)])     # ragged rows; a tail chunk; one block
+def test_gemv_dp4a_matches_the_integer_product_and_the_gemm(fmt, M, N, K):
+    """Up to eight token rows run as a GEMV on int8 activations: it equals the product of the activations as
+    quantised (per 32 values, amax / 127) with the decoded weights, and stays within the int8 noise of the
+    tensor-core route that larger batches take."""
+    from loken_b200.ops import quant
+
+    torch.manual_seed(N + K + M)
+    w = torch.randn(N, K, device=DEV) * 0.05
+    q = quant.quantize_weight(w, fmt)
+    wd = quant.dequantize_weight(q)
+    x = (torch.randn(M, K, device=DEV) * torch.rand(M, 1, device=DEV) * 2).bfloat16()
+    bias = torch.randn(N, device=DEV) * 0.1
+    g = x.float().view(M, K // 32, 32)
+    d = g.abs().amax(2, keepdim=True) / 127.0
+    xq = (torch.round(g / d.clamp_min(1e-30)).clamp(-127, 127) * d).view(M, K)
+    exact = xq @ wd.t() + bias
+    out = quant.linear_gguf(x, q, bias=bias)
+    torch.cuda.synchronize()
+    # bf16 rounding of the output; the Q4_K minimum term uses the sum of the unquantised activations (closer to
+    # the true product than the sum of their codes), which this emulation does not
+    assert rel_err(out, exact) < (2e-2 if fmt == "q4_k" else 1e-2)
+    assert rel_err(out, x.float() @ wd.t() + bias) < 2e-2
+    old = quant.GEMV_MAX_M
+    try:
+        quant.GEMV_MAX_M = 0
+        gemm = quant.linear_gguf(x, q, bias=bias)
+    finally:
+        quant.GEMV_MAX_M = old
+    assert rel_err(out, gemm) < 2e-2                   # the reference's bar for 8-bit activations
+    again = quant.linear_gguf(x, q, bias=bias)
+    assert torch.equal(out, again)
