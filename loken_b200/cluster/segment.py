@@ -127,7 +127,9 @@ class PipelineHead:
         ids = torch.tensor(list(tokens), dtype=torch.long, device=dev)
         with seg.lock:
             q = seg._prepare(request_id, int(pos0), len(ids))
-            x = (self.w.embed[ids].float() * self.cfg.embedding_scale).bfloat16()
+            from ..models.weights import embed_lookup
+
+            x = (embed_lookup(self.w, ids) * self.cfg.embedding_scale).bfloat16()
             h = seg.runner.forward_hidden(q.seq_id, x, int(pos0), seg.alloc, 0, self.cut_at, False)
             out = h.float().cpu().numpy()
         return np.asarray(self.link.boundary(request_id, out, int(pos0)))

@@ -54,9 +54,10 @@ struct GvParams {
   const __nv_bfloat16* x;     // [M, K]
   long long ldx;
   const float* bias;          // [N] or null
-  __nv_bfloat16* out;         // [M, N]
+  __nv_bfloat16* out;         // [M, N] bf16, or f32 when out_fp32
   long long ldo;
   int M, N, K;
+  int out_fp32;
 };
 
 // FMT: block format; MT: token rows (1, 2, 4 or 8); RW: output rows per warp and pass
@@ -207,7 +208,13 @@ gemv_q_kernel(const GvParams p) {
 #pragma unroll
       for (int m = 0; m < MT; ++m) {
         const float v = warp_sum(acc[r][m]);
-        if (lane == 0 && n < p.N && m < p.M) p.out[(long long)m * p.ldo + n] = f2bf(v + (p.bias ? p.bias[n] : 0.f));
+        if (lane == 0 && n < p.N && m < p.M) {
+          const float o = v + (p.bias ? p.bias[n] : 0.f);
+          if (p.out_fp32)
+            reinterpret_cast<float*>(p.out)[(long long)m * p.ldo + n] = o;
+          else
+            p.out[(long long)m * p.ldo + n] = f2bf(o);
+        }
       }
     }
   }
@@ -241,12 +248,81 @@ int dispatch_gv(const GvParams& p, int M, cudaStream_t st) {
   return launch_gv<FMT, 8>(p, st);
 }
 
+// Embedding gather from a quantised table: row tok[t] of the planes is decoded to bf16.  One CTA per token,
+// a thread per 32-value group and pass.
+template <int FMT>
+__global__ void __launch_bounds__(128)
+embed_q_kernel(const int* __restrict__ tok, const uint8_t* __restrict__ codes, long long c_ld,
+               const uint8_t* __restrict__ scales, long long s_ld, __nv_bfloat16* __restrict__ out, int H, int vocab,
+               float scale) {
+  const int t = blockIdx.x;
+  int id = tok[t];
+  if (id < 0 || id >= vocab) id = 0;
+  const uint8_t* c = codes + (long long)id * c_ld;
+  const uint8_t* s = scales + (long long)id * s_ld;
+  __nv_bfloat16* dst = out + (long long)t * H;
+  for (int g = threadIdx.x; g < (H >> 5); g += blockDim.x) {
+    const int k = g << 5;
+    float v[32];
+    if (FMT == GV_W8) {
+      const float d = h2f(s + g * 2) * scale;
+      const int8_t* q = reinterpret_cast<const int8_t*>(c + k);
+#pragma unroll
+      for (int e = 0; e < 32; ++e) v[e] = d * (float)q[e];
+    } else if (FMT == GV_W8G16) {
+      const uint8_t* rec = s + (k >> 8) * 18;
+      const float d = h2f(rec) * scale;
+      const int j = (k & 255) >> 4;
+      const float s0 = d * (float)(int8_t)rec[2 + j], s1 = d * (float)(int8_t)rec[3 + j];
+      const int8_t* q = reinterpret_cast<const int8_t*>(c + k);
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        v[e] = s0 * (float)q[e];
+        v[16 + e] = s1 * (float)q[16 + e];
+      }
+    } else {
+      const uint8_t* rec = s + (k >> 8) * 20;
+      const int j = (k & 255) >> 5;
+      const float d = h2f(rec) * (float)rec[4 + j] * scale, mn = h2f(rec + 2) * (float)rec[12 + j] * scale;
+      const uint8_t* q = c + (k >> 1);
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        v[2 * e] = d * (float)(q[e] & 0xF) - mn;
+        v[2 * e + 1] = d * (float)(q[e] >> 4) - mn;
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 32; ++e) dst[k + e] = f2bf(v[e]);
+  }
+}
+
 }  // namespace
 
+// Rows tok[0 .. T) of a quantised embedding table (planes of format fmt: 1 Q8_0, 2 Q6_K, 3 Q4_K) decoded to
+// bf16 out [T, H], times `scale`.
+LK_API int lk_embed_q(int fmt, const int* tokens, const void* codes, long long c_ld, const void* scales, long long s_ld,
+                      void* out, int T, int H, int vocab, float scale, void* stream) {
+  if (T <= 0) return LKH_OK;
+  if (!tokens || !codes || !scales || !out || (H & 31) || ((fmt == GV_W8G16 || fmt == GV_W4) && (H & 255))) return LKH_BAD_ARG;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const uint8_t* c = reinterpret_cast<const uint8_t*>(codes);
+  const uint8_t* s = reinterpret_cast<const uint8_t*>(scales);
+  __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out);
+  switch (fmt) {
+    case GV_W8: embed_q_kernel<GV_W8><<<T, 128, 0, st>>>(tokens, c, c_ld, s, s_ld, o, H, vocab, scale); break;
+    case GV_W8G16: embed_q_kernel<GV_W8G16><<<T, 128, 0, st>>>(tokens, c, c_ld, s, s_ld, o, H, vocab, scale); break;
+    case GV_W4: embed_q_kernel<GV_W4><<<T, 128, 0, st>>>(tokens, c, c_ld, s, s_ld, o, H, vocab, scale); break;
+    default: return LKH_BAD_ARG;
+  }
+  lkh::count_launch();
+  return lkh::launch_status();
+}
+
 // x [M <= 8, K] bf16 (row pitch ldx elements), W as device planes of format `fmt` (1 Q8_0, 2 Q6_K, 3 Q4_K),
-// out [M, N] bf16 (row pitch ldo).  K a multiple of 32 (256 for the K formats).
+// out [M, N] bf16 or, with out_fp32, f32 (row pitch ldo elements).  K a multiple of 32 (256 for the K formats).
 LK_API int lk_gemv_q(int fmt, const void* codes, long long c_ld, const void* scales, long long s_ld, const void* x,
-                     long long ldx, int M, int N, int K, const float* bias, void* out, long long ldo, void* stream) {
+                     long long ldx, int M, int N, int K, const float* bias, void* out, long long ldo, int out_fp32,
+                     void* stream) {
   if (M <= 0 || N <= 0) return LKH_OK;
   if (M > 8 || !codes || !scales || !x || !out || (K & 31) || (ldx & 7)) return LKH_BAD_ARG;
   if ((fmt == GV_W8G16 || fmt == GV_W4) && (K & 255)) return LKH_BAD_ARG;
@@ -261,6 +337,7 @@ LK_API int lk_gemv_q(int fmt, const void* codes, long long c_ld, const void* sca
   p.bias = bias;
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
   p.ldo = ldo;
+  p.out_fp32 = out_fp32;
   p.M = M;
   p.N = N;
   p.K = K;

@@ -94,7 +94,11 @@ int lk_rope_kv(const void* qkv, long long ld, const int* pos, const int* slots, 
 // Quantised GEMV for 1..8 token rows: int8 activations (quantised per 32 values inside the kernel) and
 // dp4a over the stored codes.  fmt: 1 Q8_0, 2 Q6_K, 3 Q4_K planes of ops/quant.py.
 int lk_gemv_q(int fmt, const void* codes, long long c_ld, const void* scales, long long s_ld, const void* x,
-              long long ldx, int M, int N, int K, const float* bias, void* out, long long ldo, void* stream);
+              long long ldx, int M, int N, int K, const float* bias, void* out, long long ldo, int out_fp32,
+              void* stream);
+// Embedding gather from a quantised table (the same planes): rows tokens[0 .. T) decoded to bf16 out [T, H].
+int lk_embed_q(int fmt, const int* tokens, const void* codes, long long c_ld, const void* scales, long long s_ld,
+               void* out, int T, int H, int vocab, float scale, void* stream);
 int lk_kv_shift(void* k_cache, void* v_cache, void* k_scale, void* v_scale, const int* src, const int* dst,
                 const int* delta, int n, int n_kv, int hd, const float* inv_freq, int rope_dim, int pairing,
                 long long num_slots, int kv_q8, int* status, void* stream);

@@ -23,6 +23,7 @@ from .moe import MoeWeights
 from .weights import LayerWeights, Linear, ModelWeights, linear_format, make_linear
 
 QUANT_TYPES = {G.Q8_0: "q8_0", G.Q4_K: "q4_k", G.Q6_K: "q6_k", G.MXFP4: "mxfp4"}
+KEEP_QUANT_TABLES = True    # embedding table and output head of a quantised file stay in their block format on one rank
 FMT_TYPES = {v: k for k, v in QUANT_TYPES.items()}
 
 
@@ -136,11 +137,29 @@ def load_gguf(path: str, device, *, tp_rank: int = 0, tp_size: int = 1, ep_rank:
     q_sl = slice(tp_rank * nql * hd, (tp_rank + 1) * nql * hd)
     kv_sl = slice(kv_lo * hd, (kv_lo + nkvl) * hd)
     emb = T("token_embd.weight")
-    embed = torch.from_numpy(emb.floats()).to(device).bfloat16()
+
+    def keep_planes(src: _Src) -> bool:
+        """A table or head stays in its block format (decoded row by row in the gather, read by the GEMV up to
+        eight token rows) on one rank, when nothing asks for another format and the kernels know the type."""
+        return (KEEP_QUANT_TABLES and tp_size == 1 and requant is None and H % 256 == 0
+                and src.type in (G.Q8_0, G.Q6_K, G.Q4_K) and str(device).startswith("cuda"))
+
+    if keep_planes(emb):
+        from ..ops.quant import from_blocks
+
+        embed = from_blocks(emb.info.data, emb.type, emb.rows, emb.K, device)
+    else:
+        embed = torch.from_numpy(emb.floats()).to(device).bfloat16()
     if has("output.weight"):
         vl = cfg.vocab // tp_size if tp_size > 1 else cfg.vocab
         v_sl = slice(tp_rank * vl, (tp_rank + 1) * vl)
-        lm_head = torch.from_numpy(T("output.weight").floats(v_sl)).to(device).bfloat16()
+        osrc = T("output.weight")
+        if keep_planes(osrc):
+            from ..ops.quant import from_blocks
+
+            lm_head = from_blocks(osrc.info.data, osrc.type, osrc.rows, osrc.K, device)
+        else:
+            lm_head = torch.from_numpy(osrc.floats(v_sl)).to(device).bfloat16()
     else:
         cfg.tie_embeddings = True
         vl = cfg.vocab // tp_size if tp_size > 1 else cfg.vocab

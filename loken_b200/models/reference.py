@@ -15,7 +15,7 @@ import torch
 
 from ..ops.attention import attention_ref
 from .config import ModelConfig
-from .weights import ModelWeights, dequant_linear
+from .weights import embed_lookup, head_matrix, ModelWeights, dequant_linear
 
 
 def _rms(x, w, eps):
@@ -101,7 +101,7 @@ def forward_ref(w: ModelWeights, tokens: Sequence[int], *, bf16_stream: bool = T
     tok = torch.tensor(list(tokens), device=dev, dtype=torch.long)
     pos = torch.arange(T, device=dev)
     rd = lambda t: t.bfloat16().float() if bf16_stream else t
-    x = w.embed[tok].float() * cfg.embedding_scale
+    x = embed_lookup(w, tok) * cfg.embedding_scale
     hd, nq, nkv = cfg.head_dim, cfg.n_q, cfg.n_kv
     rope_dim = cfg.rope_dim or hd
     for il, lw in enumerate(w.layers):
@@ -139,4 +139,4 @@ def forward_ref(w: ModelWeights, tokens: Sequence[int], *, bf16_stream: bool = T
             d = act @ dequant_linear(lw.w_down).t()
         x = rd(x + rd(d))
     h = rd(_rms(x, w.out_norm, cfg.rms_eps))
-    return (h @ w.lm_head.float().t()) * cfg.logit_scale
+    return (h @ head_matrix(w).t()) * cfg.logit_scale

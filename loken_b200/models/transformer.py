@@ -182,7 +182,12 @@ class DecoderModel:
     def embed_rows(self, inp: StepInputs):
         T = inp.T
         assert T <= self.buf.cap
-        rows.embed(inp.tokens[:T], self.w.embed, out=self.buf.x[:T], scale=self.cfg.embedding_scale)
+        if isinstance(self.w.embed, torch.Tensor):
+            rows.embed(inp.tokens[:T], self.w.embed, out=self.buf.x[:T], scale=self.cfg.embedding_scale)
+        else:       # a table kept in its block format: rows are decoded as they are gathered
+            from ..ops import quant
+
+            quant.embed_gguf(inp.tokens[:T], self.w.embed, out=self.buf.x[:T], scale=self.cfg.embedding_scale)
         for r0, t in (inp.embed_overrides or ()):
             self.buf.x[r0:r0 + t.shape[0]].copy_(t)       # a prompt given as embedding rows takes the table's place
         self._delta_local = False
@@ -270,7 +275,12 @@ class DecoderModel:
         else:
             n = T
             hsrc = b.h
-        gemm.linear_bf16(hsrc[:n], w.lm_head, out=b.logits[:n], out_fp32=True)
+        if isinstance(w.lm_head, torch.Tensor):
+            gemm.linear_bf16(hsrc[:n], w.lm_head, out=b.logits[:n], out_fp32=True)
+        else:       # a head kept in its block format (GEMV on int8 activations up to eight rows)
+            from ..ops import quant
+
+            quant.linear_gguf(hsrc[:n], w.lm_head, out=b.logits[:n], out_fp32=True)
         logits = b.logits[:n]
         if cfg.logit_scale != 1.0:
             logits.mul_(cfg.logit_scale)

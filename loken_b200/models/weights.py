@@ -95,6 +95,24 @@ def _randn(gen, shape, std, device):
     return torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * std
 
 
+def embed_lookup(w: "ModelWeights", ids: torch.Tensor) -> torch.Tensor:
+    """Rows `ids` of the embedding table as fp32, whether the table is bf16 or held in a block format."""
+    t = w.embed
+    if isinstance(t, torch.Tensor):
+        return t[ids.long().to(t.device)].float()
+    return t.rows_float(ids)
+
+
+def head_matrix(w: "ModelWeights") -> torch.Tensor:
+    """The output head as fp32 [vocab_local, hidden] (oracles and exports; never the hot path)."""
+    t = w.lm_head
+    if isinstance(t, torch.Tensor):
+        return t.float()
+    from ..ops.quant import dequantize_weight
+
+    return dequantize_weight(t)
+
+
 def linear_format(cfg: ModelConfig, role: str) -> str:
     """Per-tensor storage format.  Q4_K_M mixes Q4_K with Q6_K for `ffn_down` / `attn_v`
     (reference: per-tensor `GgmlDType`, `gguf_file.rs:380-395`); gpt-oss keeps attention in bf16

@@ -44,6 +44,16 @@ class QuantWeight:
     def shape(self):
         return (self.rows, self.K)
 
+    @property
+    def device(self):
+        return self.codes.device
+
+    def rows_float(self, ids: torch.Tensor) -> torch.Tensor:
+        """fp32 [n, K]: the decoded rows `ids` (an embedding lookup in a quantised table, on any device)."""
+        ids = ids.long().to(self.codes.device)
+        sub = QuantWeight(self.aq_fmt, self.ggml_type, int(ids.numel()), self.K, self.codes[ids], self.scales[ids])
+        return dequantize_weight(sub)
+
     def nbytes(self) -> int:
         if self.aq_fmt == AQ_MX4:
             return self.codes.numel() + self.rows * (self.K // 32)       # without the pitch padding
@@ -159,15 +169,26 @@ def _pick_bn(rows: int) -> int:
 GEMV_MAX_M = 8          # up to this many token rows the dp4a GEMV runs (gemv_q.cu); 0 turns it off
 
 
+def embed_gguf(tokens: torch.Tensor, table: QuantWeight, out: Optional[torch.Tensor] = None, scale: float = 1.0):
+    """Rows `tokens` of a quantised embedding table (Q8_0 / Q6_K / Q4_K planes), decoded to bf16 [T, H]."""
+    T = tokens.numel()
+    if out is None:
+        out = torch.empty(T, table.K, dtype=torch.bfloat16, device=table.codes.device)
+    check(cuda_lib().lk_embed_q(table.aq_fmt, ptr(tokens), ptr(table.codes), C.c_longlong(table.codes.stride(0)),
+                                ptr(table.scales), C.c_longlong(table.scales.stride(0)), ptr(out), T, table.K, table.rows,
+                                C.c_float(scale), stream()), "lk_embed_q")
+    return out
+
+
 def linear_gguf(x: torch.Tensor, w: QuantWeight, *, bias: Optional[torch.Tensor] = None,
-                out: Optional[torch.Tensor] = None, splits: int = 0) -> torch.Tensor:
-    """x bf16 [M, K] @ W.T -> bf16 [M, N].  Tokens ride the MMA N dimension in tiles of
-    16 / 64 / 128, so decode (M = 1..8) and prefill use the same kernel."""
+                out: Optional[torch.Tensor] = None, splits: int = 0, out_fp32: bool = False) -> torch.Tensor:
+    """x bf16 [M, K] @ W.T -> bf16 (or f32) [M, N].  Up to eight token rows run as a GEMV on int8 activations;
+    beyond that tokens ride the MMA N dimension in tiles of 16 / 64 / 128 with dequantising warps."""
     M, K = x.shape
     N = w.rows
     assert K == w.K and x.stride(1) == 1
     if out is None:
-        out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+        out = torch.empty(M, N, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=x.device)
     if w.aq_fmt == AQ_MX4 and MX_NATIVE and K % 32 == 0:
         # MXFP4 runs as stored on the block-scaled tensor-core path: activations to e4m3 + E8M0 exponents
         # per 32 values, weights' nibbles and exponents straight into the MMA (ops/mx.py)
@@ -182,7 +203,7 @@ def linear_gguf(x: torch.Tensor, w: QuantWeight, *, bias: Optional[torch.Tensor]
         # a handful of token rows: int8 activations and dp4a over the stored codes, every weight byte read once
         check(cuda_lib().lk_gemv_q(w.aq_fmt, ptr(w.codes), C.c_longlong(w.codes.stride(0)), ptr(w.scales),
                                    C.c_longlong(w.scales.stride(0)), ptr(x), C.c_longlong(x.stride(0)), M, N, K,
-                                   ptr(bias), ptr(out), C.c_longlong(out.stride(0)), stream()), "lk_gemv_q")
+                                   ptr(bias), ptr(out), C.c_longlong(out.stride(0)), int(out_fp32), stream()), "lk_gemv_q")
         return out
     wsp = Workspace.get(x.device)
     bn = _pick_bn(M)
@@ -195,7 +216,7 @@ def linear_gguf(x: torch.Tensor, w: QuantWeight, *, bias: Optional[torch.Tensor]
     a.A, a.B = None, ptr(x)
     a.Ra, a.Rb, a.K = N, M, K
     a.lda, a.ldb = K, x.stride(0)
-    a.out, a.out_sa, a.out_sb = ptr(out), 1, out.stride(0)
+    a.out, a.out_sa, a.out_sb, a.out_fp32 = ptr(out), 1, out.stride(0), int(out_fp32)
     a.bias, a.bias_on_a = ptr(bias), 1
     a.bn, a.splits = bn, splits
     a.ws, a.ws_floats = ptr(wsp.ws), wsp.ws.numel()

@@ -28,6 +28,7 @@ from typing import Dict, List, Optional, Sequence as Seq
 
 import torch
 
+from ..models.weights import embed_lookup
 from .kv_manager import PagedKvAllocator
 from .scheduler import Sequence
 from .speculative import DRAFT_MAX, _RowView, _greedy_twin
@@ -173,7 +174,7 @@ class HeadDrafter:
                 continue
             toks = [t for t, _ in pend]
             f = torch.stack([x for _, x in pend])
-            e = self.tw.embed[torch.tensor(toks, device=f.device)] * self.cfg.embedding_scale
+            e = embed_lookup(self.tw, torch.tensor(toks, device=f.device)) * self.cfg.embedding_scale
             embs.append(head_input(self.head, e, f, eps))
             items.append((s, toks, start))
             lens.append(len(pend))
@@ -192,7 +193,8 @@ class HeadDrafter:
             pos.append(self.known[s.seq_id])
         for step in range(1, k):
             # the head's own prediction stands in for the feature it has not seen
-            e = self.tw.embed[torch.tensor([drafts[s.seq_id][-1] for s in live], device=feats.device)] * self.cfg.embedding_scale
+            e = embed_lookup(self.tw, torch.tensor([drafts[s.seq_id][-1] for s in live], device=feats.device)) \
+                * self.cfg.embedding_scale
             x = head_input(self.head, e, feats, eps)
             items = [(s, [drafts[s.seq_id][-1]], p + step - 1) for s, p in zip(live, pos)]
             logits = self.runner.forward_rows(items, self.alloc, last_only=True, embeds=x)

@@ -75,4 +75,52 @@ def test_tensor_parallel_shards_tile_the_model(tmp_path):
         assert torch.equal(gate, dequant_linear(f.w_gate_up)[:I])
         d = torch.cat([dequant_linear(s.layers[il].w_down) for s in shards], 1)
         assert torch.equal(d, dequant_linear(f.w_down))
-    assert torch.equal(torch.cat([s.lm_head for s in shards], 0), full.lm_head)
+    from loken_b200.models.weights import head_matrix
+
+    # one rank keeps the head in its block format; the shards hold its decoded rows in bf16
+    assert torch.equal(torch.cat([s.lm_head for s in shards], 0).float(), head_matrix(full).bfloat16().float())
+
+
+@pytest.mark.parametrize("fmt", ["q8_0", "q4_k_m"])
+def test_quantised_table_and_head_stay_in_their_block_format(tmp_path, fmt):
+    """On one rank the embedding table and the output head of a quantised file are not expanded: the gather
+    decodes rows, the head runs on the stored codes (GEMV up to eight rows, dequantising GEMM beyond)."""
+    from loken_b200.models import loader
+    from loken_b200.models.config import tiny
+    from loken_b200.models.reference import forward_ref
+    from loken_b200.models.weights import embed_lookup, head_matrix
+    from loken_b200.ops import quant
+    from loken_b200.serve.engine import LLMEngine
+    from loken_b200.serve.params import GREEDY
+
+    cfg = tiny("llama", weight_format=fmt, head_dim=64, n_q=4, n_kv=2, hidden=256, intermediate=512, vocab=1000)
+    path = os.path.join(tmp_path, "m.gguf")
+    loader.export_random_gguf(path, cfg, seed=8, std=0.05)
+    w, _ = loader.load_gguf(path, torch.device(DEV))
+    assert isinstance(w.embed, quant.QuantWeight) and isinstance(w.lm_head, quant.QuantWeight)
+    ids = torch.tensor([0, 5, 999, 5], device=DEV, dtype=torch.int32)
+    got = quant.embed_gguf(ids, w.embed)
+    assert torch.equal(got.float(), embed_lookup(w, ids).bfloat16().float())
+    x = (torch.randn(20, cfg.hidden, device=DEV) * 0.5).bfloat16()
+    ref = x.float() @ head_matrix(w).t()
+    for m in (1, 3, 20):
+        out = quant.linear_gguf(x[:m], w.lm_head, out_fp32=True)
+        assert out.dtype == torch.float32
+        assert ((out - ref[:m]).abs().max() / ref.abs().max()).item() < 2e-2
+    eng = LLMEngine(w.cfg, weights=w, num_blocks=64, max_seqs=8, max_prefill_tokens=512, max_ctx=512, use_graphs=False)
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, cfg.vocab, (23,), generator=g).tolist()
+    want = forward_ref(w, prompt)
+    sid = eng.add_request(prompt, GREEDY)
+    eng.step()
+    assert _cos(eng.runner.model.buf.logits[0], want[-1]) > 0.998
+    for _ in range(3):
+        eng.step()                                  # decode steps: embedding gather and head on one row
+    assert len(eng.seqs[sid].output) == 4 and eng.runner.wsp.read_status() == 0
+    old = loader.KEEP_QUANT_TABLES
+    try:
+        loader.KEEP_QUANT_TABLES = False
+        w2, _ = loader.load_gguf(path, torch.device(DEV))
+    finally:
+        loader.KEEP_QUANT_TABLES = old
+    assert isinstance(w2.embed, torch.Tensor) and torch.equal(w2.embed.float(), embed_lookup(w, torch.arange(1000)).bfloat16().float())
