@@ -68,7 +68,6 @@ __global__ void __launch_bounds__(192, 2)
 attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                       const DecodeParamsV2 p) {
   pdl_wait();
-  pdl_launch();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* pb = smem + STAGES * STAGE_BYTES;               // 4 B tiles of P, 2 KB each
@@ -147,6 +146,9 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const uint32_t tmem_s = tmem, tmem_o = tmem + 64;
+  // only now may the next kernel be scheduled: it allocates tensor memory in its prologue, before it waits
+  // for this one, and must not take the columns this CTA was about to ask for
+  pdl_launch();
 
   if (warp == 4) {
     // ------------------------------ TMA producer ------------------------------

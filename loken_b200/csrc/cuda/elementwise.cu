@@ -81,8 +81,8 @@ add_rmsnorm_kernel(__nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restric
                    const float* __restrict__ delta_f32, const float* __restrict__ w, float eps, int H,
                    __nv_bfloat16* __restrict__ out_bf16, uint8_t* __restrict__ out_fp8,
                    float* __restrict__ scales_t, long long scale_ld, int write_x) {
+  pdl_launch();      // nothing is written before the wait: the kernel after this one may set up behind it
   pdl_wait();
-  pdl_launch();
   __shared__ float red[32];
   const int row = blockIdx.x;
   __nv_bfloat16* xr = x + (long long)row * H;
@@ -145,8 +145,8 @@ __global__ void __launch_bounds__(ROW_THREADS)
 glu_kernel(const __nv_bfloat16* __restrict__ gu, long long ld_in, int I, int mode, float alpha, float limit,
            __nv_bfloat16* __restrict__ out_bf16, uint8_t* __restrict__ out_fp8, float* __restrict__ scales_t,
            long long scale_ld) {
+  pdl_launch();      // nothing is written before the wait: the kernel after this one may set up behind it
   pdl_wait();
-  pdl_launch();
   const int row = blockIdx.y;
   const int c = blockIdx.x * ROW_THREADS + threadIdx.x;  // chunk of 8
   const int nchunk = I >> 3;
@@ -192,8 +192,8 @@ glu_kernel(const __nv_bfloat16* __restrict__ gu, long long ld_in, int I, int mod
 __global__ void __launch_bounds__(ROW_THREADS)
 quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, long long ld_in, int K, uint8_t* __restrict__ out,
                  float* __restrict__ scales_t, long long scale_ld) {
+  pdl_launch();      // nothing is written before the wait: the kernel after this one may set up behind it
   pdl_wait();
-  pdl_launch();
   const int row = blockIdx.y;
   const int c = blockIdx.x * ROW_THREADS + threadIdx.x;
   const bool live = c < (K >> 3);

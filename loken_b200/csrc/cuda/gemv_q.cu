@@ -43,6 +43,13 @@ __device__ __forceinline__ int dp4a_u8s8(uint32_t a, uint32_t b, int c) {
   asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
   return d;
 }
+// hints: bring [p, p + bytes) (16-byte aligned, a multiple of 16 bytes) or the line of p into L2
+__device__ __forceinline__ void l2_prefetch_bulk(const void* p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void l2_prefetch_line(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
 __device__ __forceinline__ float h2f(const uint8_t* p) {
   return __half2float(*reinterpret_cast<const __half*>(p));
 }
@@ -64,6 +71,24 @@ struct GvParams {
 template <int FMT, int MT, int RW>
 __global__ void __launch_bounds__(GV_WARPS * 32)
 gemv_q_kernel(const GvParams p) {
+  // The weights do not depend on the kernel before this one, and this grid is resident while that kernel
+  // still runs (programmatic launch).  So first ask for this CTA's rows to be brought into L2: the weights
+  // of a decode step then stream through the stretches in which the small kernels between two GEMVs leave
+  // the memory system idle, and the loads below find them on the chip.
+  {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_rg = (p.N + GV_WARPS * RW - 1) / (GV_WARPS * RW);
+    const uint32_t code_bytes = FMT == GV_W4 ? p.K >> 1 : p.K;
+    for (int rg = blockIdx.x; rg < n_rg; rg += gridDim.x) {
+      const int row0 = (rg * GV_WARPS + warp) * RW;
+      if (row0 >= p.N) continue;
+      const int nrows = min(RW, p.N - row0);
+      if (lane < nrows) l2_prefetch_bulk(p.codes + (long long)(row0 + lane) * p.c_ld, code_bytes);
+      const uint8_t* sb = p.scales + (long long)row0 * p.s_ld;
+      const long long span = (long long)nrows * p.s_ld;
+      for (long long off = lane * 128ll; off < span; off += 32 * 128) l2_prefetch_line(sb + off);
+    }
+  }
   pdl_wait();
   pdl_launch();
   // the activations of the whole row, quantised once per CTA: codes as words (for Q4_K de-interleaved per 8
@@ -152,7 +177,7 @@ gemv_q_kernel(const GvParams p) {
         const int n = min(row0 + r, p.N - 1);          // rows past the end repeat the last one; never stored
         if (FMT == GV_W8) {
           const uint4* c = reinterpret_cast<const uint4*>(p.codes + (long long)n * p.c_ld + k);
-          const uint4 c0 = __ldg(c), c1 = __ldg(c + 1);
+          const uint4 c0 = __ldcs(c), c1 = __ldcs(c + 1);
           const float dw = h2f(p.scales + (long long)n * p.s_ld + (k >> 5) * 2);
           const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
 #pragma unroll
@@ -164,7 +189,7 @@ gemv_q_kernel(const GvParams p) {
           }
         } else if (FMT == GV_W8G16) {
           const uint4* c = reinterpret_cast<const uint4*>(p.codes + (long long)n * p.c_ld + k);
-          const uint4 c0 = __ldg(c), c1 = __ldg(c + 1);
+          const uint4 c0 = __ldcs(c), c1 = __ldcs(c + 1);
           const uint8_t* rec = p.scales + (long long)n * p.s_ld + (k >> 8) * 18;
           const float d = h2f(rec);
           const int j = (k & 255) >> 4;                  // first of this group's two sub-scales
@@ -182,7 +207,7 @@ gemv_q_kernel(const GvParams p) {
             acc[r][m] = fmaf(dx[m], s0 * (float)a + s1 * (float)b, acc[r][m]);
           }
         } else {
-          const uint4 c0 = __ldg(reinterpret_cast<const uint4*>(p.codes + (long long)n * p.c_ld + (k >> 1)));
+          const uint4 c0 = __ldcs(reinterpret_cast<const uint4*>(p.codes + (long long)n * p.c_ld + (k >> 1)));
           const uint8_t* rec = p.scales + (long long)n * p.s_ld + (k >> 8) * 20;
           const int j = (k & 255) >> 5;
           const uint32_t dd = *reinterpret_cast<const uint32_t*>(rec);          // d and dmin: records are 4-byte aligned
@@ -235,7 +260,10 @@ int launch_gv(const GvParams& p, cudaStream_t st) {
   // every CTA quantises the activations once, then walks row groups: a few CTAs per SM, not one per group
   const int n_rg = (p.N + GV_WARPS * RW - 1) / (GV_WARPS * RW);
   const int per_sm = smem > 100 * 1024 ? 1 : smem > 48 * 1024 ? 2 : 3;
-  const int grid = n_rg < 148 * per_sm ? n_rg : 148 * per_sm;
+  // every CTA walks the same number of row groups (a capped grid with a remainder leaves most SMs idle for
+  // the last pass: 896 groups over 444 CTAs are two passes plus a third for eight of them)
+  const int passes = (n_rg + 148 * per_sm - 1) / (148 * per_sm);
+  const int grid = (n_rg + passes - 1) / passes;
   lkh::launch_pdl(kern, dim3(grid), dim3(GV_WARPS * 32), smem, st, p);
   return 0;
 }
@@ -296,7 +324,97 @@ embed_q_kernel(const int* __restrict__ tok, const uint8_t* __restrict__ codes, l
   }
 }
 
+// The whole matrix decoded to bf16 [rows, K] (row pitch ldo elements): what a prompt-sized GEMM multiplies by.
+// A thread decodes one group of 32 values (16 or 32 code bytes in, 64 bytes out); groups are walked in
+// storage order, so a warp reads and writes contiguous runs.
+template <int FMT>
+__global__ void __launch_bounds__(256)
+dequant_q_kernel(const uint8_t* __restrict__ codes, long long c_ld, const uint8_t* __restrict__ scales, long long s_ld,
+                 __nv_bfloat16* __restrict__ out, long long ldo, int rows, int K) {
+  pdl_wait();
+  pdl_launch();
+  const int ngroups = K >> 5;
+  const long long total = (long long)rows * ngroups;
+  for (long long g = blockIdx.x * 256ll + threadIdx.x; g < total; g += (long long)gridDim.x * 256) {
+    const int n = (int)(g / ngroups), gi = (int)(g % ngroups);
+    const int k = gi << 5;
+    const uint8_t* c = codes + (long long)n * c_ld;
+    const uint8_t* s = scales + (long long)n * s_ld;
+    float v[32];
+    if (FMT == GV_W8 || FMT == GV_W8G16) {
+      const uint4* cp = reinterpret_cast<const uint4*>(c + k);
+      const uint4 c0 = __ldg(cp), c1 = __ldg(cp + 1);
+      const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+      float s0, s1;
+      if (FMT == GV_W8) {
+        s0 = s1 = h2f(s + gi * 2);
+      } else {
+        const uint8_t* rec = s + (k >> 8) * 18;
+        const float d = h2f(rec);
+        const int j = (k & 255) >> 4;
+        s0 = d * (float)(int8_t)rec[2 + j];
+        s1 = d * (float)(int8_t)rec[3 + j];
+      }
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const float sc = q < 4 ? s0 : s1;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[q * 4 + e] = sc * (float)(int8_t)((cw[q] >> (8 * e)) & 0xFF);
+      }
+    } else {
+      const uint4 c0 = __ldg(reinterpret_cast<const uint4*>(c + (k >> 1)));
+      const uint8_t* rec = s + (k >> 8) * 20;
+      const int j = (k & 255) >> 5;
+      const float d = h2f(rec) * (float)rec[4 + j], mn = h2f(rec + 2) * (float)rec[12 + j];
+      const uint32_t cw[4] = {c0.x, c0.y, c0.z, c0.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const uint32_t b = (cw[q] >> (8 * e)) & 0xFF;
+          v[q * 8 + 2 * e] = d * (float)(b & 0xF) - mn;
+          v[q * 8 + 2 * e + 1] = d * (float)(b >> 4) - mn;
+        }
+    }
+    uint4* dst = reinterpret_cast<uint4*>(out + (long long)n * ldo + k);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint32_t w[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(v[q * 8 + 2 * e], v[q * 8 + 2 * e + 1]);
+        w[e] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+      dst[q] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
 }  // namespace
+
+// Planes of format fmt (1 Q8_0, 2 Q6_K, 3 Q4_K) decoded to bf16 out [rows, K], row pitch ldo elements (a
+// multiple of 8, base 16-byte aligned).
+LK_API int lk_dequant_q(int fmt, const void* codes, long long c_ld, const void* scales, long long s_ld, void* out,
+                        long long ldo, int rows, int K, void* stream) {
+  if (rows <= 0 || K <= 0) return LKH_OK;
+  if (!codes || !scales || !out || (K & 31) || (ldo & 7) || ((fmt == GV_W8G16 || fmt == GV_W4) && (K & 255))) return LKH_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(codes) & 15) || (c_ld & 15) || (reinterpret_cast<uintptr_t>(out) & 15)) return LKH_BAD_ARG;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const uint8_t* c = reinterpret_cast<const uint8_t*>(codes);
+  const uint8_t* s = reinterpret_cast<const uint8_t*>(scales);
+  __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out);
+  const long long total = (long long)rows * (K >> 5);
+  const long long want = (total + 255) / 256;
+  const dim3 grid((unsigned)(want < 148 * 16 ? want : 148 * 16));
+  switch (fmt) {
+    case GV_W8: lkh::launch_pdl(dequant_q_kernel<GV_W8>, grid, dim3(256), 0, st, c, c_ld, s, s_ld, o, ldo, rows, K); break;
+    case GV_W8G16: lkh::launch_pdl(dequant_q_kernel<GV_W8G16>, grid, dim3(256), 0, st, c, c_ld, s, s_ld, o, ldo, rows, K); break;
+    case GV_W4: lkh::launch_pdl(dequant_q_kernel<GV_W4>, grid, dim3(256), 0, st, c, c_ld, s, s_ld, o, ldo, rows, K); break;
+    default: return LKH_BAD_ARG;
+  }
+  lkh::count_launch();
+  return lkh::launch_status();
+}
 
 // Rows tok[0 .. T) of a quantised embedding table (planes of format fmt: 1 Q8_0, 2 Q6_K, 3 Q4_K) decoded to
 // bf16 out [T, H], times `scale`.

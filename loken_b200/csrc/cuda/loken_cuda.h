@@ -96,6 +96,9 @@ int lk_rope_kv(const void* qkv, long long ld, const int* pos, const int* slots, 
 int lk_gemv_q(int fmt, const void* codes, long long c_ld, const void* scales, long long s_ld, const void* x,
               long long ldx, int M, int N, int K, const float* bias, void* out, long long ldo, int out_fp32,
               void* stream);
+// The same planes decoded to bf16 out [rows, K], row pitch ldo elements: the operand of prompt-sized GEMMs.
+int lk_dequant_q(int fmt, const void* codes, long long c_ld, const void* scales, long long s_ld, void* out,
+                 long long ldo, int rows, int K, void* stream);
 // Embedding gather from a quantised table (the same planes): rows tokens[0 .. T) decoded to bf16 out [T, H].
 int lk_embed_q(int fmt, const int* tokens, const void* codes, long long c_ld, const void* scales, long long s_ld,
                void* out, int T, int H, int vocab, float scale, void* stream);

@@ -30,8 +30,8 @@ rope_kv_kernel(const __nv_bfloat16* __restrict__ qkv, long long ld, const int* _
                int pairing, float mscale, __nv_bfloat16* __restrict__ q_out, void* __restrict__ k_cache,
                void* __restrict__ v_cache, __half* __restrict__ k_scale, __half* __restrict__ v_scale,
                long long num_slots, int kv_q8, int* __restrict__ status) {
+  pdl_launch();      // nothing is written before the wait: the kernel after this one may set up behind it
   pdl_wait();
-  pdl_launch();
   constexpr int EPL = HD / 32;  // values per lane
   __shared__ float sh[4][HD];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;

@@ -167,6 +167,37 @@ def _pick_bn(rows: int) -> int:
 
 
 GEMV_MAX_M = 8          # up to this many token rows the dp4a GEMV runs (gemv_q.cu); 0 turns it off
+# From this many token rows on, a GGUF matrix is decoded to bf16 once (in row chunks that stay in L2) and
+# multiplied by the plain bf16 GEMM: the dequantising warps of the fused kernel decode every weight tile
+# again for every 128 tokens and top out near 1e12 values/s, a fifth of what the tensor cores could take
+# (Llama-8B gate/up, 1024 tokens: 1.03 ms fused).  0 turns it off.
+DEQUANT_ONCE_MIN_M = 129
+DEQUANT_CHUNK_BYTES = 48 << 20
+_scratch = {}
+
+
+def dequant_rows(w: QuantWeight, n0: int, n1: int, out: torch.Tensor) -> torch.Tensor:
+    """Rows [n0, n1) of `w` (Q8_0 / Q6_K / Q4_K planes) decoded to bf16 into out [n1 - n0, K]."""
+    check(cuda_lib().lk_dequant_q(w.aq_fmt, ptr(w.codes[n0:]), C.c_longlong(w.codes.stride(0)), ptr(w.scales[n0:]),
+                                  C.c_longlong(w.scales.stride(0)), ptr(out), C.c_longlong(out.stride(0)), n1 - n0, w.K,
+                                  stream()), "lk_dequant_q")
+    return out
+
+
+def _linear_dequant_once(x, w: QuantWeight, bias, out, out_fp32):
+    from .gemm import linear_bf16
+
+    N, K = w.rows, w.K
+    per = max(128, DEQUANT_CHUNK_BYTES // (2 * K) // 128 * 128)
+    key = (x.device, per * K)
+    buf = _scratch.get(key)
+    if buf is None:
+        buf = _scratch[key] = torch.empty(per * K, dtype=torch.bfloat16, device=x.device)
+    for n0 in range(0, N, per):
+        n1 = min(N, n0 + per)
+        wt = dequant_rows(w, n0, n1, buf[:(n1 - n0) * K].view(n1 - n0, K))
+        linear_bf16(x, wt, bias=None if bias is None else bias[n0:n1], out=out[:, n0:n1], out_fp32=out_fp32)
+    return out
 
 
 def embed_gguf(tokens: torch.Tensor, table: QuantWeight, out: Optional[torch.Tensor] = None, scale: float = 1.0):
@@ -205,6 +236,9 @@ def linear_gguf(x: torch.Tensor, w: QuantWeight, *, bias: Optional[torch.Tensor]
                                    C.c_longlong(w.scales.stride(0)), ptr(x), C.c_longlong(x.stride(0)), M, N, K,
                                    ptr(bias), ptr(out), C.c_longlong(out.stride(0)), int(out_fp32), stream()), "lk_gemv_q")
         return out
+    if DEQUANT_ONCE_MIN_M and M >= DEQUANT_ONCE_MIN_M and w.aq_fmt in (AQ_W8, AQ_W8G16, AQ_W4) and K % 8 == 0 \
+            and out.stride(0) % 8 == 0:
+        return _linear_dequant_once(x, w, bias, out, out_fp32)
     wsp = Workspace.get(x.device)
     bn = _pick_bn(M)
     tiles = ((N + 127) // 128) * ((M + bn - 1) // bn)

@@ -80,3 +80,34 @@ def test_gemv_dp4a_matches_the_integer_product_and_the_gemm(fmt, M, N, K):
     assert rel_err(out, gemm) < 2e-2                   # the reference's bar for 8-bit activations
     again = quant.linear_gguf(x, q, bias=bias)
     assert torch.equal(out, again)
+
+
+@pytest.mark.parametrize("fmt", ["q8_0", "q4_k", "q6_k"])
+@pytest.mark.parametrize("M,N,K", [(129, 1000, 512), (700, 2304, 1024)])
+def test_prompt_sized_gemm_decodes_the_matrix_once(fmt, M, N, K):
+    """From 129 token rows on the planes are decoded to bf16 in row chunks and the bf16 GEMM multiplies:
+    the decoded rows equal the reference decode, and the product equals the fused kernel's."""
+    from loken_b200.ops import quant
+    from loken_b200.ops._lib import Workspace
+
+    torch.manual_seed(N + K)
+    q = quant.quantize_weight(torch.randn(N, K, device=DEV) * 0.05, fmt)
+    wd = quant.dequantize_weight(q)
+    got = quant.dequant_rows(q, 128, N, torch.empty(N - 128, K, dtype=torch.bfloat16, device=DEV))
+    assert (got.float() - wd[128:]).abs().max().item() <= wd.abs().max().item() * 2.0 ** -7
+    x = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+    bias = torch.randn(N, device=DEV)
+    ref = x.float() @ wd.bfloat16().float().t() + bias
+    old = quant.DEQUANT_ONCE_MIN_M, quant.DEQUANT_CHUNK_BYTES
+    try:
+        quant.DEQUANT_CHUNK_BYTES = 256 * K * 2            # several chunks, the last one ragged
+        once = quant.linear_gguf(x, q, bias=bias)
+        once32 = quant.linear_gguf(x, q, bias=bias, out_fp32=True)
+        quant.DEQUANT_ONCE_MIN_M = 0
+        fused = quant.linear_gguf(x, q, bias=bias)
+    finally:
+        quant.DEQUANT_ONCE_MIN_M, quant.DEQUANT_CHUNK_BYTES = old
+    torch.cuda.synchronize()
+    assert Workspace.get(torch.device(DEV)).read_status() == 0
+    assert once32.dtype == torch.float32
+    assert rel_err(once, ref) < 1e-2 and rel_err(once32, ref) < 2e-3 and rel_err(once, fused) < 1e-2
