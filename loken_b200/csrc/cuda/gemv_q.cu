@@ -25,6 +25,7 @@
 #include "common.cuh"
 #include "host_common.h"
 #include "loken_cuda.h"
+#include "tc100.cuh"
 
 using namespace lk;
 
@@ -67,6 +68,58 @@ struct GvParams {
   int out_fp32;
 };
 
+// One group of 32 activations of token row m to int8: codes as words (for Q4_K de-interleaved per 8 values,
+// even values then odd ones, to line up with the nibble planes), scale and sum of the group.
+template <int FMT>
+__device__ __forceinline__ void quantise_group(const GvParams& p, int m, int gi, uint32_t* xq, float* xd, float* xs,
+                                               int ngroups) {
+  float v[32];
+  if (m < p.M) {
+    const uint4* src = reinterpret_cast<const uint4*>(p.x + (long long)m * p.ldx + gi * 32);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint4 u = src[q];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        v[q * 8 + 2 * e] = f.x;
+        v[q * 8 + 2 * e + 1] = f.y;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < 32; ++e) v[e] = 0.f;
+  }
+  float amax = 0.f, sum = 0.f;
+#pragma unroll
+  for (int e = 0; e < 32; ++e) {
+    amax = fmaxf(amax, fabsf(v[e]));
+    sum += v[e];
+  }
+  const float d = amax * (1.f / 127.f);
+  const float id = d > 0.f ? 1.f / d : 0.f;
+  uint32_t wq[8];
+#pragma unroll
+  for (int w8 = 0; w8 < 4; ++w8) {
+    int q8[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) q8[e] = __float2int_rn(v[w8 * 8 + e] * id) & 0xFF;
+    if (FMT == GV_W4) {
+      wq[2 * w8] = q8[0] | (q8[2] << 8) | (q8[4] << 16) | (q8[6] << 24);
+      wq[2 * w8 + 1] = q8[1] | (q8[3] << 8) | (q8[5] << 16) | (q8[7] << 24);
+    } else {
+      wq[2 * w8] = q8[0] | (q8[1] << 8) | (q8[2] << 16) | (q8[3] << 24);
+      wq[2 * w8 + 1] = q8[4] | (q8[5] << 8) | (q8[6] << 16) | (q8[7] << 24);
+    }
+  }
+  uint4* dst = reinterpret_cast<uint4*>(xq + (size_t)m * (p.K >> 2) + gi * 8);
+  dst[0] = make_uint4(wq[0], wq[1], wq[2], wq[3]);
+  dst[1] = make_uint4(wq[4], wq[5], wq[6], wq[7]);
+  xd[m * ngroups + gi] = d;
+  xs[m * ngroups + gi] = sum;
+}
+
 // FMT: block format; MT: token rows (1, 2, 4 or 8); RW: output rows per warp and pass
 template <int FMT, int MT, int RW>
 __global__ void __launch_bounds__(GV_WARPS * 32)
@@ -93,7 +146,7 @@ gemv_q_kernel(const GvParams p) {
   pdl_launch();
   // the activations of the whole row, quantised once per CTA: codes as words (for Q4_K de-interleaved per 8
   // values, even values then odd ones, to line up with the nibble planes), scale and sum per 32-value group
-  extern __shared__ __align__(16) uint8_t gv_smem[];
+  extern __shared__ __align__(128) uint8_t gv_smem[];
   const int ngroups = p.K >> 5;
   uint32_t* xq = reinterpret_cast<uint32_t*>(gv_smem);                         // [MT][K / 4]
   float* xd = reinterpret_cast<float*>(gv_smem + (size_t)MT * p.K);            // [MT][K / 32]
@@ -101,51 +154,7 @@ gemv_q_kernel(const GvParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int g = threadIdx.x; g < MT * ngroups; g += GV_WARPS * 32) {
     const int m = g / ngroups, gi = g % ngroups;
-    float v[32];
-    if (m < p.M) {
-      const uint4* src = reinterpret_cast<const uint4*>(p.x + (long long)m * p.ldx + gi * 32);
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const uint4 u = src[q];
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f = __bfloat1622float2(h[e]);
-          v[q * 8 + 2 * e] = f.x;
-          v[q * 8 + 2 * e + 1] = f.y;
-        }
-      }
-    } else {
-#pragma unroll
-      for (int e = 0; e < 32; ++e) v[e] = 0.f;
-    }
-    float amax = 0.f, sum = 0.f;
-#pragma unroll
-    for (int e = 0; e < 32; ++e) {
-      amax = fmaxf(amax, fabsf(v[e]));
-      sum += v[e];
-    }
-    const float d = amax * (1.f / 127.f);
-    const float id = d > 0.f ? 1.f / d : 0.f;
-    uint32_t wq[8];
-#pragma unroll
-    for (int w8 = 0; w8 < 4; ++w8) {
-      int q8[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) q8[e] = __float2int_rn(v[w8 * 8 + e] * id) & 0xFF;
-      if (FMT == GV_W4) {
-        wq[2 * w8] = q8[0] | (q8[2] << 8) | (q8[4] << 16) | (q8[6] << 24);
-        wq[2 * w8 + 1] = q8[1] | (q8[3] << 8) | (q8[5] << 16) | (q8[7] << 24);
-      } else {
-        wq[2 * w8] = q8[0] | (q8[1] << 8) | (q8[2] << 16) | (q8[3] << 24);
-        wq[2 * w8 + 1] = q8[4] | (q8[5] << 8) | (q8[6] << 16) | (q8[7] << 24);
-      }
-    }
-    uint4* dst = reinterpret_cast<uint4*>(xq + (size_t)m * (p.K >> 2) + gi * 8);
-    dst[0] = make_uint4(wq[0], wq[1], wq[2], wq[3]);
-    dst[1] = make_uint4(wq[4], wq[5], wq[6], wq[7]);
-    xd[m * ngroups + gi] = d;
-    xs[m * ngroups + gi] = sum;
+    quantise_group<FMT>(p, m, gi, xq, xd, xs, ngroups);
   }
   __syncthreads();
 
@@ -245,6 +254,285 @@ gemv_q_kernel(const GvParams p) {
   }
 }
 
+// ---- the streaming form ---------------------------------------------------------------------------------
+// The form above keeps few bytes in flight: a lane's loads of one pass are all it has outstanding, and a
+// GEMV of 10 to 60 MB took 10 to 22 us even with its weights already in L2.  Here a producer warp streams
+// the CTA's rows through a ring of shared-memory stages with bulk asynchronous copies, so tens of KB per
+// CTA are on their way at any time, and it does not wait for the kernel before this one (weights do not
+// depend on it): by the time the activations exist the ring is full.
+//
+// A stage holds R whole rows (8, 4, 2 or 1: what fits 64 KB) and is filled by TWO copies, the rows' codes
+// and the rows' scale records, both contiguous in their planes.  (A first form copied 2048 values of one
+// row at a time, sixteen copies of 0.1 to 2 KB per stage: a stage then took 1.2 to 1.4 us whatever its
+// size, the rate at which the copy engine takes requests.)  The eight consumer warps split a stage into
+// R / RWP row groups times KS slices of K; a warp holds the activations of a group of 32 values in
+// registers for its RWP rows.  Partial sums meet in shared memory, one barrier per stage.
+constexpr int GS_WARPS = 8;                 // consumer warps
+constexpr int GS_THREADS = (GS_WARPS + 1) * 32;
+
+template <int FMT>
+__host__ __device__ constexpr int gs_code_bytes(int vals) { return FMT == GV_W4 ? vals / 2 : vals; }
+template <int FMT>
+__host__ __device__ constexpr int gs_scale_bytes(int vals) {
+  return FMT == GV_W8 ? vals / 16 : FMT == GV_W8G16 ? vals / 256 * 18 : vals / 256 * 20;
+}
+
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(GS_WARPS * 32) : "memory"); }
+
+// R: rows per stage; RWP: rows per warp; S: stages.  Row pitches equal the row sizes (contiguous planes).
+template <int FMT, int MT, int R, int RWP>
+__global__ void __launch_bounds__(GS_THREADS)
+gemv_q_stream_kernel(const GvParams p, int S, long long l2_budget, int* status) {
+  constexpr int NRG = R / RWP;             // row groups of a stage
+  constexpr int KS = GS_WARPS / NRG;       // warps per row group, each takes every KS-th run of 32 groups
+  static_assert(R % RWP == 0 && GS_WARPS % NRG == 0, "stage geometry");
+  extern __shared__ __align__(128) uint8_t gv_smem[];
+  const int ngroups = p.K >> 5;
+  uint32_t* xq = reinterpret_cast<uint32_t*>(gv_smem);                         // [MT][K / 4]
+  float* xd = reinterpret_cast<float*>(gv_smem + (size_t)MT * p.K);            // [MT][K / 32]
+  float* xs = xd + MT * ngroups;                                               // [MT][K / 32]
+  const int cb = gs_code_bytes<FMT>(p.K), sb = gs_scale_bytes<FMT>(p.K);       // bytes of a row in each plane
+  const int pitch = (R * (cb + sb) + 127) & ~127;
+  uint8_t* stages = gv_smem + (((size_t)MT * p.K + (size_t)MT * ngroups * 8 + 127) & ~(size_t)127);
+  float* part = reinterpret_cast<float*>(stages + (size_t)S * pitch);          // [2][GS_WARPS][RWP * MT]
+  uint64_t* full = reinterpret_cast<uint64_t*>(part + 2 * GS_WARPS * RWP * MT);
+  uint64_t* empty = full + S;
+  CtaAbort* ab = reinterpret_cast<CtaAbort*>(empty + S);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nblk = (p.N + R - 1) / R;
+  const int b0 = (int)((long long)blockIdx.x * nblk / gridDim.x);
+  const int b1 = (int)((long long)(blockIdx.x + 1) * nblk / gridDim.x);
+  const int nitems = b1 - b0;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], GS_WARPS);
+    }
+    ab->flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+
+  if (warp == GS_WARPS) {
+    // ------------------------------ producer ------------------------------
+    // what the ring cannot hold yet is at least asked into L2 (up to this CTA's share of a budget that fits
+    // there), so that it arrives while the kernels before this one leave the memory system idle
+    {
+      const long long r0 = (long long)b0 * R, r1 = min((long long)p.N, (long long)b1 * R);
+      const long long rows = min(r1 - r0, l2_budget / (cb + sb));
+      const uint8_t* c0 = p.codes + r0 * cb;
+      const uint8_t* s0 = p.scales + r0 * sb;
+      for (long long off = lane * 4096ll; off < rows * cb; off += 32 * 4096)
+        l2_prefetch_bulk(c0 + off, (uint32_t)min(4096ll, rows * cb - off));
+      for (long long off = lane * 128ll; off < rows * sb; off += 32 * 128) l2_prefetch_line(s0 + off);
+    }
+    for (int it = 0; it < nitems; ++it) {
+      const int s = it % S;
+      if (!mbar_wait(&empty[s], ((it / S) & 1) ^ 1, ab, status, 1)) break;
+      const long long row0 = (long long)(b0 + it) * R;
+      const int nvalid = (int)min((long long)R, p.N - row0);
+      uint8_t* st = stages + (size_t)s * pitch;
+      if (lane == 0) {
+        mbar_expect_tx(&full[s], (uint32_t)(nvalid * (cb + sb)));
+        bulk_g2s(st, p.codes + row0 * cb, (uint32_t)(nvalid * cb), &full[s]);
+        bulk_g2s(st + R * cb, p.scales + row0 * sb, (uint32_t)(nvalid * sb), &full[s]);
+      }
+      __syncwarp();
+    }
+    return;
+  }
+
+  // ------------------------------ consumers ------------------------------
+  pdl_wait();
+  pdl_launch();
+  for (int g = threadIdx.x; g < MT * ngroups; g += GS_WARPS * 32) {
+    const int m = g / ngroups, gi = g % ngroups;
+    quantise_group<FMT>(p, m, gi, xq, xd, xs, ngroups);
+  }
+  consumer_sync();
+
+  const int rgp = warp / KS, ks = warp % KS;
+  bool dead = false;                       // a wait gave up: no more waits, but every barrier below is still met
+  for (int it = 0; it < nitems; ++it) {
+    const int s = it % S;
+    if (!dead && !mbar_wait(&full[s], (it / S) & 1, ab, status, 2)) dead = true;
+    const long long row0 = (long long)(b0 + it) * R;
+    const uint8_t* st = stages + (size_t)s * pitch;
+    const uint8_t* cbase = st + (size_t)(rgp * RWP) * cb;
+    const uint8_t* sbase = st + (size_t)R * cb + (size_t)(rgp * RWP) * sb;
+    // rows of this warp that exist (the copy did not write rows past the matrix)
+    const int live = dead ? 0 : (int)min((long long)RWP, p.N - (row0 + rgp * RWP));
+    float acc[RWP][MT];
+#pragma unroll
+    for (int r = 0; r < RWP; ++r)
+#pragma unroll
+      for (int m = 0; m < MT; ++m) acc[r][m] = 0.f;
+#pragma unroll(MT <= 2 ? 2 : 1)
+    for (int g = ks * 32 + lane; g < (live > 0 ? ngroups : 0); g += KS * 32) {
+      uint32_t xw[MT][8];
+      float dx[MT], sx[MT];
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        const uint4* src = reinterpret_cast<const uint4*>(xq + (size_t)m * (p.K >> 2) + g * 8);
+        const uint4 a = src[0], b = src[1];
+        xw[m][0] = a.x; xw[m][1] = a.y; xw[m][2] = a.z; xw[m][3] = a.w;
+        xw[m][4] = b.x; xw[m][5] = b.y; xw[m][6] = b.z; xw[m][7] = b.w;
+        dx[m] = xd[m * ngroups + g];
+        sx[m] = xs[m * ngroups + g];
+      }
+#pragma unroll
+      for (int r = 0; r < RWP; ++r) {
+        if (r >= live) break;
+        const uint8_t* crow = cbase + (size_t)r * cb;
+        const uint8_t* srow = sbase + (size_t)r * sb;
+        if (FMT == GV_W8 || FMT == GV_W8G16) {
+          const uint4* c = reinterpret_cast<const uint4*>(crow + g * 32);
+          const uint4 c0 = c[0], c1 = c[1];
+          const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+          float s0, s1;
+          if (FMT == GV_W8) {
+            s0 = s1 = h2f(srow + g * 2);
+          } else {
+            const uint8_t* rec = srow + (g >> 3) * 18;
+            const float d = h2f(rec);
+            const uint32_t two = *reinterpret_cast<const uint16_t*>(rec + 2 + (g & 7) * 2);
+            s0 = d * (float)(int8_t)(two & 0xFF);
+            s1 = d * (float)(int8_t)(two >> 8);
+          }
+#pragma unroll
+          for (int m = 0; m < MT; ++m) {
+            int a = 0, b = 0;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              a = dp4a_s8(cw[q], xw[m][q], a);
+              b = dp4a_s8(cw[4 + q], xw[m][4 + q], b);
+            }
+            acc[r][m] = fmaf(dx[m], s0 * (float)a + s1 * (float)b, acc[r][m]);
+          }
+        } else {
+          const uint4 c0 = *reinterpret_cast<const uint4*>(crow + g * 16);
+          const uint8_t* rec = srow + (g >> 3) * 20;
+          const int j = g & 7;
+          const uint32_t dd = *reinterpret_cast<const uint32_t*>(rec);
+          const float d = __half2float(__ushort_as_half((unsigned short)(dd & 0xFFFF))) * (float)rec[4 + j];
+          const float mn = __half2float(__ushort_as_half((unsigned short)(dd >> 16))) * (float)rec[12 + j];
+          const uint32_t cw[4] = {c0.x, c0.y, c0.z, c0.w};
+#pragma unroll
+          for (int m = 0; m < MT; ++m) {
+            int sum = 0;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              sum = dp4a_u8s8(cw[q] & 0x0F0F0F0Fu, xw[m][2 * q], sum);
+              sum = dp4a_u8s8((cw[q] >> 4) & 0x0F0F0F0Fu, xw[m][2 * q + 1], sum);
+            }
+            acc[r][m] += d * dx[m] * (float)sum - mn * sx[m];
+          }
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0 && !dead) mbar_arrive(&empty[s]);      // the stage has been read
+    float* mine = part + ((size_t)(it & 1) * GS_WARPS + warp) * (RWP * MT);
+#pragma unroll
+    for (int r = 0; r < RWP; ++r)
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        const float v = warp_sum(acc[r][m]);
+        if (lane == 0) mine[r * MT + m] = v;
+      }
+    consumer_sync();
+    // the buffer of this parity is written again two stages on, after the barrier of the next stage, which
+    // no thread passes before every reader below is done
+    if (threadIdx.x < R * MT) {
+      const int row = threadIdx.x / MT, m = threadIdx.x % MT;
+      const int g2 = row / RWP, rr = row % RWP;
+      const float* src = part + ((size_t)(it & 1) * GS_WARPS + g2 * KS) * (RWP * MT) + rr * MT + m;
+      float v = 0.f;
+#pragma unroll
+      for (int k = 0; k < KS; ++k) v += src[k * (RWP * MT)];
+      const long long n = row0 + row;
+      if (n < p.N && m < p.M) {
+        const float o = v + (p.bias ? p.bias[n] : 0.f);
+        if (p.out_fp32)
+          reinterpret_cast<float*>(p.out)[(long long)m * p.ldo + n] = o;
+        else
+          p.out[(long long)m * p.ldo + n] = f2bf(o);
+      }
+    }
+  }
+  if (ab->flag && threadIdx.x == 0) {
+    // a wait gave up: give the copies still on their way a bounded time (0.2 ms) to land before the CTA leaves
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+}
+
+static int g_gemv_stream = 1;
+
+template <int FMT, int MT, int R>
+int launch_gs_r(const GvParams& p, cudaStream_t st, int* status) {
+  constexpr int RWP = R >= 4 ? (MT >= 4 ? 4 : 2) : R;
+  const size_t row = (size_t)gs_code_bytes<FMT>(p.K) + gs_scale_bytes<FMT>(p.K);
+  const size_t xbytes = ((size_t)MT * p.K + (size_t)MT * (p.K >> 5) * 8 + 127) & ~(size_t)127;
+  const size_t pitch = ((size_t)R * row + 127) & ~(size_t)127;
+  const size_t fixed = xbytes + 2 * GS_WARPS * RWP * MT * sizeof(float) + 12 * 16 + 16;
+  // two CTAs per SM when the ring is at least three stages deep within half of the shared memory, else one
+  size_t budget = 100 * 1024;
+  if (fixed + 3 * pitch > budget) budget = 200 * 1024;
+  if (fixed + 2 * pitch > budget) return -1;
+  int S = (int)((budget - fixed) / pitch);
+  if (S > 12) S = 12;
+  const size_t smem = fixed + (size_t)S * pitch;
+  auto kern = gemv_q_stream_kernel<FMT, MT, R, RWP>;
+  static bool granted = false;
+  if (!granted) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 201 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    granted = true;
+  }
+  const int nblk = (p.N + R - 1) / R;
+  const int per_sm = budget > 100 * 1024 ? 1 : 2;
+  const int grid = nblk < 148 * per_sm ? nblk : 148 * per_sm;
+  const long long l2_budget = (64ll << 20) / grid;
+  lkh::launch_pdl(kern, dim3(grid), dim3(GS_THREADS), smem, st, p, S, l2_budget, status);
+  return 0;
+}
+
+// Takes the shape when both planes are contiguous and every copy starts and ends on 16 bytes.
+template <int FMT, int MT>
+int launch_gs(const GvParams& p, cudaStream_t st, int* status, bool* taken) {
+  *taken = false;
+  if (!g_gemv_stream || !status) return 0;
+  // eight consumer warps are too few once every group of weights meets four or more token rows: there the
+  // register form (24 warps per SM) is as fast or faster, except for the 8-bit planes at up to four rows
+  // (Q6_K 4096 x 14336 at four rows: 25 us here, 33 us there; Q4_K 28672 x 4096: 46 us here, 32 us there)
+  if (MT > 4 || (MT == 4 && FMT == GV_W4)) return 0;
+  const long long cb = gs_code_bytes<FMT>(p.K), sb = gs_scale_bytes<FMT>(p.K);
+  if (p.c_ld != cb || p.s_ld != sb || (reinterpret_cast<uintptr_t>(p.scales) & 15)) return 0;
+  int R = 8;
+  while (R > 1 && (size_t)R * (cb + sb) > 64 * 1024) R >>= 1;
+  if ((size_t)R * (cb + sb) > 64 * 1024) return 0;
+  const long long tail = p.N % R;
+  if (((R * cb) & 15) || ((R * sb) & 15) || ((tail * cb) & 15) || ((tail * sb) & 15)) return 0;
+  int rc;
+  switch (R) {
+    case 8: rc = launch_gs_r<FMT, MT, 8>(p, st, status); break;
+    case 4: rc = launch_gs_r<FMT, MT, 4>(p, st, status); break;
+    case 2: rc = launch_gs_r<FMT, MT, 2>(p, st, status); break;
+    default: rc = launch_gs_r<FMT, MT, 1>(p, st, status); break;
+  }
+  if (rc < 0) return 0;            // does not fit: the register form takes it
+  if (rc == 0) *taken = true;
+  return rc;
+}
+
 template <int FMT, int MT>
 int launch_gv(const GvParams& p, cudaStream_t st) {
   constexpr int RW = MT <= 2 ? 4 : 2;
@@ -268,12 +556,20 @@ int launch_gv(const GvParams& p, cudaStream_t st) {
   return 0;
 }
 
+template <int FMT, int MT>
+int launch_either(const GvParams& p, cudaStream_t st, int* status) {
+  bool taken = false;
+  const int rc = launch_gs<FMT, MT>(p, st, status, &taken);
+  if (rc || taken) return rc;
+  return launch_gv<FMT, MT>(p, st);
+}
+
 template <int FMT>
-int dispatch_gv(const GvParams& p, int M, cudaStream_t st) {
-  if (M == 1) return launch_gv<FMT, 1>(p, st);
-  if (M == 2) return launch_gv<FMT, 2>(p, st);
-  if (M <= 4) return launch_gv<FMT, 4>(p, st);
-  return launch_gv<FMT, 8>(p, st);
+int dispatch_gv(const GvParams& p, int M, cudaStream_t st, int* status) {
+  if (M == 1) return launch_either<FMT, 1>(p, st, status);
+  if (M == 2) return launch_either<FMT, 2>(p, st, status);
+  if (M <= 4) return launch_either<FMT, 4>(p, st, status);
+  return launch_either<FMT, 8>(p, st, status);
 }
 
 // Embedding gather from a quantised table: row tok[t] of the planes is decoded to bf16.  One CTA per token,
@@ -436,11 +732,16 @@ LK_API int lk_embed_q(int fmt, const int* tokens, const void* codes, long long c
   return lkh::launch_status();
 }
 
+// Measurement hook: 0 keeps every GEMV on the register form, 1 (the default) lets the streaming form take
+// the shapes it can.
+LK_API void lk_gemv_q_stream(int on) { g_gemv_stream = on; }
+
+// `status` (device word, may be null: then the register form runs) receives the code of a wait that gave up.
 // x [M <= 8, K] bf16 (row pitch ldx elements), W as device planes of format `fmt` (1 Q8_0, 2 Q6_K, 3 Q4_K),
 // out [M, N] bf16 or, with out_fp32, f32 (row pitch ldo elements).  K a multiple of 32 (256 for the K formats).
 LK_API int lk_gemv_q(int fmt, const void* codes, long long c_ld, const void* scales, long long s_ld, const void* x,
                      long long ldx, int M, int N, int K, const float* bias, void* out, long long ldo, int out_fp32,
-                     void* stream) {
+                     int* status, void* stream) {
   if (M <= 0 || N <= 0) return LKH_OK;
   if (M > 8 || !codes || !scales || !x || !out || (K & 31) || (ldx & 7)) return LKH_BAD_ARG;
   if ((fmt == GV_W8G16 || fmt == GV_W4) && (K & 255)) return LKH_BAD_ARG;
@@ -462,9 +763,9 @@ LK_API int lk_gemv_q(int fmt, const void* codes, long long c_ld, const void* sca
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int rc;
   switch (fmt) {
-    case GV_W8: rc = dispatch_gv<GV_W8>(p, M, st); break;
-    case GV_W8G16: rc = dispatch_gv<GV_W8G16>(p, M, st); break;
-    case GV_W4: rc = dispatch_gv<GV_W4>(p, M, st); break;
+    case GV_W8: rc = dispatch_gv<GV_W8>(p, M, st, status); break;
+    case GV_W8G16: rc = dispatch_gv<GV_W8G16>(p, M, st, status); break;
+    case GV_W4: rc = dispatch_gv<GV_W4>(p, M, st, status); break;
     default: return LKH_BAD_ARG;
   }
   if (rc) return rc;

@@ -95,7 +95,9 @@ int lk_rope_kv(const void* qkv, long long ld, const int* pos, const int* slots, 
 // dp4a over the stored codes.  fmt: 1 Q8_0, 2 Q6_K, 3 Q4_K planes of ops/quant.py.
 int lk_gemv_q(int fmt, const void* codes, long long c_ld, const void* scales, long long s_ld, const void* x,
               long long ldx, int M, int N, int K, const float* bias, void* out, long long ldo, int out_fp32,
-              void* stream);
+              int* status, void* stream);
+// 0: every GEMV on the register form; 1 (default): the streaming form (bulk-copy ring) where the shape allows.
+void lk_gemv_q_stream(int on);
 // The same planes decoded to bf16 out [rows, K], row pitch ldo elements: the operand of prompt-sized GEMMs.
 int lk_dequant_q(int fmt, const void* codes, long long c_ld, const void* scales, long long s_ld, void* out,
                  long long ldo, int rows, int K, void* stream);
@@ -174,6 +176,8 @@ int lk_token_bitmask(float* logits, long long ld, int B, int V, const unsigned* 
                      void* stream);
 int lk_sample(const float* logits, long long ld, int B, int V, const float* temperature, const int* top_k,
               const float* top_p, const float* min_p, const float* uniform, int* out, void* stream);
+// 0: every row on the one-CTA sampler; 1 (default): a cluster of eight CTAs per row up to 148 rows.
+void lk_sample_cluster(int on);
 int lk_advance_decode(int* tokens, int* positions, int* slots, int* seq_lens, const int* sampled,
                       const int* block_table, int max_blocks, int block_size, int rows, long long num_slots,
                       int* history, int hist_ld, const int* hist_base, int* status, void* stream);

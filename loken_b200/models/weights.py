@@ -152,6 +152,15 @@ def random_weights(cfg: ModelConfig, device, seed: int = 0, tp_rank: int = 0, tp
     assert cfg.vocab % tp_size == 0 or tp_size == 1
     vl = cfg.vocab // tp_size
     lm_head = head_full[tp_rank * vl:(tp_rank + 1) * vl].contiguous() if tp_size > 1 else head_full
+    if tp_size == 1 and cfg.weight_format in ("q8_0", "q4_k", "q4_k_m", "q6_k") and H % 256 == 0 \
+            and str(device).startswith("cuda"):
+        # as the files of these mixes store them: table and head one step above the matrices (Q6_K under a
+        # 4-bit mix, Q8_0 under Q8_0), kept in that format on one rank
+        from ..ops.quant import quantize_weight_torch
+
+        tf = "q8_0" if cfg.weight_format == "q8_0" else "q6_k"
+        embed = quantize_weight_torch(embed.float(), tf)
+        lm_head = embed if cfg.tie_embeddings else quantize_weight_torch(head_full.float(), tf)
     inv, mscale = cfg.rope_tables()
     mw = ModelWeights(cfg, embed, torch.ones(H, device=device), lm_head, [],
                       torch.tensor(inv, dtype=torch.float32, device=device), mscale, tp_rank, tp_size, nql, nkvl, vl,

@@ -234,7 +234,8 @@ def linear_gguf(x: torch.Tensor, w: QuantWeight, *, bias: Optional[torch.Tensor]
         # a handful of token rows: int8 activations and dp4a over the stored codes, every weight byte read once
         check(cuda_lib().lk_gemv_q(w.aq_fmt, ptr(w.codes), C.c_longlong(w.codes.stride(0)), ptr(w.scales),
                                    C.c_longlong(w.scales.stride(0)), ptr(x), C.c_longlong(x.stride(0)), M, N, K,
-                                   ptr(bias), ptr(out), C.c_longlong(out.stride(0)), int(out_fp32), stream()), "lk_gemv_q")
+                                   ptr(bias), ptr(out), C.c_longlong(out.stride(0)), int(out_fp32),
+                                   ptr(Workspace.get(x.device).status), stream()), "lk_gemv_q")
         return out
     if DEQUANT_ONCE_MIN_M and M >= DEQUANT_ONCE_MIN_M and w.aq_fmt in (AQ_W8, AQ_W8G16, AQ_W4) and K % 8 == 0 \
             and out.stride(0) % 8 == 0:

@@ -377,6 +377,37 @@ def test_sample_matches_reference(T, k, p, mp):
     assert hits >= B - 1
 
 
+@pytest.mark.parametrize("V", [1000, 32000, 128256, 151936])
+def test_cluster_sampler_equals_the_one_cta_sampler(V):
+    """Up to 37 rows a cluster of eight CTAs shares each row (logits in registers, histograms merged through
+    distributed shared memory).  Masses are fixed-point integers, so every cut and draw equals the one-CTA
+    kernel's exactly, whatever the mix of rules per row."""
+    from loken_b200.ops import sampling
+    from loken_b200.ops._lib import cuda_lib
+
+    torch.manual_seed(V)
+    B = 24
+    x = (torch.randn(B, V, device=DEV) * 3).bfloat16().float()        # bf16-rounded: ties at the cuts
+    x[3, 100:] = float("-inf")                                        # a nearly empty row
+    x[4] = 0.25                                                       # one value everywhere: all ties
+    x[5, ::2] = float("-inf")
+    T = torch.tensor([0.0, 0.7, 1.0, 0.8, 1.3, 1.0] * 4, device=DEV)
+    k = torch.tensor([0, 0, 40, 40, 0, 5] * 4, device=DEV, dtype=torch.int32)
+    p = torch.tensor([1.0, 0.9, 1.0, 0.9, 1.0, 0.5] * 4, device=DEV)
+    mp = torch.tensor([0.0, 0.0, 0.0, 0.0, 0.05, 0.0] * 4, device=DEV)
+    for seed in range(3):
+        u = torch.rand(B, device=DEV, generator=torch.Generator(device=DEV).manual_seed(seed))
+        got = sampling.sample(x, T, u, top_k=k, top_p=p, min_p=mp)
+        try:
+            cuda_lib().lk_sample_cluster(0)
+            want = sampling.sample(x, T, u, top_k=k, top_p=p, min_p=mp)
+        finally:
+            cuda_lib().lk_sample_cluster(1)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want), (got.tolist(), want.tolist())
+        assert ((got >= 0) & (got < V)).all()
+
+
 def test_sample_distribution():
     from loken_b200.ops import sampling
 

@@ -48,7 +48,8 @@ def test_linear_gguf(fmt, M, N, K):
 
 @pytest.mark.parametrize("fmt", ["q8_0", "q4_k", "q6_k"])
 @pytest.mark.parametrize("M", [1, 2, 3, 8])
-@pytest.mark.parametrize("N,K", [(300, 2048), (4096, 1280), (1234, 256)])     # ragged rows; a tail chunk; one block
+# streaming form: ragged rows, two chunks, 1024-value chunks; register form: a tail chunk, one block
+@pytest.mark.parametrize("N,K", [(300, 2048), (300, 4096), (2000, 3072), (4096, 1280), (1234, 256)])
 def test_gemv_dp4a_matches_the_integer_product_and_the_gemm(fmt, M, N, K):
     """Up to eight token rows run as a GEMV on int8 activations: it equals the product of the activations as
     quantised (per 32 values, amax / 127) with the decoded weights, and stays within the int8 noise of the
@@ -80,6 +81,17 @@ def test_gemv_dp4a_matches_the_integer_product_and_the_gemm(fmt, M, N, K):
     assert rel_err(out, gemm) < 2e-2                   # the reference's bar for 8-bit activations
     again = quant.linear_gguf(x, q, bias=bias)
     assert torch.equal(out, again)
+    # the register form (the only one for shapes the bulk-copy ring does not take) agrees up to summation order
+    from loken_b200.ops._lib import Workspace, cuda_lib
+
+    try:
+        cuda_lib().lk_gemv_q_stream(0)
+        reg = quant.linear_gguf(x, q, bias=bias)
+    finally:
+        cuda_lib().lk_gemv_q_stream(1)
+    torch.cuda.synchronize()
+    assert rel_err(out, reg) < 1e-2
+    assert Workspace.get(torch.device(DEV)).read_status() == 0
 
 
 @pytest.mark.parametrize("fmt", ["q8_0", "q4_k", "q6_k"])
