@@ -51,6 +51,11 @@ __device__ __forceinline__ void l2_prefetch_bulk(const void* p, uint32_t bytes) 
 __device__ __forceinline__ void l2_prefetch_line(const void* p) {
   asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ float h2f(const uint8_t* p) {
   return __half2float(*reinterpret_cast<const __half*>(p));
 }
@@ -66,58 +71,177 @@ struct GvParams {
   long long ldo;
   int M, N, K;
   int out_fp32;
+  LkGemvPre pre;              // what the activations are computed from (plain rows, a norm, a gated unit)
 };
 
-// One group of 32 activations of token row m to int8: codes as words (for Q4_K de-interleaved per 8 values,
-// even values then odd ones, to line up with the nibble planes), scale and sum of the group.
-template <int FMT>
-__device__ __forceinline__ void quantise_group(const GvParams& p, int m, int gi, uint32_t* xq, float* xd, float* xs,
-                                               int ngroups) {
-  float v[32];
-  if (m < p.M) {
-    const uint4* src = reinterpret_cast<const uint4*>(p.x + (long long)m * p.ldx + gi * 32);
+__device__ __forceinline__ void load8f(const __nv_bfloat16* src, float* v) {
+  const uint4 u = *reinterpret_cast<const uint4*>(src);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const uint4 u = src[q];
-      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+  for (int e = 0; e < 4; ++e) {
+    const float2 f = __bfloat1622float2(h[e]);
+    v[2 * e] = f.x;
+    v[2 * e + 1] = f.y;
+  }
+}
+// Values 8 c .. 8 c + 7 of token row m of the residual stream as the norm sees it: x, plus the pending
+// update rounded into bf16 the way the stream stores it.
+__device__ __forceinline__ void residual8(const GvParams& p, int m, int c, float* v) {
+  load8f(p.x + (long long)m * p.ldx + c * 8, v);
+  if (p.pre.delta) {
+    float d[8];
+    load8f(reinterpret_cast<const __nv_bfloat16*>(p.pre.delta) + (long long)m * p.pre.ldd + c * 8, d);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 f = __bfloat1622float2(h[e]);
-        v[q * 8 + 2 * e] = f.x;
-        v[q * 8 + 2 * e + 1] = f.y;
+    for (int e = 0; e < 8; ++e) v[e] = bf2f(f2bf(v[e] + d[e]));
+  }
+}
+
+// Eight activations of token row m as the GEMV multiplies them: the rows of x themselves, or
+// RMSNorm(x + delta) * gamma (rinv = 1 / rms of the row), or the gated unit of x = [gate | up]; each rounded
+// to bf16 where the separate kernels store bf16.
+__device__ __forceinline__ void activation8(const GvParams& p, int m, int c, float rinv, float* v) {
+  if (p.pre.mode == 1) {
+    residual8(p, m, c, v);
+    const float4* g4 = reinterpret_cast<const float4*>(p.pre.gamma + c * 8);
+    const float4 ga = g4[0], gb = g4[1];
+    const float g[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = bf2f(f2bf(v[e] * rinv * g[e]));
+  } else if (p.pre.mode == 2) {
+    float u[8];
+    load8f(p.x + (long long)m * p.ldx + c * 8, v);
+    load8f(p.x + (long long)m * p.ldx + p.K + c * 8, u);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float o;
+      if (p.pre.glu_mode == 0) {
+        o = silu(v[e]) * u[e];
+      } else {
+        const float gg = fminf(v[e], p.pre.glu_limit);
+        const float uu = fminf(fmaxf(u[e], -p.pre.glu_limit), p.pre.glu_limit);
+        o = gg / (1.f + __expf(-p.pre.glu_alpha * gg)) * (1.f + uu);
       }
+      v[e] = bf2f(f2bf(o));
     }
   } else {
-#pragma unroll
-    for (int e = 0; e < 32; ++e) v[e] = 0.f;
+    load8f(p.x + (long long)m * p.ldx + c * 8, v);
   }
-  float amax = 0.f, sum = 0.f;
+}
+
+// The activations of the M token rows, quantised once per CTA into shared memory by its 256 compute threads
+// (threadIdx.x 0 .. 255; SYNC is the barrier those threads share): int8 codes as words (for Q4_K de-interleaved
+// per 8 values, even values then odd ones, to line up with the nibble planes), one scale and one sum per group
+// of 32.  A thread takes 8 values, four neighbouring lanes make a group: the phase sits between the kernel
+// before this one and the first product, so it is spread over every thread rather than run as 128 serial
+// groups.  With a norm in front, a first pass sums the squares of every row.  CTA 0 also applies a residual
+// update that an earlier kernel of the step left pending (upd_x += upd_delta): every reader of the old rows
+// finished with the kernel before this one.
+template <int FMT, int MT, class SYNC>
+__device__ __forceinline__ void stage_activations(const GvParams& p, uint32_t* xq, float* xd, float* xs, int ngroups,
+                                                  SYNC sync) {
+  __shared__ float s_red[GV_WARPS][8];
+  __shared__ float s_rinv[8];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int cpr = p.K >> 3;                        // chunks of 8 per row
+  if (p.pre.upd_x && blockIdx.x == 0) {
+    __nv_bfloat16* ux = reinterpret_cast<__nv_bfloat16*>(p.pre.upd_x);
+    const __nv_bfloat16* ud = reinterpret_cast<const __nv_bfloat16*>(p.pre.upd_delta);
+    const int per_row = p.pre.upd_cols >> 3;
+    for (int i = tid; i < p.M * per_row; i += GV_WARPS * 32) {
+      const int m = i / per_row, c = (i % per_row) * 8;
+      uint4 a = *reinterpret_cast<const uint4*>(ux + (long long)m * p.pre.upd_ldx + c);
+      const uint4 d = *reinterpret_cast<const uint4*>(ud + (long long)m * p.pre.upd_ldd + c);
+      __nv_bfloat162* ah = reinterpret_cast<__nv_bfloat162*>(&a);
+      const __nv_bfloat162* dh = reinterpret_cast<const __nv_bfloat162*>(&d);
 #pragma unroll
-  for (int e = 0; e < 32; ++e) {
-    amax = fmaxf(amax, fabsf(v[e]));
-    sum += v[e];
-  }
-  const float d = amax * (1.f / 127.f);
-  const float id = d > 0.f ? 1.f / d : 0.f;
-  uint32_t wq[8];
-#pragma unroll
-  for (int w8 = 0; w8 < 4; ++w8) {
-    int q8[8];
-#pragma unroll
-    for (int e = 0; e < 8; ++e) q8[e] = __float2int_rn(v[w8 * 8 + e] * id) & 0xFF;
-    if (FMT == GV_W4) {
-      wq[2 * w8] = q8[0] | (q8[2] << 8) | (q8[4] << 16) | (q8[6] << 24);
-      wq[2 * w8 + 1] = q8[1] | (q8[3] << 8) | (q8[5] << 16) | (q8[7] << 24);
-    } else {
-      wq[2 * w8] = q8[0] | (q8[1] << 8) | (q8[2] << 16) | (q8[3] << 24);
-      wq[2 * w8 + 1] = q8[4] | (q8[5] << 8) | (q8[6] << 16) | (q8[7] << 24);
+      for (int e = 0; e < 4; ++e) {
+        const float2 fa = __bfloat1622float2(ah[e]), fd = __bfloat1622float2(dh[e]);
+        ah[e] = __floats2bfloat162_rn(fa.x + fd.x, fa.y + fd.y);
+      }
+      *reinterpret_cast<uint4*>(ux + (long long)m * p.pre.upd_ldx + c) = a;
     }
   }
-  uint4* dst = reinterpret_cast<uint4*>(xq + (size_t)m * (p.K >> 2) + gi * 8);
-  dst[0] = make_uint4(wq[0], wq[1], wq[2], wq[3]);
-  dst[1] = make_uint4(wq[4], wq[5], wq[6], wq[7]);
-  xd[m * ngroups + gi] = d;
-  xs[m * ngroups + gi] = sum;
+  if (p.pre.mode == 1) {
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      float ss = 0.f;
+      if (m < p.M)
+#pragma unroll 4
+        for (int c = tid; c < cpr; c += GV_WARPS * 32) {
+          float v[8];
+          residual8(p, m, c, v);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
+        }
+      ss = warp_sum(ss);
+      if (lane == 0) s_red[warp][m] = ss;
+    }
+    sync();
+    if (tid < MT) {
+      float t = 0.f;
+#pragma unroll
+      for (int w = 0; w < GV_WARPS; ++w) t += s_red[w][tid];
+      s_rinv[tid] = rsqrtf(t / (float)p.K + p.pre.eps);
+    }
+    sync();
+  }
+  // chunks of a row are a multiple of four, so the four lanes of a group are in or out of range together;
+  // every lane of a warp runs every trip (the shuffles below name the whole warp).  Four trips at a time: their
+  // loads are all issued before the first value is used, so a batch costs one trip to L2 instead of four (the
+  // phase took 3 us at K = 4096 and 7 us at K = 14336 with one load in flight per thread).
+  constexpr int UB = 4;
+  const int total = MT * cpr;
+  for (int base = 0; base < total; base += UB * GV_WARPS * 32) {
+    float v[UB][8];
+#pragma unroll
+    for (int u = 0; u < UB; ++u) {
+      const int ch = base + u * GV_WARPS * 32 + tid;
+      const int m = ch / cpr, c = ch % cpr;
+      if (ch < total && m < p.M) {
+        activation8(p, m, c, p.pre.mode == 1 ? s_rinv[m] : 1.f, v[u]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[u][e] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UB; ++u) {
+      const int ch = base + u * GV_WARPS * 32 + tid;
+      const int m = ch / cpr, c = ch % cpr;
+      float amax = 0.f, sum = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        amax = fmaxf(amax, fabsf(v[u][e]));
+        sum += v[u][e];
+      }
+#pragma unroll
+      for (int o = 1; o <= 2; o <<= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      }
+      const float d = amax * (1.f / 127.f);
+      const float id = d > 0.f ? 1.f / d : 0.f;
+      int q8[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) q8[e] = __float2int_rn(v[u][e] * id) & 0xFF;
+      uint2 w;
+      if (FMT == GV_W4) {
+        w.x = q8[0] | (q8[2] << 8) | (q8[4] << 16) | (q8[6] << 24);
+        w.y = q8[1] | (q8[3] << 8) | (q8[5] << 16) | (q8[7] << 24);
+      } else {
+        w.x = q8[0] | (q8[1] << 8) | (q8[2] << 16) | (q8[3] << 24);
+        w.y = q8[4] | (q8[5] << 8) | (q8[6] << 16) | (q8[7] << 24);
+      }
+      if (ch < total) {
+        *reinterpret_cast<uint2*>(xq + (size_t)m * (p.K >> 2) + c * 2) = w;
+        if ((c & 3) == 0) {
+          xd[m * ngroups + (c >> 2)] = d;
+          xs[m * ngroups + (c >> 2)] = sum;
+        }
+      }
+    }
+  }
+  sync();
 }
 
 // FMT: block format; MT: token rows (1, 2, 4 or 8); RW: output rows per warp and pass
@@ -152,11 +276,7 @@ gemv_q_kernel(const GvParams p) {
   float* xd = reinterpret_cast<float*>(gv_smem + (size_t)MT * p.K);            // [MT][K / 32]
   float* xs = xd + MT * ngroups;                                               // [MT][K / 32]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int g = threadIdx.x; g < MT * ngroups; g += GV_WARPS * 32) {
-    const int m = g / ngroups, gi = g % ngroups;
-    quantise_group<FMT>(p, m, gi, xq, xd, xs, ngroups);
-  }
-  __syncthreads();
+  stage_activations<FMT, MT>(p, xq, xd, xs, ngroups, [] { __syncthreads(); });
 
   // row groups of RW rows per warp, strided over the grid; no barrier from here on
   const int n_rg = (p.N + GV_WARPS * RW - 1) / (GV_WARPS * RW);
@@ -267,6 +387,57 @@ gemv_q_kernel(const GvParams p) {
 // size, the rate at which the copy engine takes requests.)  The eight consumer warps split a stage into
 // R / RWP row groups times KS slices of K; a warp holds the activations of a group of 32 values in
 // registers for its RWP rows.  Partial sums meet in shared memory, one barrier per stage.
+// One group of 32 weights of one row (codes and scale records in shared memory: crow, srow) times the same
+// group of every token row: acc[m] += w . x[m].  For Q4_K the high nibbles are multiplied where they stand
+// (as multiples of 16) and the sum is shifted once: two logic operations per word instead of three.
+template <int FMT, int MT>
+__device__ __forceinline__ void row_dot(const uint8_t* crow, const uint8_t* srow, int g, const uint32_t (*xw)[8],
+                                        const float* dx, const float* sx, float* acc) {
+  if (FMT == GV_W8 || FMT == GV_W8G16) {
+    const uint4* c = reinterpret_cast<const uint4*>(crow + g * 32);
+    const uint4 c0 = c[0], c1 = c[1];
+    const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    float s0, s1;
+    if (FMT == GV_W8) {
+      s0 = s1 = h2f(srow + g * 2);
+    } else {
+      const uint8_t* rec = srow + (g >> 3) * 18;
+      const float d = h2f(rec);
+      const uint32_t two = *reinterpret_cast<const uint16_t*>(rec + 2 + (g & 7) * 2);
+      s0 = d * (float)(int8_t)(two & 0xFF);
+      s1 = d * (float)(int8_t)(two >> 8);
+    }
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      int a = 0, b = 0;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        a = dp4a_s8(cw[q], xw[m][q], a);
+        b = dp4a_s8(cw[4 + q], xw[m][4 + q], b);
+      }
+      acc[m] = fmaf(dx[m], s0 * (float)a + s1 * (float)b, acc[m]);
+    }
+  } else {
+    const uint4 c0 = *reinterpret_cast<const uint4*>(crow + g * 16);
+    const uint8_t* rec = srow + (g >> 3) * 20;
+    const int j = g & 7;
+    const uint32_t dd = *reinterpret_cast<const uint32_t*>(rec);
+    const float d = __half2float(__ushort_as_half((unsigned short)(dd & 0xFFFF))) * (float)rec[4 + j];
+    const float mn = __half2float(__ushort_as_half((unsigned short)(dd >> 16))) * (float)rec[12 + j];
+    const uint32_t cw[4] = {c0.x, c0.y, c0.z, c0.w};
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      int lo = 0, hi = 0;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        lo = dp4a_u8s8(cw[q] & 0x0F0F0F0Fu, xw[m][2 * q], lo);          // even values
+        hi = dp4a_u8s8(cw[q] & 0xF0F0F0F0u, xw[m][2 * q + 1], hi);      // odd values, times 16
+      }
+      acc[m] += d * dx[m] * (float)(lo + (hi >> 4)) - mn * sx[m];
+    }
+  }
+}
+
 constexpr int GS_WARPS = 8;                 // consumer warps
 constexpr int GS_THREADS = (GS_WARPS + 1) * 32;
 
@@ -286,9 +457,12 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* src, uint32
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(GS_WARPS * 32) : "memory"); }
 
 // R: rows per stage; RWP: rows per warp; S: stages.  Row pitches equal the row sizes (contiguous planes).
-template <int FMT, int MT, int R, int RWP>
+// XR (one token row, at most two groups of K per lane): the lane's activation codes stay in registers for
+// the whole kernel instead of being read from shared memory for every row.
+template <int FMT, int MT, int R, int RWP, bool XR>
 __global__ void __launch_bounds__(GS_THREADS)
 gemv_q_stream_kernel(const GvParams p, int S, long long l2_budget, int* status) {
+  static_assert(!XR || MT == 1, "activations in registers: one token row");
   constexpr int NRG = R / RWP;             // row groups of a stage
   constexpr int KS = GS_WARPS / NRG;       // warps per row group, each takes every KS-th run of 32 groups
   static_assert(R % RWP == 0 && GS_WARPS % NRG == 0, "stage geometry");
@@ -321,26 +495,32 @@ gemv_q_stream_kernel(const GvParams p, int S, long long l2_budget, int* status) 
   }
   __syncthreads();
 
+  long long* prof = reinterpret_cast<long long*>(p.pre.prof);     // measurement hook: eight time stamps per CTA
+  if (prof && threadIdx.x == 0) prof[blockIdx.x * 8 + 0] = (long long)globaltimer_ns();
   if (warp == GS_WARPS) {
     // ------------------------------ producer ------------------------------
-    // what the ring cannot hold yet is at least asked into L2 (up to this CTA's share of a budget that fits
-    // there), so that it arrives while the kernels before this one leave the memory system idle
-    {
-      const long long r0 = (long long)b0 * R, r1 = min((long long)p.N, (long long)b1 * R);
-      const long long rows = min(r1 - r0, l2_budget / (cb + sb));
-      const uint8_t* c0 = p.codes + r0 * cb;
-      const uint8_t* s0 = p.scales + r0 * sb;
-      for (long long off = lane * 4096ll; off < rows * cb; off += 32 * 4096)
-        l2_prefetch_bulk(c0 + off, (uint32_t)min(4096ll, rows * cb - off));
-      for (long long off = lane * 128ll; off < rows * sb; off += 32 * 128) l2_prefetch_line(s0 + off);
-    }
     for (int it = 0; it < nitems; ++it) {
       const int s = it % S;
+      if (it == S && l2_budget > 0) {
+        // a measurement hook, off by default: the ring is full and its copies are on their way; what it cannot
+        // hold yet is asked into L2 (up to this CTA's share of a budget that fits there).  The requests queue
+        // in front of the activation loads of every CTA, whose staging phase then takes 5 us instead of 3:
+        // a single-stream step of an 8B Q4_K_M model ran 4 to 5 % slower with the hints than without.
+        const long long r0 = (long long)(b0 + S) * R, r1 = min((long long)p.N, (long long)b1 * R);
+        const long long rows = min(r1 - r0, l2_budget / (cb + sb));
+        const uint8_t* c0 = p.codes + r0 * cb;
+        const uint8_t* s0 = p.scales + r0 * sb;
+        for (long long off = lane * 4096ll; off < rows * cb; off += 32 * 4096)
+          l2_prefetch_bulk(c0 + off, (uint32_t)min(4096ll, rows * cb - off));
+        for (long long off = lane * 128ll; off < rows * sb; off += 32 * 128) l2_prefetch_line(s0 + off);
+      }
       if (!mbar_wait(&empty[s], ((it / S) & 1) ^ 1, ab, status, 1)) break;
       const long long row0 = (long long)(b0 + it) * R;
       const int nvalid = (int)min((long long)R, p.N - row0);
       uint8_t* st = stages + (size_t)s * pitch;
       if (lane == 0) {
+        if (prof && it == 0) prof[blockIdx.x * 8 + 5] = (long long)globaltimer_ns();
+        if (prof && it == nitems - 1) prof[blockIdx.x * 8 + 6] = (long long)globaltimer_ns();
         mbar_expect_tx(&full[s], (uint32_t)(nvalid * (cb + sb)));
         bulk_g2s(st, p.codes + row0 * cb, (uint32_t)(nvalid * cb), &full[s]);
         bulk_g2s(st + R * cb, p.scales + row0 * sb, (uint32_t)(nvalid * sb), &full[s]);
@@ -352,18 +532,38 @@ gemv_q_stream_kernel(const GvParams p, int S, long long l2_budget, int* status) 
 
   // ------------------------------ consumers ------------------------------
   pdl_wait();
+  if (prof && threadIdx.x == 0) prof[blockIdx.x * 8 + 1] = (long long)globaltimer_ns();
   pdl_launch();
-  for (int g = threadIdx.x; g < MT * ngroups; g += GS_WARPS * 32) {
-    const int m = g / ngroups, gi = g % ngroups;
-    quantise_group<FMT>(p, m, gi, xq, xd, xs, ngroups);
-  }
-  consumer_sync();
+  stage_activations<FMT, MT>(p, xq, xd, xs, ngroups, [] { consumer_sync(); });
+  if (prof && threadIdx.x == 0) prof[blockIdx.x * 8 + 2] = (long long)globaltimer_ns();
 
   const int rgp = warp / KS, ks = warp % KS;
+  // XR: this lane's (at most two) groups of K, fixed for every row it will see
+  uint32_t xr[2][8];
+  float dxr[2], sxr[2];
+  if (XR) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int g = ks * 32 + lane + i * KS * 32;
+      if (g < ngroups) {
+        const uint4* src = reinterpret_cast<const uint4*>(xq + g * 8);
+        const uint4 a = src[0], b = src[1];
+        xr[i][0] = a.x; xr[i][1] = a.y; xr[i][2] = a.z; xr[i][3] = a.w;
+        xr[i][4] = b.x; xr[i][5] = b.y; xr[i][6] = b.z; xr[i][7] = b.w;
+        dxr[i] = xd[g];
+        sxr[i] = xs[g];
+      } else {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) xr[i][q] = 0;
+        dxr[i] = sxr[i] = 0.f;
+      }
+    }
+  }
   bool dead = false;                       // a wait gave up: no more waits, but every barrier below is still met
   for (int it = 0; it < nitems; ++it) {
     const int s = it % S;
     if (!dead && !mbar_wait(&full[s], (it / S) & 1, ab, status, 2)) dead = true;
+    if (prof && threadIdx.x == 0 && it == 0) prof[blockIdx.x * 8 + 3] = (long long)globaltimer_ns();
     const long long row0 = (long long)(b0 + it) * R;
     const uint8_t* st = stages + (size_t)s * pitch;
     const uint8_t* cbase = st + (size_t)(rgp * RWP) * cb;
@@ -375,67 +575,34 @@ gemv_q_stream_kernel(const GvParams p, int S, long long l2_budget, int* status) 
     for (int r = 0; r < RWP; ++r)
 #pragma unroll
       for (int m = 0; m < MT; ++m) acc[r][m] = 0.f;
-#pragma unroll(MT <= 2 ? 2 : 1)
-    for (int g = ks * 32 + lane; g < (live > 0 ? ngroups : 0); g += KS * 32) {
-      uint32_t xw[MT][8];
-      float dx[MT], sx[MT];
+    if (XR) {
 #pragma unroll
-      for (int m = 0; m < MT; ++m) {
-        const uint4* src = reinterpret_cast<const uint4*>(xq + (size_t)m * (p.K >> 2) + g * 8);
-        const uint4 a = src[0], b = src[1];
-        xw[m][0] = a.x; xw[m][1] = a.y; xw[m][2] = a.z; xw[m][3] = a.w;
-        xw[m][4] = b.x; xw[m][5] = b.y; xw[m][6] = b.z; xw[m][7] = b.w;
-        dx[m] = xd[m * ngroups + g];
-        sx[m] = xs[m * ngroups + g];
-      }
+      for (int i = 0; i < 2; ++i) {
+        const int g = ks * 32 + lane + i * KS * 32;
+        if (g < ngroups) {
 #pragma unroll
-      for (int r = 0; r < RWP; ++r) {
-        if (r >= live) break;
-        const uint8_t* crow = cbase + (size_t)r * cb;
-        const uint8_t* srow = sbase + (size_t)r * sb;
-        if (FMT == GV_W8 || FMT == GV_W8G16) {
-          const uint4* c = reinterpret_cast<const uint4*>(crow + g * 32);
-          const uint4 c0 = c[0], c1 = c[1];
-          const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-          float s0, s1;
-          if (FMT == GV_W8) {
-            s0 = s1 = h2f(srow + g * 2);
-          } else {
-            const uint8_t* rec = srow + (g >> 3) * 18;
-            const float d = h2f(rec);
-            const uint32_t two = *reinterpret_cast<const uint16_t*>(rec + 2 + (g & 7) * 2);
-            s0 = d * (float)(int8_t)(two & 0xFF);
-            s1 = d * (float)(int8_t)(two >> 8);
-          }
-#pragma unroll
-          for (int m = 0; m < MT; ++m) {
-            int a = 0, b = 0;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              a = dp4a_s8(cw[q], xw[m][q], a);
-              b = dp4a_s8(cw[4 + q], xw[m][4 + q], b);
-            }
-            acc[r][m] = fmaf(dx[m], s0 * (float)a + s1 * (float)b, acc[r][m]);
-          }
-        } else {
-          const uint4 c0 = *reinterpret_cast<const uint4*>(crow + g * 16);
-          const uint8_t* rec = srow + (g >> 3) * 20;
-          const int j = g & 7;
-          const uint32_t dd = *reinterpret_cast<const uint32_t*>(rec);
-          const float d = __half2float(__ushort_as_half((unsigned short)(dd & 0xFFFF))) * (float)rec[4 + j];
-          const float mn = __half2float(__ushort_as_half((unsigned short)(dd >> 16))) * (float)rec[12 + j];
-          const uint32_t cw[4] = {c0.x, c0.y, c0.z, c0.w};
-#pragma unroll
-          for (int m = 0; m < MT; ++m) {
-            int sum = 0;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              sum = dp4a_u8s8(cw[q] & 0x0F0F0F0Fu, xw[m][2 * q], sum);
-              sum = dp4a_u8s8((cw[q] >> 4) & 0x0F0F0F0Fu, xw[m][2 * q + 1], sum);
-            }
-            acc[r][m] += d * dx[m] * (float)sum - mn * sx[m];
-          }
+          for (int r = 0; r < RWP; ++r)
+            if (r < live)
+              row_dot<FMT, 1>(cbase + (size_t)r * cb, sbase + (size_t)r * sb, g, &xr[i], &dxr[i], &sxr[i], acc[r]);
         }
+      }
+    } else {
+#pragma unroll(MT <= 2 ? 2 : 1)
+      for (int g = ks * 32 + lane; g < (live > 0 ? ngroups : 0); g += KS * 32) {
+        uint32_t xw[MT][8];
+        float dx[MT], sx[MT];
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          const uint4* src = reinterpret_cast<const uint4*>(xq + (size_t)m * (p.K >> 2) + g * 8);
+          const uint4 a = src[0], b = src[1];
+          xw[m][0] = a.x; xw[m][1] = a.y; xw[m][2] = a.z; xw[m][3] = a.w;
+          xw[m][4] = b.x; xw[m][5] = b.y; xw[m][6] = b.z; xw[m][7] = b.w;
+          dx[m] = xd[m * ngroups + g];
+          sx[m] = xs[m * ngroups + g];
+        }
+#pragma unroll
+        for (int r = 0; r < RWP; ++r)
+          if (r < live) row_dot<FMT, MT>(cbase + (size_t)r * cb, sbase + (size_t)r * sb, g, xw, dx, sx, acc[r]);
       }
     }
     __syncwarp();
@@ -468,6 +635,7 @@ gemv_q_stream_kernel(const GvParams p, int S, long long l2_budget, int* status) 
       }
     }
   }
+  if (prof && threadIdx.x == 0) prof[blockIdx.x * 8 + 4] = (long long)globaltimer_ns();
   if (ab->flag && threadIdx.x == 0) {
     // a wait gave up: give the copies still on their way a bounded time (0.2 ms) to land before the CTA leaves
     for (int i = 0; i < 200; ++i) __nanosleep(1000);
@@ -476,9 +644,11 @@ gemv_q_stream_kernel(const GvParams p, int S, long long l2_budget, int* status) 
 
 static int g_gemv_stream = 1;
 
-template <int FMT, int MT, int R>
-int launch_gs_r(const GvParams& p, cudaStream_t st, int* status) {
-  constexpr int RWP = R >= 4 ? (MT >= 4 ? 4 : 2) : R;
+template <int FMT, int MT, int R, bool XR>
+int launch_gs_x(const GvParams& p, cudaStream_t st, int* status) {
+  // rows per warp: as many as leave every lane of the warps that share a row group a group of K (R = 8:
+  // four rows, four warps per group; shorter stages come with long rows)
+  constexpr int RWP = R == 8 ? 4 : R >= 2 ? 2 : 1;
   const size_t row = (size_t)gs_code_bytes<FMT>(p.K) + gs_scale_bytes<FMT>(p.K);
   const size_t xbytes = ((size_t)MT * p.K + (size_t)MT * (p.K >> 5) * 8 + 127) & ~(size_t)127;
   const size_t pitch = ((size_t)R * row + 127) & ~(size_t)127;
@@ -490,7 +660,7 @@ int launch_gs_r(const GvParams& p, cudaStream_t st, int* status) {
   int S = (int)((budget - fixed) / pitch);
   if (S > 12) S = 12;
   const size_t smem = fixed + (size_t)S * pitch;
-  auto kern = gemv_q_stream_kernel<FMT, MT, R, RWP>;
+  auto kern = gemv_q_stream_kernel<FMT, MT, R, RWP, XR>;
   static bool granted = false;
   if (!granted) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 201 * 1024);
@@ -500,9 +670,17 @@ int launch_gs_r(const GvParams& p, cudaStream_t st, int* status) {
   const int nblk = (p.N + R - 1) / R;
   const int per_sm = budget > 100 * 1024 ? 1 : 2;
   const int grid = nblk < 148 * per_sm ? nblk : 148 * per_sm;
-  const long long l2_budget = (64ll << 20) / grid;
+  const long long l2_budget = (g_gemv_stream & 2) ? (64ll << 20) / grid : 0;
   lkh::launch_pdl(kern, dim3(grid), dim3(GS_THREADS), smem, st, p, S, l2_budget, status);
   return 0;
+}
+
+template <int FMT, int MT, int R>
+int launch_gs_r(const GvParams& p, cudaStream_t st, int* status) {
+  constexpr int RWP = R == 8 ? 4 : R >= 2 ? 2 : 1;
+  constexpr int KS = GS_WARPS / (R / RWP);
+  if (MT == 1 && (p.K >> 5) <= 2 * KS * 32) return launch_gs_x<FMT, 1, R, true>(p, st, status);
+  return launch_gs_x<FMT, MT, R, false>(p, st, status);
 }
 
 // Takes the shape when both planes are contiguous and every copy starts and ends on 16 bytes.
@@ -733,7 +911,7 @@ LK_API int lk_embed_q(int fmt, const int* tokens, const void* codes, long long c
 }
 
 // Measurement hook: 0 keeps every GEMV on the register form, 1 (the default) lets the streaming form take
-// the shapes it can.
+// the shapes it can, 3 the same with L2 hints for the rows the ring does not hold yet.
 LK_API void lk_gemv_q_stream(int on) { g_gemv_stream = on; }
 
 // `status` (device word, may be null: then the register form runs) receives the code of a wait that gave up.
@@ -741,7 +919,7 @@ LK_API void lk_gemv_q_stream(int on) { g_gemv_stream = on; }
 // out [M, N] bf16 or, with out_fp32, f32 (row pitch ldo elements).  K a multiple of 32 (256 for the K formats).
 LK_API int lk_gemv_q(int fmt, const void* codes, long long c_ld, const void* scales, long long s_ld, const void* x,
                      long long ldx, int M, int N, int K, const float* bias, void* out, long long ldo, int out_fp32,
-                     int* status, void* stream) {
+                     const LkGemvPre* pre, int* status, void* stream) {
   if (M <= 0 || N <= 0) return LKH_OK;
   if (M > 8 || !codes || !scales || !x || !out || (K & 31) || (ldx & 7)) return LKH_BAD_ARG;
   if ((fmt == GV_W8G16 || fmt == GV_W4) && (K & 255)) return LKH_BAD_ARG;
@@ -760,6 +938,20 @@ LK_API int lk_gemv_q(int fmt, const void* codes, long long c_ld, const void* sca
   p.M = M;
   p.N = N;
   p.K = K;
+  memset(&p.pre, 0, sizeof(p.pre));
+  if (pre) {
+    p.pre = *pre;
+    if (p.pre.mode < 0 || p.pre.mode > 2 || (p.pre.mode == 1 && !p.pre.gamma)) return LKH_BAD_ARG;
+    if (p.pre.mode == 1 && p.pre.delta && ((reinterpret_cast<uintptr_t>(p.pre.delta) & 15) || (p.pre.ldd & 7)))
+      return LKH_BAD_ARG;
+    if (p.pre.mode == 1 && (reinterpret_cast<uintptr_t>(p.pre.gamma) & 15)) return LKH_BAD_ARG;
+    if (p.pre.upd_x) {
+      // the update is applied while this kernel's own rows are read: they must be other memory
+      if (!p.pre.upd_delta || p.pre.upd_x == x || (p.pre.upd_cols & 7) || (p.pre.upd_ldx & 7) || (p.pre.upd_ldd & 7) ||
+          (reinterpret_cast<uintptr_t>(p.pre.upd_x) & 15) || (reinterpret_cast<uintptr_t>(p.pre.upd_delta) & 15))
+        return LKH_BAD_ARG;
+    }
+  }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int rc;
   switch (fmt) {

@@ -91,12 +91,29 @@ int lk_rope_kv(const void* qkv, long long ld, const int* pos, const int* slots, 
                long long num_slots, int kv_q8, int* status, void* stream);
 // Context shift: cache positions move from `src` to `dst` slots (no overlap); key i is turned by delta[i]
 // positions on the way, values are copied.
+// What the activations of a GEMV are computed from, and a residual update it applies on the side.
+typedef struct {
+  int mode;                 // 0: the rows of x; 1: RMSNorm(x + delta) * gamma; 2: gated unit of x = [gate | up] (2K wide)
+  const void* delta;        // mode 1: bf16 [M, K] update still pending on x (row pitch ldd elements), or null
+  long long ldd;
+  const float* gamma;       // mode 1: [K]
+  float eps;
+  int glu_mode;             // mode 2: 0 silu(g) * u; 1 the clamped form (alpha, limit)
+  float glu_alpha, glu_limit;
+  void* upd_x;              // bf16 [M, upd_cols]: upd_x += upd_delta (rounded once), applied by one CTA; or null
+  const void* upd_delta;
+  long long upd_ldx, upd_ldd;
+  int upd_cols;
+  void* prof;               // measurement hook: int64 [CTAs][8] time stamps of the streaming form, or null
+} LkGemvPre;
+
 // Quantised GEMV for 1..8 token rows: int8 activations (quantised per 32 values inside the kernel) and
 // dp4a over the stored codes.  fmt: 1 Q8_0, 2 Q6_K, 3 Q4_K planes of ops/quant.py.
 int lk_gemv_q(int fmt, const void* codes, long long c_ld, const void* scales, long long s_ld, const void* x,
               long long ldx, int M, int N, int K, const float* bias, void* out, long long ldo, int out_fp32,
-              int* status, void* stream);
-// 0: every GEMV on the register form; 1 (default): the streaming form (bulk-copy ring) where the shape allows.
+              const LkGemvPre* pre, int* status, void* stream);
+// 0: every GEMV on the register form; 1 (default): the streaming form (bulk-copy ring) where the shape allows;
+// 3: the same plus L2 hints for the rows the ring does not hold yet.
 void lk_gemv_q_stream(int on);
 // The same planes decoded to bf16 out [rows, K], row pitch ldo elements: the operand of prompt-sized GEMMs.
 int lk_dequant_q(int fmt, const void* codes, long long c_ld, const void* scales, long long s_ld, void* out,

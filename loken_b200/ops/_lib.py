@@ -55,6 +55,16 @@ vp = C.c_void_p
 ll = C.c_longlong
 
 
+class GemvPre(C.Structure):
+    """LkGemvPre of loken_cuda.h: what a quantised GEMV computes its activations from, and a residual
+    update it applies on the side."""
+    _fields_ = [
+        ("mode", C.c_int), ("delta", vp), ("ldd", ll), ("gamma", vp), ("eps", C.c_float), ("glu_mode", C.c_int),
+        ("glu_alpha", C.c_float), ("glu_limit", C.c_float), ("upd_x", vp), ("upd_delta", vp), ("upd_ldx", ll),
+        ("upd_ldd", ll), ("upd_cols", C.c_int), ("prof", vp),
+    ]
+
+
 class GemmArgs(C.Structure):
     _fields_ = [
         ("kind", C.c_int), ("A", vp), ("B", vp), ("Ra", C.c_int), ("Rb", C.c_int), ("K", C.c_int),

@@ -21,7 +21,7 @@ import numpy as np
 import torch
 
 from ..formats import gguf
-from ._lib import GemmArgs, Workspace, check, cuda_lib, ptr, stream
+from ._lib import GemmArgs, GemvPre, Workspace, check, cuda_lib, ptr, stream
 from .gemm import KIND_BF16, NUM_SMS
 
 AQ_W8, AQ_W8G16, AQ_W4, AQ_MX4 = 1, 2, 3, 4
@@ -211,13 +211,59 @@ def embed_gguf(tokens: torch.Tensor, table: QuantWeight, out: Optional[torch.Ten
     return out
 
 
+def gemv_takes(M: int, w, x_stride: int = 0) -> bool:
+    """Does a product of M token rows with `w` run as the dp4a GEMV (the form that can take a `GemvFront`)?"""
+    return (isinstance(w, QuantWeight) and 0 < M <= GEMV_MAX_M and w.aq_fmt in (AQ_W8, AQ_W8G16, AQ_W4)
+            and x_stride % 8 == 0 and (1 if M == 1 else 2 if M == 2 else 4 if M <= 4 else 8) * w.K * 1.25 <= 200 * 1024)
+
+
+@dataclass
+class GemvFront:
+    """What runs in front of a GEMV inside its kernel instead of as kernels of its own.
+
+    norm / eps / delta : the activations are RMSNorm(x + delta) * norm (delta: an update of the residual
+                         stream that is still pending, or None); x itself is NOT written
+    glu                : (mode, alpha, limit): x is [gate | up], 2K wide, and the activations are the gated unit
+    update             : (rows, delta): rows += delta, applied on the side by one CTA: the pending update of
+                         an earlier GEMV of the step, whose readers are all done by now.  `rows` must not
+                         be this GEMV's own input."""
+    norm: Optional[torch.Tensor] = None
+    eps: float = 1e-6
+    delta: Optional[torch.Tensor] = None
+    glu: Optional[tuple] = None
+    update: Optional[tuple] = None
+    prof: Optional[torch.Tensor] = None        # measurement hook: int64 [CTAs, 8] time stamps (streaming form)
+
+    def pack(self, M: int) -> GemvPre:
+        a = GemvPre()
+        a.prof = ptr(self.prof)
+        if self.norm is not None:
+            assert self.norm.dtype == torch.float32
+            a.mode, a.gamma, a.eps = 1, ptr(self.norm), float(self.eps)
+            if self.delta is not None:
+                assert self.delta.dtype == torch.bfloat16 and self.delta.stride(1) == 1
+                a.delta, a.ldd = ptr(self.delta), self.delta.stride(0)
+        elif self.glu is not None:
+            a.mode, a.glu_mode, a.glu_alpha, a.glu_limit = 2, int(self.glu[0]), float(self.glu[1]), float(self.glu[2])
+        if self.update is not None:
+            ux, ud = self.update
+            assert ux.dtype == ud.dtype == torch.bfloat16 and ux.shape[1] == ud.shape[1] and ux.shape[0] >= M
+            a.upd_x, a.upd_delta, a.upd_ldx, a.upd_ldd, a.upd_cols = ptr(ux), ptr(ud), ux.stride(0), ud.stride(0), ux.shape[1]
+        return a
+
+
 def linear_gguf(x: torch.Tensor, w: QuantWeight, *, bias: Optional[torch.Tensor] = None,
-                out: Optional[torch.Tensor] = None, splits: int = 0, out_fp32: bool = False) -> torch.Tensor:
+                out: Optional[torch.Tensor] = None, splits: int = 0, out_fp32: bool = False,
+                front: Optional[GemvFront] = None) -> torch.Tensor:
     """x bf16 [M, K] @ W.T -> bf16 (or f32) [M, N].  Up to eight token rows run as a GEMV on int8 activations;
-    beyond that tokens ride the MMA N dimension in tiles of 16 / 64 / 128 with dequantising warps."""
-    M, K = x.shape
+    beyond that tokens ride the MMA N dimension in tiles of 16 / 64 / 128 with dequantising warps.  `front`
+    (GEMV only, see `gemv_takes`) fuses a norm or gated unit in front and a residual update on the side."""
+    M = x.shape[0]
+    K = w.K
     N = w.rows
-    assert K == w.K and x.stride(1) == 1
+    assert x.stride(1) == 1 and x.shape[1] == (2 * K if front is not None and front.glu is not None else K)
+    if front is not None and not gemv_takes(M, w, x.stride(0)):
+        raise ValueError("a fused front needs the GEMV path (see gemv_takes)")
     if out is None:
         out = torch.empty(M, N, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=x.device)
     if w.aq_fmt == AQ_MX4 and MX_NATIVE and K % 32 == 0:
@@ -229,12 +275,12 @@ def linear_gguf(x: torch.Tensor, w: QuantWeight, *, bias: Optional[torch.Tensor]
             w._mx = mx.mx_weight(w)
         xa = mx.quant_mx8(x, rows=M)
         return mx.linear_mx(xa, w._mx, bias=bias, out=out, rows=M)
-    if M <= GEMV_MAX_M and w.aq_fmt in (AQ_W8, AQ_W8G16, AQ_W4) and x.stride(0) % 8 == 0 \
-            and (1 if M == 1 else 2 if M == 2 else 4 if M <= 4 else 8) * K * 1.25 <= 200 * 1024:
+    if gemv_takes(M, w, x.stride(0)):
         # a handful of token rows: int8 activations and dp4a over the stored codes, every weight byte read once
         check(cuda_lib().lk_gemv_q(w.aq_fmt, ptr(w.codes), C.c_longlong(w.codes.stride(0)), ptr(w.scales),
                                    C.c_longlong(w.scales.stride(0)), ptr(x), C.c_longlong(x.stride(0)), M, N, K,
                                    ptr(bias), ptr(out), C.c_longlong(out.stride(0)), int(out_fp32),
+                                   C.byref(front.pack(M)) if front is not None else None,
                                    ptr(Workspace.get(x.device).status), stream()), "lk_gemv_q")
         return out
     if DEQUANT_ONCE_MIN_M and M >= DEQUANT_ONCE_MIN_M and w.aq_fmt in (AQ_W8, AQ_W8G16, AQ_W4) and K % 8 == 0 \

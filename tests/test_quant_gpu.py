@@ -123,3 +123,54 @@ def test_prompt_sized_gemm_decodes_the_matrix_once(fmt, M, N, K):
     assert Workspace.get(torch.device(DEV)).read_status() == 0
     assert once32.dtype == torch.float32
     assert rel_err(once, ref) < 1e-2 and rel_err(once32, ref) < 2e-3 and rel_err(once, fused) < 1e-2
+
+
+@pytest.mark.parametrize("fmt", ["q8_0", "q4_k", "q6_k"])
+@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("ring", [1, 0])                    # the bulk-copy ring and the register form
+def test_gemv_front_equals_the_separate_kernels(fmt, M, ring):
+    """A GEMV can compute its activations from RMSNorm(x + pending update) or from a gated unit and fold an
+    earlier update into the residual rows on the side: the result is that of the separate kernels."""
+    from loken_b200.ops import quant, rows
+    from loken_b200.ops._lib import Workspace, cuda_lib
+
+    K, N = 2048, 520
+    torch.manual_seed(M + K)
+    cuda_lib().lk_gemv_q_stream(ring)
+    try:
+        _front_case(quant, rows, fmt, M, N, K)
+    finally:
+        cuda_lib().lk_gemv_q_stream(1)
+    torch.cuda.synchronize()
+    assert Workspace.get(torch.device(DEV)).read_status() == 0
+
+
+def _front_case(quant, rows, fmt, M, N, K):
+    q = quant.quantize_weight(torch.randn(N, K, device=DEV) * 0.05, fmt)
+    x = torch.randn(M, K, device=DEV).bfloat16()
+    delta = (torch.randn(M, K, device=DEV) * 0.3).bfloat16()
+    gamma = 1 + 0.1 * torch.randn(K, device=DEV)
+    # norm in front; x itself stays as it was
+    x1 = x.clone()
+    h = torch.empty_like(x)
+    rows.add_rmsnorm(x1, gamma, 1e-5, delta=delta, out=h, rows=M)
+    want = quant.linear_gguf(h, q)
+    x2 = x.clone()
+    got = quant.linear_gguf(x2, q, front=quant.GemvFront(norm=gamma, eps=1e-5, delta=delta))
+    assert torch.equal(x2, x)
+    assert rel_err(got, want) < 1e-2
+    got0 = quant.linear_gguf(x1, q, front=quant.GemvFront(norm=gamma, eps=1e-5))        # nothing pending
+    assert rel_err(got0, want) < 1e-2
+    # gated unit in front, and the pending update folded into other rows on the side
+    for mode, alpha, limit in ((0, 0.0, 0.0), (1, 1.702, 7.0)):
+        gu = (torch.randn(M, 2 * K, device=DEV) * 2).bfloat16()
+        act = torch.empty(M, K, device=DEV, dtype=torch.bfloat16)
+        rows.glu(gu, mode=mode, alpha=alpha, limit=limit, out=act, rows=M)
+        want = quant.linear_gguf(act, q)
+        res = torch.randn(8, K, device=DEV).bfloat16()
+        res0 = res.clone()
+        got = quant.linear_gguf(gu, q, front=quant.GemvFront(glu=(mode, alpha, limit), update=(res, delta)))
+        assert rel_err(got, want) < 1e-2
+        assert torch.equal(res[:M], (res0[:M].float() + delta.float()).bfloat16()) and torch.equal(res[M:], res0[M:])
+    with pytest.raises(ValueError):
+        quant.linear_gguf(torch.zeros(9, K, device=DEV, dtype=torch.bfloat16), q, front=quant.GemvFront(norm=gamma))
