@@ -694,9 +694,17 @@ int launch_gs(const GvParams& p, cudaStream_t st, int* status, bool* taken) {
   if (MT > 4 || (MT == 4 && FMT == GV_W4)) return 0;
   const long long cb = gs_code_bytes<FMT>(p.K), sb = gs_scale_bytes<FMT>(p.K);
   if (p.c_ld != cb || p.s_ld != sb || (reinterpret_cast<uintptr_t>(p.scales) & 15)) return 0;
+  // rows per stage: eight or four when a ring of three such stages fits half of an SM's shared memory (two
+  // CTAs, sixteen consumer warps per SM: Q4_K 57344 x 8192 took 71 us with one CTA per SM and stages of eight
+  // rows); else as many as fit 64 KB, one CTA per SM
+  const size_t xb = (size_t)MT * p.K + (size_t)MT * (p.K >> 5) * 8 + 2048;
   int R = 8;
-  while (R > 1 && (size_t)R * (cb + sb) > 64 * 1024) R >>= 1;
-  if ((size_t)R * (cb + sb) > 64 * 1024) return 0;
+  while (R > 4 && xb + 3 * (size_t)R * (cb + sb) > 100 * 1024) R >>= 1;
+  if (xb + 3 * (size_t)R * (cb + sb) > 100 * 1024) {
+    R = 8;
+    while (R > 1 && (size_t)R * (cb + sb) > 64 * 1024) R >>= 1;
+    if ((size_t)R * (cb + sb) > 64 * 1024) return 0;
+  }
   const long long tail = p.N % R;
   if (((R * cb) & 15) || ((R * sb) & 15) || ((tail * cb) & 15) || ((tail * sb) & 15)) return 0;
   int rc;

@@ -9,6 +9,8 @@
     python -m loken_b200.utils.prof_cases attn_prefill --seqs 8 --ctx 2048
     python -m loken_b200.utils.prof_cases add_rmsnorm --batch 64      # also glu, rope_kv, embed
     python -m loken_b200.utils.prof_cases moe --batch 128 --fmt mxfp4
+    python -m loken_b200.utils.prof_cases gemm_q4_k --m 1             # up to 8 rows: the dp4a GEMV
+    python -m loken_b200.utils.prof_cases gemv_timeline --fmt q4_k --n 28672 --k 4096
 
 Each case warms up, then runs the measured launches between cudaProfilerStart/Stop, so a
 profiler started with `--profile-from-start off` sees only those.  Inputs are larger than the L2
@@ -75,7 +77,7 @@ def gemm_case(kind: str, M: int, N: int, K: int, swap_max_m: int = -1, bn: int =
     if kind in ("q8_0", "q4_k", "q6_k", "mxfp4"):
         from ..ops import quant
 
-        wq = quant.quantize_weight(w, kind)
+        wq = quant.quantize_weight_torch(w, kind)        # encoded on the device: seconds, not minutes
         del w
         fn = lambda: quant.linear_gguf(x, wq, out=out)
         nbytes = wq.nbytes()
@@ -220,6 +222,38 @@ def sampler_case(batch: int, vocab: int):
     print(f"sampler batch={batch} vocab={vocab}: {ms * 1e3:.1f} us, {batch * vocab * 4 / ms / 1e6:.0f} GB/s of logits")
 
 
+def gemv_timeline_case(fmt: str, N: int, K: int):
+    """Six back-to-back one-row GEMVs over six copies of a GGUF matrix (launched eagerly with programmatic
+    dependent launch, as in a decode step) with the streaming kernel's own time stamps: when each CTA entered,
+    when its wait for the kernel before ended, when the activations were staged, when the first stage of
+    weights had landed, when it finished, and when its producer issued the first and the last copy.  Printed
+    for the last two launches as min..max over CTAs, in us from the first entry."""
+    from ..ops import quant
+
+    dev = torch.device("cuda")
+    ws = [quant.quantize_weight_torch(torch.randn(N, K, device=dev) * 0.05, fmt) for _ in range(6)]
+    x = (torch.randn(1, K, device=dev) * 0.5).bfloat16()
+    out = torch.empty(1, N, dtype=torch.bfloat16, device=dev)
+    profs = [torch.zeros(300, 8, dtype=torch.int64, device=dev) for _ in range(2)]
+    torch.cuda.profiler.start()
+    for _ in range(3):
+        for i in range(6):
+            quant.linear_gguf(x, ws[i], out=out, front=quant.GemvFront(prof=profs[i % 2]))
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    a, b = profs[0].cpu(), profs[1].cpu()
+    a, b = a[a[:, 0] > 0], b[b[:, 0] > 0]
+    if len(a) == 0:
+        print(f"gemv_timeline {fmt} {N}x{K}: the streaming form did not take this shape")
+        return
+    t0 = int(a[:, 0].min())
+    names = ("entry", "wait ended", "staged", "first stage", "end", "first copy", "last copy")
+    print(f"gemv_timeline {fmt} {N}x{K}: {len(a)} CTAs, {ws[0].nbytes() / 1e6:.1f} MB")
+    for label, t in (("launch 5", a), ("launch 6", b)):
+        cols = [((t[:, i] - t0).float() / 1000) for i in range(7)]
+        print(f"  {label}: " + "  ".join(f"{n} {c.min():.1f}..{c.max():.1f}" for n, c in zip(names, cols)) + " us")
+
+
 def attn_prefill_case(n_seqs: int, ctx: int, n_q: int, n_kv: int):
     """Variable-length flash prefill over keys gathered from the q8 paged cache (kv_gather +
     attn_prefill_kernel), `n_seqs` prompts of `ctx` tokens."""
@@ -333,7 +367,7 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("case", choices=["gemm_sweep", "gemm_fp8", "gemm_bf16", "gemm_q8_0", "gemm_q4_k", "gemm_q6_k", "gemm_mxfp4",
                                     "decode_step", "attn_decode", "sampler", "attn_prefill", "add_rmsnorm", "glu",
-                                    "rope_kv", "embed", "moe"])
+                                    "rope_kv", "embed", "moe", "gemv_timeline"])
     ap.add_argument("--m", type=int, default=64)
     ap.add_argument("--n", type=int, default=57344)
     ap.add_argument("--k", type=int, default=8192)
@@ -360,6 +394,8 @@ def main(argv=None):
     a = ap.parse_args(argv)
     if a.case == "gemm_sweep":
         gemm_sweep_case(a.m, [tuple(int(t) for t in sh.split("x")) for sh in a.shapes.split(",")], a.variants.split(","))
+    elif a.case == "gemv_timeline":
+        gemv_timeline_case(a.fmt if a.fmt != "mxfp4" else "q4_k", a.n, a.k)
     elif a.case.startswith("gemm_"):
         gemm_case(a.case[5:], a.m, a.n, a.k, a.swap_max_m, a.bn, a.gemm_splits)
     elif a.case == "decode_step":
