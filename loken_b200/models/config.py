@@ -15,7 +15,7 @@ from typing import Dict, List, Optional
 ARCH_FACTS: Dict[str, dict] = {
     "llama": dict(rope_pairing=0),
     "mistral": dict(rope_pairing=0),
-    "qwen2": dict(rope_pairing=1),
+    "qwen2": dict(rope_pairing=1, attn_bias=True),
     "qwen3": dict(rope_pairing=1, qk_norm=True),
     "qwen3moe": dict(rope_pairing=1, qk_norm=True, router="softmax", renorm=True),
     "gpt-oss": dict(rope_pairing=1, swa_period=2, yarn_by_default=True, glu_mode=1, glu_alpha=1.702, glu_limit=7.0,
@@ -39,6 +39,8 @@ class RopeScaling:
     beta_fast: float = 32.0        # yarn
     beta_slow: float = 1.0         # yarn
     attn_factor: Optional[float] = None
+    truncate: bool = True          # yarn: the correction range is rounded outwards to whole dimensions (GGUF
+                                   # runtimes do; gpt-oss checkpoints say "truncate": false)
 
 
 @dataclass
@@ -134,8 +136,10 @@ class ModelConfig:
         elif sc.kind == "yarn":
             def corr_dim(n_rot):
                 return (rd * math.log(sc.original_context / (n_rot * 2 * math.pi))) / (2 * math.log(self.rope_theta))
-            lo = max(math.floor(corr_dim(sc.beta_fast)), 0)
-            hi = min(math.ceil(corr_dim(sc.beta_slow)), rd - 1)
+            lo, hi = corr_dim(sc.beta_fast), corr_dim(sc.beta_slow)
+            if sc.truncate:
+                lo, hi = math.floor(lo), math.ceil(hi)
+            lo, hi = max(lo, 0), min(hi, rd - 1)
             out = []
             for i, f in enumerate(inv):
                 ramp = min(max((i - lo) / max(hi - lo, 1e-3), 0.0), 1.0)

@@ -21,7 +21,13 @@ from .config import ARCH_FACTS, ModelConfig, RopeScaling
 from .weights import LayerWeights, Linear, ModelWeights, make_linear
 
 HF_ARCH = {"LlamaForCausalLM": "llama", "MistralForCausalLM": "mistral", "Qwen2ForCausalLM": "qwen2",
-           "Qwen3ForCausalLM": "qwen3", "GptOssForCausalLM": "gpt-oss"}
+           "Qwen3ForCausalLM": "qwen3", "GptOssForCausalLM": "gpt-oss", "MixtralForCausalLM": "mixtral",
+           "Qwen3MoeForCausalLM": "qwen3moe"}
+# mixture families that store one tensor per expert and matrix: (router, expert stem, gate, up, down)
+HF_EXPERT_NAMES = {
+    "mixtral": ("block_sparse_moe.gate", "block_sparse_moe.experts.{e}.", "w1", "w3", "w2"),
+    "qwen3moe": ("mlp.gate", "mlp.experts.{e}.", "gate_proj", "up_proj", "down_proj"),
+}
 
 
 def config_from_hf(cfg: dict, name: str = "hf") -> ModelConfig:
@@ -30,23 +36,38 @@ def config_from_hf(cfg: dict, name: str = "hf") -> ModelConfig:
     n_q = int(cfg["num_attention_heads"])
     hidden = int(cfg["hidden_size"])
     sc = RopeScaling()
-    rs = cfg.get("rope_scaling") or {}
-    if rs.get("rope_type", rs.get("type")) in ("linear", "yarn"):
-        sc = RopeScaling(kind=rs.get("rope_type", rs.get("type")), factor=float(rs.get("factor", 1.0)),
-                         original_context=int(rs.get("original_max_position_embeddings", 8192)))
+    # `rope_scaling` in older files, `rope_parameters` (which also carries the base) in newer ones
+    rs = cfg.get("rope_scaling") or cfg.get("rope_parameters") or {}
+    theta = cfg.get("rope_theta") or rs.get("rope_theta")
+    kind = rs.get("rope_type", rs.get("type"))
+    if kind in ("linear", "yarn"):
+        sc = RopeScaling(kind=kind, factor=float(rs.get("factor", 1.0)),
+                         original_context=int(rs.get("original_max_position_embeddings", 8192)),
+                         beta_fast=float(rs.get("beta_fast") or 32.0), beta_slow=float(rs.get("beta_slow") or 1.0),
+                         attn_factor=rs.get("attention_factor"), truncate=bool(rs.get("truncate", True)))
+        if kind == "yarn" and sc.attn_factor is None and sc.factor > 1:
+            import math
+
+            sc.attn_factor = 0.1 * math.log(sc.factor) + 1.0        # what these files mean when they say nothing
+    elif kind == "llama3":
+        sc = RopeScaling(kind="llama3", factor=float(rs.get("factor", 8.0)),
+                         original_context=int(rs.get("original_max_position_embeddings", 8192)),
+                         low_freq_factor=float(rs.get("low_freq_factor", 1.0)),
+                         high_freq_factor=float(rs.get("high_freq_factor", 4.0)))
     qc = cfg.get("quantization_config") or {}
     fmt = "fp8_block" if qc.get("quant_method") == "fp8" and qc.get("weight_block_size") else "bf16"
     if arch == "gpt-oss":
         # mixture of experts with MXFP4 expert matrices (`*_blocks` / `*_scales`), attention sinks, a sliding
         # window on alternate layers, YaRN, biases everywhere, the clamped SwiGLU
-        if rs.get("rope_type", rs.get("type")) == "yarn":
+        if kind == "yarn":
             sc = RopeScaling(kind="yarn", factor=float(rs.get("factor", 32.0)),
                              original_context=int(rs.get("original_max_position_embeddings", 4096)),
-                             beta_fast=float(rs.get("beta_fast", 32.0)), beta_slow=float(rs.get("beta_slow", 1.0)))
+                             beta_fast=float(rs.get("beta_fast", 32.0)), beta_slow=float(rs.get("beta_slow", 1.0)),
+                             attn_factor=rs.get("attention_factor"), truncate=bool(rs.get("truncate", True)))
         out = ModelConfig(name=name, arch=arch, n_layers=int(cfg["num_hidden_layers"]), hidden=hidden, n_q=n_q,
                           n_kv=int(cfg.get("num_key_value_heads", n_q)), head_dim=int(cfg.get("head_dim") or hidden // n_q),
                           intermediate=int(cfg["intermediate_size"]), vocab=int(cfg["vocab_size"]),
-                          rope_theta=float(cfg.get("rope_theta", 150000.0)), rope_pairing=1, rope_scaling=sc,
+                          rope_theta=float(theta or 150000.0), rope_pairing=1, rope_scaling=sc,
                           rms_eps=float(cfg.get("rms_norm_eps", 1e-5)), attn_bias=True,
                           context_length=int(cfg.get("max_position_embeddings", 131072)),
                           tie_embeddings=bool(cfg.get("tie_word_embeddings", False)),
@@ -61,14 +82,25 @@ def config_from_hf(cfg: dict, name: str = "hf") -> ModelConfig:
         if isinstance(kinds, list) and len(kinds) == out.n_layers:
             out.swa_layers = [k == "sliding_attention" for k in kinds]
         return out
+    moe = {}
+    if arch in HF_EXPERT_NAMES:
+        # softmax over all experts, the best k kept (and, unless the file says otherwise, renormalised)
+        n_exp = int(cfg.get("num_local_experts") or cfg.get("num_experts"))
+        moe = dict(n_experts=n_exp, top_k=int(cfg.get("num_experts_per_tok", 2)),
+                   expert_intermediate=int(cfg.get("moe_intermediate_size") or cfg["intermediate_size"]),
+                   router=facts.get("router", "softmax"),
+                   renorm=bool(cfg.get("norm_topk_prob", True)) if arch == "qwen3moe" else facts.get("renorm", True))
+        if any(int(x) for x in (cfg.get("mlp_only_layers") or [])) or int(cfg.get("decoder_sparse_step", 1) or 1) != 1:
+            raise ValueError("checkpoints that mix dense and mixture layers are not read")
     # HF checkpoints store q/k in the half-split (NeoX) layout whatever the family
-    return ModelConfig(name=name, arch=arch, n_layers=int(cfg["num_hidden_layers"]), hidden=hidden, n_q=n_q,
+    return ModelConfig(name=name, arch=arch, n_layers=int(cfg["num_hidden_layers"]), hidden=hidden, n_q=n_q, **moe,
+                       sliding_window=int(cfg.get("sliding_window") or 0) if arch in ("mistral", "mixtral") else 0,
                        n_kv=int(cfg.get("num_key_value_heads", n_q)),
                        head_dim=int(cfg.get("head_dim") or hidden // n_q),
                        intermediate=int(cfg["intermediate_size"]), vocab=int(cfg["vocab_size"]),
-                       rope_theta=float(cfg.get("rope_theta", 10000.0)), rope_pairing=1, rope_scaling=sc,
+                       rope_theta=float(theta or 10000.0), rope_pairing=1, rope_scaling=sc,
                        rms_eps=float(cfg.get("rms_norm_eps", 1e-5)), qk_norm=facts.get("qk_norm", False),
-                       attn_bias=bool(cfg.get("attention_bias", False)),
+                       attn_bias=bool(cfg.get("attention_bias", facts.get("attn_bias", False))),
                        context_length=int(cfg.get("max_position_embeddings", 8192)),
                        tie_embeddings=bool(cfg.get("tie_word_embeddings", False)), weight_format=fmt)
 
@@ -203,6 +235,26 @@ def _oss_experts(sh: _Shards, stem: str, what: str, cfg: ModelConfig, elo: int, 
     return w, (bias.to(device).contiguous() if bias is not None else None), fmt
 
 
+def _stacked_experts(sh: _Shards, layer_stem: str, cfg: ModelConfig, elo: int, ecnt: int, device, requant):
+    """Experts stored one tensor per expert and matrix (Mixtral: w1 / w3 / w2; Qwen3-MoE: gate_proj / up_proj /
+    down_proj) -> this library's stacked layout: [E_local * 2I, H] with every expert's gate rows first, then
+    its up rows, and [E_local * H, I]."""
+    from ..ops import quant as Q
+    from .moe import MoeWeights
+
+    router, stem, gname, uname, dname = HF_EXPERT_NAMES[cfg.arch]
+    gu, dn = [], []
+    for e in range(elo, elo + ecnt):
+        es = layer_stem + stem.format(e=e)
+        gu += [sh.get(es + gname + ".weight").float(), sh.get(es + uname + ".weight").float()]
+        dn.append(sh.get(es + dname + ".weight").float())
+    gu, dn = torch.cat(gu, 0), torch.cat(dn, 0)
+    fmt = requant if requant in ("mxfp4", "q8_0", "q4_k", "q6_k") else "bf16"
+    conv = (lambda w: w.to(device).bfloat16()) if fmt == "bf16" else (lambda w: Q.quantize_weight(w.to(device), fmt))
+    return MoeWeights(sh.get(layer_stem + router + ".weight").to(device).bfloat16(), None, conv(gu), conv(dn), None, None,
+                      elo, ecnt, fmt)
+
+
 def load_hf(directory: str, device, *, tp_rank: int = 0, tp_size: int = 1, requant: Optional[str] = None,
             kv_format: Optional[str] = None):
     """-> (ModelWeights, hf config dict).  Under tensor parallelism a mixture model's experts are split
@@ -250,7 +302,7 @@ def load_hf(directory: str, device, *, tp_rank: int = 0, tp_size: int = 1, requa
         p = f"model.layers.{il}."
         a = p + "self_attn."
         bqkv = bo = None
-        if cfg.attn_bias and sh.has(a + "q_proj.bias"):
+        if sh.has(a + "q_proj.bias"):               # Qwen2 files carry q/k/v biases without saying so in the config
             bqkv = torch.cat([vec(a + "q_proj.bias")[q_sl], vec(a + "k_proj.bias")[kv_sl],
                               vec(a + "v_proj.bias")[kv_sl]]).contiguous()
             if sh.has(a + "o_proj.bias"):
@@ -276,6 +328,9 @@ def load_hf(directory: str, device, *, tp_rank: int = 0, tp_size: int = 1, requa
             lw.moe = MoeWeights(sh.get(m + "router.weight").to(device).bfloat16(),
                                 vec(m + "router.bias") if sh.has(m + "router.bias") else None,
                                 gu, dn, gub, dnb, elo, ecnt, fmt)
+        elif cfg.is_moe and cfg.arch in HF_EXPERT_NAMES:
+            ecnt = cfg.n_experts // tp_size
+            lw.moe = _stacked_experts(sh, p, cfg, tp_rank * ecnt, ecnt, device, requant)
         else:
             lw.w_gate_up = linear([m + "gate_proj", m + "up_proj"], [i_sl, i_sl])
             lw.w_down = linear([m + "down_proj"], [None], col=i_sl if tp_size > 1 else None)

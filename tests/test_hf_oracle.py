@@ -1,0 +1,79 @@
+"""Families read from Hugging Face checkpoints against the `transformers` implementation itself: a tiny random
+model of each class is saved as safetensors, read by `load_hf` on the CPU and run through the fp32 reference
+forward; the logits of every position have to agree (the reference's own oracle tests do the same against
+stored vectors, with cosine >= 0.998 and the same argmax where the top-2 gap is clear)."""
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+
+
+def _tiny(cls_name):
+    c = dict(vocab_size=320, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+             num_key_value_heads=2, max_position_embeddings=256, rms_norm_eps=1e-5, rope_theta=10000.0,
+             tie_word_embeddings=False, attention_dropout=0.0)
+    if cls_name == "Llama":
+        return transformers.LlamaConfig(**c), transformers.LlamaForCausalLM
+    if cls_name == "Mistral":
+        return transformers.MistralConfig(**c, sliding_window=None), transformers.MistralForCausalLM
+    if cls_name == "Qwen2":
+        return transformers.Qwen2Config(**c), transformers.Qwen2ForCausalLM
+    if cls_name == "Qwen3":
+        return transformers.Qwen3Config(**c, head_dim=32), transformers.Qwen3ForCausalLM
+    if cls_name == "Mixtral":
+        return (transformers.MixtralConfig(**c, num_local_experts=4, num_experts_per_tok=2, sliding_window=None),
+                transformers.MixtralForCausalLM)
+    if cls_name == "Qwen3Moe":
+        return (transformers.Qwen3MoeConfig(**c, head_dim=32, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48,
+                                            norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[]),
+                transformers.Qwen3MoeForCausalLM)
+    if cls_name == "Llama3Rope":
+        rope = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                "original_max_position_embeddings": 32, "rope_theta": 500000.0}
+        c.pop("rope_theta")
+        return transformers.LlamaConfig(**c, rope_parameters=rope), transformers.LlamaForCausalLM
+    if cls_name == "Qwen3Yarn":
+        rope = {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 64, "rope_theta": 1000000.0}
+        c.pop("rope_theta")
+        return transformers.Qwen3Config(**c, head_dim=32, rope_parameters=rope), transformers.Qwen3ForCausalLM
+    if cls_name == "GptOss":
+        # sinks, a sliding window on alternate layers, biases everywhere, the clamped gated unit, softmax over the
+        # chosen experts, YaRN without rounding of the correction range
+        c.pop("rope_theta")
+        rope = {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 64, "beta_fast": 32.0,
+                "beta_slow": 1.0, "truncate": False, "rope_theta": 150000.0}
+        return (transformers.GptOssConfig(**c, head_dim=32, num_local_experts=4, num_experts_per_tok=2, sliding_window=8,
+                                          layer_types=["sliding_attention", "full_attention"], rope_parameters=rope),
+                transformers.GptOssForCausalLM)
+    raise KeyError(cls_name)
+
+
+@pytest.mark.parametrize("family", ["Llama", "Mistral", "Qwen2", "Qwen3", "Mixtral", "Qwen3Moe", "GptOss", "Llama3Rope",
+                                    "Qwen3Yarn"])
+def test_logits_match_transformers(tmp_path, family):
+    from loken_b200.models import loader_hf
+    from loken_b200.models.reference import forward_ref
+
+    torch.manual_seed(3)
+    hc, cls = _tiny(family)
+    model = cls(hc).float().eval()
+    with torch.no_grad():
+        for p in model.parameters():                 # the default init is too narrow for a routing or argmax test
+            if p.dim() >= 2:
+                p.normal_(0.0, 0.08)
+            elif p.dim() == 1 and p.numel() > 1:
+                p.add_(torch.randn_like(p) * 0.05)
+    model.save_pretrained(str(tmp_path), safe_serialization=True)
+    w, hf = loader_hf.load_hf(str(tmp_path), torch.device("cpu"))
+    assert w.cfg.is_moe == (family in ("Mixtral", "Qwen3Moe", "GptOss"))
+    toks = torch.randint(0, hc.vocab_size, (40,), generator=torch.Generator().manual_seed(1)).tolist()
+    with torch.no_grad():
+        want = model(torch.tensor([toks])).logits[0].float()
+    got = forward_ref(w, toks).float()
+    assert got.shape == want.shape
+    cos = torch.nn.functional.cosine_similarity(got, want, dim=1)
+    # weights pass through bf16 on the way in: that, not the arithmetic, is the difference
+    assert cos.min().item() > 0.998, cos
+    top2 = want.topk(2, dim=1).values
+    clear = (top2[:, 0] - top2[:, 1]) > 0.05 * want.abs().amax(1)
+    assert torch.equal(got.argmax(1)[clear], want.argmax(1)[clear])
