@@ -26,6 +26,7 @@ ARCH_FACTS: Dict[str, dict] = {
     "mixtral": dict(rope_pairing=0, router="softmax", renorm=True),
     "olmoe": dict(rope_pairing=1, router="softmax", renorm=False),
     "phi3": dict(rope_pairing=1),
+    "granite": dict(rope_pairing=0),
 }
 
 
@@ -117,6 +118,8 @@ class ModelConfig:
         mscale = 1.0
         if self.rope_freq_factors is not None:
             inv = [f / d for f, d in zip(inv, self.rope_freq_factors)]
+            if sc.attn_factor is not None:
+                mscale = sc.attn_factor
         elif sc.kind == "linear":
             inv = [f / sc.factor for f in inv]
         elif sc.kind == "llama3":
@@ -196,6 +199,8 @@ class ModelConfig:
                   glu_alpha=facts.get("glu_alpha", 1.702), glu_limit=facts.get("glu_limit", 7.0),
                   embedding_scale=float(g("embedding_scale", 1.0) or 1.0),
                   logit_scale=float(g("logit_scale", 1.0) or 1.0), attn_scale=g("attention.scale"))
+        if arch == "granite" and cfg.logit_scale not in (0.0, 1.0):
+            cfg.logit_scale = 1.0 / cfg.logit_scale           # these files store the divisor of the logits
         pat = g("attention.sliding_window_pattern")
         if isinstance(pat, list):
             cfg.swa_layers = [bool(x) for x in pat]

@@ -99,6 +99,21 @@ def _linear_from(parts: List[Tuple[_Src, Optional[slice]]], device, requant: Opt
     return make_linear(t, fmt, bias)
 
 
+def _scale_linear(lin: Linear, mul: float) -> Linear:
+    """Folds a multiplier on the layer's output into its weights (Granite's residual multiplier)."""
+    if mul == 1.0:
+        return lin
+    if lin.kind == "bf16":
+        lin.weight = (lin.weight.float() * mul).bfloat16()
+    elif lin.kind == "gguf":
+        quant.scale_weight_(lin.weight, mul)
+    else:
+        raise NotImplementedError(f"a residual multiplier on {lin.kind} weights")
+    if lin.bias is not None:
+        lin.bias = lin.bias * mul
+    return lin
+
+
 def _vec(r: G.GGUFReader, name: str, device, sl: Optional[slice] = None) -> Optional[torch.Tensor]:
     if name not in r.tensors:
         return None
@@ -176,6 +191,8 @@ def load_gguf(path: str, device, *, tp_rank: int = 0, tp_size: int = 1, ep_rank:
                       torch.tensor(inv, dtype=torch.float32, device=device), mscale, tp_rank, tp_size, nql, nkvl, vl,
                       tp_rank * vl if tp_size > 1 else 0)
     mw.layer_range = tuple(layer_range) if layer_range is not None else None
+    # Granite: every block's output is multiplied before it joins the residual stream; folded into the weights
+    res_mul = float(meta.get(f"{cfg.arch}.residual_scale", 1.0) or 1.0) if cfg.arch == "granite" else 1.0
     for il in range(cfg.n_layers):
         if layer_range is not None and not (layer_range[0] <= il < layer_range[1]):
             mw.layers.append(None)
@@ -196,8 +213,8 @@ def load_gguf(path: str, device, *, tp_rank: int = 0, tp_size: int = 1, ep_rank:
         bo = _vec(r, p + "attn_output.bias", device)
         if bo is not None and tp_rank != 0:
             bo = torch.zeros_like(bo)
-        wo = _linear_from([(T(p + "attn_output.weight"), None)], device, requant, bo,
-                          col_sl=q_sl if tp_size > 1 else None)
+        wo = _scale_linear(_linear_from([(T(p + "attn_output.weight"), None)], device, requant, bo,
+                                        col_sl=q_sl if tp_size > 1 else None), res_mul)
         ffn_norm = _vec(r, p + "ffn_norm.weight", device)
         if ffn_norm is None:
             ffn_norm = _vec(r, p + "post_attention_norm.weight", device)
@@ -214,10 +231,14 @@ def load_gguf(path: str, device, *, tp_rank: int = 0, tp_size: int = 1, ep_rank:
             I = cfg.intermediate
             il_ = I // tp_size
             i_sl = slice(tp_rank * il_, (tp_rank + 1) * il_)
-            lw.w_gate_up = _linear_from([(T(p + "ffn_gate.weight"), i_sl), (T(p + "ffn_up.weight"), i_sl)], device,
-                                        requant)
-            lw.w_down = _linear_from([(T(p + "ffn_down.weight"), None)], device, requant,
-                                     col_sl=i_sl if tp_size > 1 else None)
+            if has(p + "ffn_gate.weight"):
+                gu_parts = [(T(p + "ffn_gate.weight"), i_sl), (T(p + "ffn_up.weight"), i_sl)]
+            else:           # Phi-3: gate rows, then up rows, in one tensor
+                up = T(p + "ffn_up.weight")
+                gu_parts = [(up, i_sl), (up, slice(I + i_sl.start, I + i_sl.stop))]
+            lw.w_gate_up = _linear_from(gu_parts, device, requant)
+            lw.w_down = _scale_linear(_linear_from([(T(p + "ffn_down.weight"), None)], device, requant,
+                                                   col_sl=i_sl if tp_size > 1 else None), res_mul)
         mw.layers.append(lw)
     r.close()
     return mw, meta

@@ -22,7 +22,7 @@ from .weights import LayerWeights, Linear, ModelWeights, make_linear
 
 HF_ARCH = {"LlamaForCausalLM": "llama", "MistralForCausalLM": "mistral", "Qwen2ForCausalLM": "qwen2",
            "Qwen3ForCausalLM": "qwen3", "GptOssForCausalLM": "gpt-oss", "MixtralForCausalLM": "mixtral",
-           "Qwen3MoeForCausalLM": "qwen3moe"}
+           "Qwen3MoeForCausalLM": "qwen3moe", "Phi3ForCausalLM": "phi3", "GraniteForCausalLM": "granite"}
 # mixture families that store one tensor per expert and matrix: (router, expert stem, gate, up, down)
 HF_EXPERT_NAMES = {
     "mixtral": ("block_sparse_moe.gate", "block_sparse_moe.experts.{e}.", "w1", "w3", "w2"),
@@ -82,11 +82,34 @@ def config_from_hf(cfg: dict, name: str = "hf") -> ModelConfig:
         if isinstance(kinds, list) and len(kinds) == out.n_layers:
             out.swa_layers = [k == "sliding_attention" for k in kinds]
         return out
-    moe = {}
+    extra = {}
+    if kind in ("longrope", "su"):
+        # Phi-3 long-context files: one divisor per rotary pair, the long list once the context exceeds the
+        # length the model was trained at (chosen for the configured context, not per sequence), and a
+        # magnitude factor on cos / sin
+        import math
+
+        orig = int(cfg.get("original_max_position_embeddings") or rs.get("original_max_position_embeddings") or 4096)
+        ctx = int(cfg.get("max_position_embeddings", orig))
+        extra["rope_freq_factors"] = [float(x) for x in (rs["long_factor"] if ctx > orig else rs["short_factor"])]
+        f = rs.get("attention_factor")
+        if f is None:
+            f = math.sqrt(1.0 + math.log(ctx / orig) / math.log(orig)) if ctx > orig else 1.0
+        sc = RopeScaling(kind="none", attn_factor=float(f))
+    if arch == "granite":
+        # four multipliers: on the embeddings, on the attention scores (instead of 1 / sqrt(head_dim)), on every
+        # block's output before it joins the residual stream (folded into the o and down projections at load),
+        # and a divisor of the logits
+        extra.update(embedding_scale=float(cfg.get("embedding_multiplier", 1.0)),
+                     attn_scale=float(cfg["attention_multiplier"]) if cfg.get("attention_multiplier") else None,
+                     logit_scale=1.0 / float(cfg.get("logits_scaling", 1.0) or 1.0))
+    if cfg.get("partial_rotary_factor") not in (None, 1.0):
+        extra["rope_dim"] = int(float(cfg["partial_rotary_factor"]) * int(cfg.get("head_dim") or hidden // n_q))
+    moe = extra
     if arch in HF_EXPERT_NAMES:
         # softmax over all experts, the best k kept (and, unless the file says otherwise, renormalised)
         n_exp = int(cfg.get("num_local_experts") or cfg.get("num_experts"))
-        moe = dict(n_experts=n_exp, top_k=int(cfg.get("num_experts_per_tok", 2)),
+        moe = dict(extra, n_experts=n_exp, top_k=int(cfg.get("num_experts_per_tok", 2)),
                    expert_intermediate=int(cfg.get("moe_intermediate_size") or cfg["intermediate_size"]),
                    router=facts.get("router", "softmax"),
                    renorm=bool(cfg.get("norm_topk_prob", True)) if arch == "qwen3moe" else facts.get("renorm", True))
@@ -286,13 +309,19 @@ def load_hf(directory: str, device, *, tp_rank: int = 0, tp_size: int = 1, requa
                       torch.tensor(inv, dtype=torch.float32, device=device), mscale, tp_rank, tp_size, nql, nkvl, vl,
                       tp_rank * vl if tp_size > 1 else 0)
 
-    def linear(stems, rows, col=None, bias=None):
+    # Granite: every block's output is multiplied before it joins the residual stream; folded into the weights
+    res_mul = float(hf.get("residual_multiplier", 1.0) or 1.0) if cfg.arch == "granite" else 1.0
+
+    def linear(stems, rows, col=None, bias=None, mul: float = 1.0):
         fp8 = all(sh.has(s + ".weight") and sh.get(s + ".weight").dtype == torch.float8_e4m3fn for s in stems)
-        if fp8 and requant in (None, "fp8_block"):
+        if fp8 and requant in (None, "fp8_block") and mul == 1.0:
             lin = _fp8_linear(sh, stems, rows, device, col, bias)
             if lin is not None:
                 return lin
         w = torch.cat([_float_rows(sh, s, r, col) for s, r in zip(stems, rows)], 0).to(device)
+        if mul != 1.0:
+            w = w * mul
+            bias = bias * mul if bias is not None else None
         fmt = requant or ("fp8_block" if fp8 else "bf16")
         if fmt == "fp8_block" and (w.shape[0] % 128 or w.shape[1] % 128):
             fmt = "bf16"
@@ -307,10 +336,16 @@ def load_hf(directory: str, device, *, tp_rank: int = 0, tp_size: int = 1, requa
                               vec(a + "v_proj.bias")[kv_sl]]).contiguous()
             if sh.has(a + "o_proj.bias"):
                 bo = vec(a + "o_proj.bias") if tp_rank == 0 else torch.zeros(H, device=device)
+        if sh.has(a + "qkv_proj.weight"):
+            # Phi-3: one tensor holds the q rows, then the k rows, then the v rows
+            k0, v0 = cfg.n_q * hd, (cfg.n_q + cfg.n_kv) * hd
+            shift = lambda sl, off: slice(sl.start + off, sl.stop + off)
+            wqkv = linear([a + "qkv_proj"] * 3, [q_sl, shift(kv_sl, k0), shift(kv_sl, v0)], bias=bqkv)
+        else:
+            wqkv = linear([a + "q_proj", a + "k_proj", a + "v_proj"], [q_sl, kv_sl, kv_sl], bias=bqkv)
         lw = LayerWeights(attn_norm=vec(p + "input_layernorm.weight"),
-                          ffn_norm=vec(p + "post_attention_layernorm.weight"),
-                          wqkv=linear([a + "q_proj", a + "k_proj", a + "v_proj"], [q_sl, kv_sl, kv_sl], bias=bqkv),
-                          wo=linear([a + "o_proj"], [None], col=q_sl if tp_size > 1 else None, bias=bo),
+                          ffn_norm=vec(p + "post_attention_layernorm.weight"), wqkv=wqkv,
+                          wo=linear([a + "o_proj"], [None], col=q_sl if tp_size > 1 else None, bias=bo, mul=res_mul),
                           window=cfg.layer_window(il))
         if sh.has(a + "q_norm.weight"):
             lw.q_norm, lw.k_norm = vec(a + "q_norm.weight"), vec(a + "k_norm.weight")
@@ -332,8 +367,12 @@ def load_hf(directory: str, device, *, tp_rank: int = 0, tp_size: int = 1, requa
             ecnt = cfg.n_experts // tp_size
             lw.moe = _stacked_experts(sh, p, cfg, tp_rank * ecnt, ecnt, device, requant)
         else:
-            lw.w_gate_up = linear([m + "gate_proj", m + "up_proj"], [i_sl, i_sl])
-            lw.w_down = linear([m + "down_proj"], [None], col=i_sl if tp_size > 1 else None)
+            if sh.has(m + "gate_up_proj.weight"):          # Phi-3: gate rows, then up rows, in one tensor
+                I = cfg.intermediate
+                lw.w_gate_up = linear([m + "gate_up_proj"] * 2, [i_sl, slice(i_sl.start + I, i_sl.stop + I)])
+            else:
+                lw.w_gate_up = linear([m + "gate_proj", m + "up_proj"], [i_sl, i_sl])
+            lw.w_down = linear([m + "down_proj"], [None], col=i_sl if tp_size > 1 else None, mul=res_mul)
         mw.layers.append(lw)
     return mw, hf
 

@@ -131,6 +131,24 @@ def quantize_weight(w: torch.Tensor, fmt: str) -> QuantWeight:
     return from_blocks(raw, ty, rows, K, w.device)
 
 
+def scale_weight_(q: QuantWeight, mul: float) -> QuantWeight:
+    """W *= mul in place, by multiplying the half-precision scale fields of every block (the codes stay): what
+    folds a per-layer multiplier of a file's metadata into a stored matrix."""
+    rows, K = q.rows, q.K
+    s = q.scales
+    if q.aq_fmt == AQ_W8:
+        h = s.view(torch.float16)
+        h.copy_((h.float() * mul).half())
+    elif q.aq_fmt in (AQ_W8G16, AQ_W4):
+        rec_bytes, n_half = (18, 1) if q.aq_fmt == AQ_W8G16 else (20, 2)
+        rec = s.view(rows, K // 256, rec_bytes)
+        h = rec[:, :, :2 * n_half].contiguous().view(torch.float16)
+        rec[:, :, :2 * n_half] = (h.float() * mul).half().view(torch.uint8).view(rows, K // 256, 2 * n_half)
+    else:
+        raise ValueError("a power-of-two exponent format cannot take an arbitrary multiplier")
+    return q
+
+
 def dequantize_weight(q: QuantWeight) -> torch.Tensor:
     """fp32 [rows, K]: what the kernel multiplies by before its bf16 rounding."""
     rows, K = q.rows, q.K

@@ -27,6 +27,19 @@ def _tiny(cls_name):
         return (transformers.Qwen3MoeConfig(**c, head_dim=32, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48,
                                             norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[]),
                 transformers.Qwen3MoeForCausalLM)
+    if cls_name == "Phi3":
+        return transformers.Phi3Config(**c, pad_token_id=0), transformers.Phi3ForCausalLM
+    if cls_name == "Phi3Long":
+        c.pop("rope_theta")
+        c["max_position_embeddings"] = 256
+        rope = {"rope_type": "longrope", "short_factor": [1.0 + 0.05 * i for i in range(8)],
+                "long_factor": [1.5 + 0.3 * i for i in range(8)], "rope_theta": 10000.0,
+                "original_max_position_embeddings": 64}
+        return (transformers.Phi3Config(**c, pad_token_id=0, original_max_position_embeddings=64, rope_parameters=rope),
+                transformers.Phi3ForCausalLM)
+    if cls_name == "Granite":
+        return (transformers.GraniteConfig(**c, embedding_multiplier=6.0, attention_multiplier=0.1, residual_multiplier=0.4,
+                                           logits_scaling=3.0), transformers.GraniteForCausalLM)
     if cls_name == "Llama3Rope":
         rope = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
                 "original_max_position_embeddings": 32, "rope_theta": 500000.0}
@@ -49,7 +62,7 @@ def _tiny(cls_name):
 
 
 @pytest.mark.parametrize("family", ["Llama", "Mistral", "Qwen2", "Qwen3", "Mixtral", "Qwen3Moe", "GptOss", "Llama3Rope",
-                                    "Qwen3Yarn"])
+                                    "Qwen3Yarn", "Phi3", "Phi3Long", "Granite"])
 def test_logits_match_transformers(tmp_path, family):
     from loken_b200.models import loader_hf
     from loken_b200.models.reference import forward_ref
@@ -66,7 +79,10 @@ def test_logits_match_transformers(tmp_path, family):
     model.save_pretrained(str(tmp_path), safe_serialization=True)
     w, hf = loader_hf.load_hf(str(tmp_path), torch.device("cpu"))
     assert w.cfg.is_moe == (family in ("Mixtral", "Qwen3Moe", "GptOss"))
-    toks = torch.randint(0, hc.vocab_size, (40,), generator=torch.Generator().manual_seed(1)).tolist()
+    # (Phi-3's long-context files switch to their long divisors once a sequence is longer than the trained length;
+    # the loader picks the list for the configured context, so that case runs a sequence beyond that length)
+    n_tok = 80 if family == "Phi3Long" else 40
+    toks = torch.randint(0, hc.vocab_size, (n_tok,), generator=torch.Generator().manual_seed(1)).tolist()
     with torch.no_grad():
         want = model(torch.tensor([toks])).logits[0].float()
     got = forward_ref(w, toks).float()
