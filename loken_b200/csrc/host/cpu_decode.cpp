@@ -6,7 +6,8 @@
 //     matrix product; a Q8_0 x Q8_0 row dot is per block (sum a*b as i32) * d_x * d_y, one f32
 //     rounding per block; AVX-512 VNNI, AVX2 and scalar versions picked at run time, the scalar
 //     one being the definition the others are tested against;
-//   * other weight formats (Q4_K, Q6_K, F16, BF16, F32) go through a row dequantiser + f32 dot;
+//   * Q4_K and Q6_K rows take integer dots with the same Q8_0 activation (their sub-blocks sit inside its
+//     blocks of 32), AVX2 and scalar; the float formats (F16, BF16, F32) a row conversion + f32 dot;
 //   * one arena of per-token scratch sized once from the model shape — no allocation per token;
 //   * a persistent worker pool: workers spin briefly on a generation counter, take chunk indices
 //     from a shared ticket word, and park on a condition variable when nothing arrives;
@@ -94,6 +95,161 @@ DotFn pick_dot(int level) {
 #endif
   (void)level;
   return dot_q8_scalar;
+}
+
+// ---- K-quant rows against Q8_0 activations -----------------------------------------------------
+// The activation of a product is quantised per 32 values (Q8_0), and both K formats are built from groups
+// that sit inside such a block, so their row dots run on the stored integer codes as well:
+//   Q4_K  sub-block s (32 values, 6-bit scale sc and minimum m against the block's d, dmin):
+//           dx * (d * sc * sum(q * xq) - dmin * m * sum(xq))
+//   Q6_K  two groups of 16 values (int8 scales sa, sb against d) per activation block, codes stored
+//         unsigned with an offset of 32:   dx * d * (sa * (sum_a(qu * xq) - 32 sum_a(xq)) + sb * (...))
+// One f32 rounding per activation block.  The scalar versions are the definitions.
+// (reference: src/tensor/quant_cpu/format/{q4_k,q6_k}.rs, int8 dots of the same shape)
+float dot_q4k_scalar(const BlockQ4_K* w, const BlockQ8_0* x, int nsb) {
+  float acc = 0.f;
+  for (int i = 0; i < nsb; ++i) {
+    const float d = f16_to_f32(w[i].d), dmin = f16_to_f32(w[i].dmin);
+    const uint8_t* q = w[i].qs;
+    for (int j = 0; j < 4; ++j, q += 32) {
+      const BlockQ8_0& xa = x[i * 8 + 2 * j];
+      const BlockQ8_0& xb = x[i * 8 + 2 * j + 1];
+      uint8_t sa, ma, sb, mb;
+      get_scale_min_k4(2 * j, w[i].scales, &sa, &ma);
+      get_scale_min_k4(2 * j + 1, w[i].scales, &sb, &mb);
+      int32_t ia = 0, ib = 0, xsa = 0, xsb = 0;
+      for (int l = 0; l < 32; ++l) {
+        ia += (int32_t)(q[l] & 0xF) * xa.qs[l];
+        ib += (int32_t)(q[l] >> 4) * xb.qs[l];
+        xsa += xa.qs[l];
+        xsb += xb.qs[l];
+      }
+      acc += f16_to_f32(xa.d) * (d * (float)sa * (float)ia - dmin * (float)ma * (float)xsa);
+      acc += f16_to_f32(xb.d) * (d * (float)sb * (float)ib - dmin * (float)mb * (float)xsb);
+    }
+  }
+  return acc;
+}
+
+float dot_q6k_scalar(const BlockQ6_K* w, const BlockQ8_0* x, int nsb) {
+  float acc = 0.f;
+  for (int i = 0; i < nsb; ++i) {
+    const float d = f16_to_f32(w[i].d);
+    for (int half = 0; half < 2; ++half) {
+      const uint8_t* ql = w[i].ql + 64 * half;
+      const uint8_t* qh = w[i].qh + 32 * half;
+      const int8_t* sc = w[i].scales + 8 * half;
+      for (int part = 0; part < 4; ++part) {            // 32 values each: one activation block
+        const BlockQ8_0& xb = x[i * 8 + half * 4 + part];
+        int32_t sum[2] = {0, 0};
+        for (int l = 0; l < 32; ++l) {
+          const int lo = (part & 1) ? ql[l + 32] : ql[l];
+          const int nib = (part & 2) ? (lo >> 4) : (lo & 0xF);
+          const int q = (nib | (((qh[l] >> (2 * part)) & 3) << 4)) - 32;
+          sum[l / 16] += q * xb.qs[l];
+        }
+        acc += f16_to_f32(xb.d) * d * ((float)sc[2 * part] * (float)sum[0] + (float)sc[2 * part + 1] * (float)sum[1]);
+      }
+    }
+  }
+  return acc;
+}
+
+#if defined(__x86_64__)
+__attribute__((target("avx2"))) static inline int32_t hsum_i32(__m256i v) {
+  __m128i s = _mm_add_epi32(_mm256_castsi256_si128(v), _mm256_extracti128_si256(v, 1));
+  s = _mm_add_epi32(s, _mm_shuffle_epi32(s, 0x4E));
+  s = _mm_add_epi32(s, _mm_shuffle_epi32(s, 0xB1));
+  return _mm_cvtsi128_si32(s);
+}
+
+// u8 codes times s8 activations, summed to eight i32 lanes (lanes 0-3: values 0-15, lanes 4-7: values 16-31)
+__attribute__((target("avx2"))) static inline __m256i mul_sum_i32(__m256i qu, __m256i xs) {
+  return _mm256_madd_epi16(_mm256_maddubs_epi16(qu, xs), _mm256_set1_epi16(1));
+}
+
+// The AVX2 versions keep eight f32 partial sums (one per i32 lane of the products) and add them up once per
+// row, instead of reducing every sub-block to a scalar.
+__attribute__((target("avx2,fma,f16c"))) static inline float hsum_f32(__m256 v) {
+  __m128 s = _mm_add_ps(_mm256_castps256_ps128(v), _mm256_extractf128_ps(v, 1));
+  s = _mm_add_ps(s, _mm_movehl_ps(s, s));
+  s = _mm_add_ss(s, _mm_shuffle_ps(s, s, 1));
+  return _mm_cvtss_f32(s);
+}
+
+__attribute__((target("avx2,fma,f16c"))) float dot_q4k_avx2(const BlockQ4_K* w, const BlockQ8_0* x, int nsb) {
+  const __m256i m4 = _mm256_set1_epi8(0xF), one = _mm256_set1_epi8(1);
+  __m256 acc = _mm256_setzero_ps();
+  for (int i = 0; i < nsb; ++i) {
+    const float d = f16_to_f32(w[i].d), dmin = f16_to_f32(w[i].dmin);
+    const uint8_t* q = w[i].qs;
+    for (int j = 0; j < 4; ++j, q += 32) {
+      const BlockQ8_0& xa = x[i * 8 + 2 * j];
+      const BlockQ8_0& xb = x[i * 8 + 2 * j + 1];
+      uint8_t sa, ma, sb, mb;
+      get_scale_min_k4(2 * j, w[i].scales, &sa, &ma);
+      get_scale_min_k4(2 * j + 1, w[i].scales, &sb, &mb);
+      const float dxa = f16_to_f32(xa.d), dxb = f16_to_f32(xb.d);
+      const __m256i qq = _mm256_loadu_si256((const __m256i*)q);
+      const __m256i va = _mm256_loadu_si256((const __m256i*)xa.qs), vb = _mm256_loadu_si256((const __m256i*)xb.qs);
+      const __m256 pa = _mm256_cvtepi32_ps(mul_sum_i32(_mm256_and_si256(qq, m4), va));
+      const __m256 pb = _mm256_cvtepi32_ps(mul_sum_i32(_mm256_and_si256(_mm256_srli_epi16(qq, 4), m4), vb));
+      const __m256 xsa = _mm256_cvtepi32_ps(mul_sum_i32(one, va)), xsb = _mm256_cvtepi32_ps(mul_sum_i32(one, vb));
+      acc = _mm256_fmadd_ps(pa, _mm256_set1_ps(dxa * d * (float)sa), acc);
+      acc = _mm256_fnmadd_ps(xsa, _mm256_set1_ps(dxa * dmin * (float)ma), acc);
+      acc = _mm256_fmadd_ps(pb, _mm256_set1_ps(dxb * d * (float)sb), acc);
+      acc = _mm256_fnmadd_ps(xsb, _mm256_set1_ps(dxb * dmin * (float)mb), acc);
+    }
+  }
+  return hsum_f32(acc);
+}
+
+__attribute__((target("avx2,fma,f16c"))) float dot_q6k_avx2(const BlockQ6_K* w, const BlockQ8_0* x, int nsb) {
+  const __m256i m4 = _mm256_set1_epi8(0xF), m2 = _mm256_set1_epi8(3), one = _mm256_set1_epi8(1);
+  __m256 acc = _mm256_setzero_ps();
+  for (int i = 0; i < nsb; ++i) {
+    const float d = f16_to_f32(w[i].d);
+    for (int half = 0; half < 2; ++half) {
+      const __m256i l0 = _mm256_loadu_si256((const __m256i*)(w[i].ql + 64 * half));
+      const __m256i l1 = _mm256_loadu_si256((const __m256i*)(w[i].ql + 64 * half + 32));
+      const __m256i h = _mm256_loadu_si256((const __m256i*)(w[i].qh + 32 * half));
+      const int8_t* sc = w[i].scales + 8 * half;
+      // the four 32-value parts of this half: low nibbles of ql[0..31], of ql[32..63], then the high nibbles
+      const __m256i nib[4] = {_mm256_and_si256(l0, m4), _mm256_and_si256(l1, m4),
+                              _mm256_and_si256(_mm256_srli_epi16(l0, 4), m4), _mm256_and_si256(_mm256_srli_epi16(l1, 4), m4)};
+      const __m256i top[4] = {_mm256_and_si256(h, m2), _mm256_and_si256(_mm256_srli_epi16(h, 2), m2),
+                              _mm256_and_si256(_mm256_srli_epi16(h, 4), m2), _mm256_and_si256(_mm256_srli_epi16(h, 6), m2)};
+      for (int part = 0; part < 4; ++part) {
+        const BlockQ8_0& xb = x[i * 8 + half * 4 + part];
+        const __m256i xv = _mm256_loadu_si256((const __m256i*)xb.qs);
+        const __m256i qu = _mm256_or_si256(nib[part], _mm256_slli_epi16(top[part], 4));     // 0 .. 63
+        // sum(qu * x) - 32 sum(x) per group of 16, then the group's scale
+        const __m256i sums = _mm256_sub_epi32(mul_sum_i32(qu, xv), _mm256_slli_epi32(mul_sum_i32(one, xv), 5));
+        const float dd = f16_to_f32(xb.d) * d;
+        const float sa = dd * (float)sc[2 * part], sb = dd * (float)sc[2 * part + 1];
+        acc = _mm256_fmadd_ps(_mm256_cvtepi32_ps(sums), _mm256_set_ps(sb, sb, sb, sb, sa, sa, sa, sa), acc);
+      }
+    }
+  }
+  return hsum_f32(acc);
+}
+#endif
+
+typedef float (*DotQ4kFn)(const BlockQ4_K*, const BlockQ8_0*, int);
+typedef float (*DotQ6kFn)(const BlockQ6_K*, const BlockQ8_0*, int);
+DotQ4kFn pick_dot_q4k(int level) {
+#if defined(__x86_64__)
+  if (level >= 2) return dot_q4k_avx2;
+#endif
+  (void)level;
+  return dot_q4k_scalar;
+}
+DotQ6kFn pick_dot_q6k(int level) {
+#if defined(__x86_64__)
+  if (level >= 2) return dot_q6k_avx2;
+#endif
+  (void)level;
+  return dot_q6k_scalar;
 }
 
 float dot_f32(const float* a, const float* b, int n) {
@@ -284,6 +440,25 @@ void gemv(Model& m, const Tensor& w, int N, int K, const BlockQ8_0* xq, const fl
       const int r1 = (c + 1) * chunk < N ? (c + 1) * chunk : N;
       for (int r = c * chunk; r < r1; ++r) out[r] = dot(W + (size_t)r * nb, xq, nb);
     });
+    return;
+  }
+  if ((w.type == T_Q4_K || w.type == T_Q6_K) && K % 256 == 0 && xq) {
+    const int nsb = K / 256;
+    if (w.type == T_Q4_K) {
+      const BlockQ4_K* W = (const BlockQ4_K*)w.data;
+      DotQ4kFn dot = pick_dot_q4k(m.level);
+      m.pool->run(chunks, [&](int c) {
+        const int r1 = (c + 1) * chunk < N ? (c + 1) * chunk : N;
+        for (int r = c * chunk; r < r1; ++r) out[r] = dot(W + (size_t)r * nsb, xq, nsb);
+      });
+    } else {
+      const BlockQ6_K* W = (const BlockQ6_K*)w.data;
+      DotQ6kFn dot = pick_dot_q6k(m.level);
+      m.pool->run(chunks, [&](int c) {
+        const int r1 = (c + 1) * chunk < N ? (c + 1) * chunk : N;
+        for (int r = c * chunk; r < r1; ++r) out[r] = dot(W + (size_t)r * nsb, xq, nsb);
+      });
+    }
     return;
   }
   m.pool->run(chunks, [&](int c) {
@@ -516,6 +691,24 @@ LKH_API float lkcpu_dot_q8_0(const void* x, const void* y, int nblocks, int leve
   int have = lkc_cpu_level();
   if (level > have) level = have;
   return pick_dot(level)((const BlockQ8_0*)x, (const BlockQ8_0*)y, nblocks);
+}
+
+// The same for any stored row type (`type`: the file's type code; Q8_0, Q4_K and Q6_K take integer dots with
+// the Q8_0-quantised activation, the rest a row dequantiser and an f32 dot).
+LKH_API int lkcpu_gemv_any(int type, const void* w, const float* x, float* out, int N, int K, int threads, int level) {
+  if (K % 32) return -1;
+  Model m;
+  int have = lkc_cpu_level();
+  m.level = level > have ? have : level;
+  m.dot = pick_dot(m.level);
+  Pool pool(threads);
+  m.pool = &pool;
+  std::vector<BlockQ8_0> xq(K / 32);
+  quant_q8_0(x, xq.data(), K);
+  Tensor t{w, type};
+  gemv(m, t, N, K, xq.data(), x, out);
+  m.pool = nullptr;
+  return 0;
 }
 
 LKH_API int lkcpu_gemv_q8_0(const void* w, const float* x, float* out, int N, int K, int threads, int level) {

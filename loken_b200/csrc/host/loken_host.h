@@ -64,6 +64,7 @@ LKH_API int lkcpu_level(void* h);
 LKH_API int lkcpu_threads(void* h);
 LKH_API float lkcpu_dot_q8_0(const void* x, const void* y, int nblocks, int level);
 LKH_API int lkcpu_gemv_q8_0(const void* w, const float* x, float* out, int N, int K, int threads, int level);
+LKH_API int lkcpu_gemv_any(int type, const void* w, const float* x, float* out, int N, int K, int threads, int level);
 
 // ---- wire codec (wire.cpp) ----
 LKH_API long long lkwire_header_bytes(int rank);

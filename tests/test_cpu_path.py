@@ -44,6 +44,33 @@ def test_pooled_gemv_matches_float(threads):
     assert np.abs(out - ref).max() < 0.02 * np.abs(ref).max()
 
 
+@pytest.mark.parametrize("ty", [G.Q4_K, G.Q6_K])
+def test_k_quant_rows_take_integer_dots(ty):
+    """Q4_K and Q6_K rows against the Q8_0-quantised activation: the scalar definition equals the float product
+    of the decoded weights with the decoded activation, and the AVX2 version equals the scalar one."""
+    rng = np.random.default_rng(2)
+    L = _lib()
+    have = L.lkc_cpu_level()
+    N, K = 67, 1024
+    w = rng.standard_normal((N, K)).astype(np.float32) * 0.1
+    x = (rng.standard_normal(K) * 2).astype(np.float32)
+    wq = G.quantize(w, ty)
+    xq = G.dequantize(G.quantize(x, G.Q8_0), G.Q8_0, (K,))               # what the integer dot multiplies by
+    ref = G.dequantize(wq, ty, (N, K)).astype(np.float64) @ xq.astype(np.float64)
+    outs = {}
+    for level in (0, 2):
+        if level > have:
+            continue
+        out = np.zeros(N, dtype=np.float32)
+        rc = L.lkcpu_gemv_any(int(ty), wq.ctypes.data_as(C.c_void_p), x.ctypes.data_as(C.c_void_p),
+                              out.ctypes.data_as(C.c_void_p), N, K, 3, level)
+        assert rc == 0
+        outs[level] = out
+        assert np.abs(out - ref).max() < 1e-4 * max(1.0, np.abs(ref).max()), (level, np.abs(out - ref).max())
+    if 2 in outs:
+        assert np.abs(outs[2] - outs[0]).max() <= 2e-5 * max(1.0, np.abs(ref).max())
+
+
 @pytest.mark.parametrize("arch,fmt", [("qwen3", "q8_0"), ("llama", "q8_0"), ("llama", "q4_k_m")])
 def test_cpu_model_matches_oracle(tmp_path, arch, fmt):
     from loken_b200.models import loader
