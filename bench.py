@@ -57,6 +57,9 @@ def parse():
                     help="config 4: keep only SLOTS experts per layer on the GPU, the rest in pinned host memory")
     ap.add_argument("--draft-k", type=int, default=0,
                     help="config 5: fixed draft length (0 = learned from the acceptance seen, as the server runs it)")
+    ap.add_argument("--shape", default="", help="config 2: another model preset in place of llama-3.1-8b (e.g. qwen2.5-32b)")
+    ap.add_argument("--weight-format", default="", help="config 2: weight format of the model (default q4_k_m)")
+    ap.add_argument("--fixed-prompt", type=int, default=0, help="config 2: every prompt this many tokens (0 = 128-2048 at random)")
     ap.add_argument("--requests", type=int, default=0, help="configs 2/4/5: number of concurrent requests (0 = the set's)")
     ap.add_argument("--out-tokens", type=int, default=0, help="configs 1/2/4/5: tokens generated per request (0 = the set's)")
     return ap.parse_args()
@@ -187,11 +190,15 @@ def extra_config(args):
     sp = SamplingParams(temperature=0.7, top_k=0, top_p=0.9, ignore_eos=True, seed=1234)
     prefix_len, spec, moe_factory, par = 0, None, None, f"tp{world}"
     if args.config == 2:
-        cfg = dataclasses.replace(get_config("llama-3.1-8b"), weight_format="q4_k_m")
+        cfg = dataclasses.replace(get_config(args.shape or "llama-3.1-8b"), weight_format=args.weight_format or "q4_k_m")
         n_req = args.requests or 64
         lens = torch.randint(128, 2049, (n_req,), generator=g).tolist()
+        if args.fixed_prompt:
+            lens = [args.fixed_prompt] * n_req
         n_out, top_k = args.out_tokens or 256, 0
-        dtype = "Q4_K_M weights (Q4_K + Q6_K blocks, dequant-fused tcgen05 GEMM), bf16 activations, q8 paged KV"
+        dtype = "Q4_K_M weights (Q4_K + Q6_K blocks: dp4a GEMV up to 8 rows, dequant-fused tcgen05 GEMM to 128, decoded once " \
+                "per call beyond), bf16 activations, q8 paged KV" if cfg.weight_format == "q4_k_m" else \
+            f"{cfg.weight_format} weights, bf16 activations, q8 paged KV"
     elif args.config == 4:
         cfg = get_config("gpt-oss-120b")
         n_req = args.requests or 128

@@ -317,6 +317,12 @@ int launch_g(const DecodeParams& p, int G, dim3 grid, cudaStream_t st) {
     case 2: attn_decode_kernel<HD, 2, Q8><<<grid, 128, 0, st>>>(p); break;
     case 4: attn_decode_kernel<HD, 4, Q8><<<grid, 128, 0, st>>>(p); break;
     case 8: attn_decode_kernel<HD, 8, Q8><<<grid, 128, 0, st>>>(p); break;
+    // groups that are not a power of two (Llama-3.2-3B: 3, Qwen2.5-14B / 32B: 5, Qwen2.5-7B: 7) run here;
+    // the tensor-core decode kernels are built for 1, 2, 4 and 8
+    case 3: attn_decode_kernel<HD, 3, Q8><<<grid, 128, 0, st>>>(p); break;
+    case 5: attn_decode_kernel<HD, 5, Q8><<<grid, 128, 0, st>>>(p); break;
+    case 6: attn_decode_kernel<HD, 6, Q8><<<grid, 128, 0, st>>>(p); break;
+    case 7: attn_decode_kernel<HD, 7, Q8><<<grid, 128, 0, st>>>(p); break;
     default: return LKH_BAD_ARG;
   }
   lkh::count_launch();

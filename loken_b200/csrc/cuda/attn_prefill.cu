@@ -37,6 +37,7 @@ struct PrefillParams {
   const int* kv_len;
   int* status;
   int n_q, n_kv, window;
+  int g_real;          // query heads per kv head in the model; the tile holds G >= g_real head slots (a power of two)
   float scale_log2;
 };
 
@@ -117,7 +118,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_expect_tx(q_full, S::Q_BYTES);
 #pragma unroll
       for (int a = 0; a < NQA; ++a)
-        tma_load_3d(smem + S::Q_OFF + a * 16384, &tmQ, q_full, a * 64, kvh * G, qrow0);
+        // G head slots from the group's first head on: slots past g_real hold the next group's heads (zeros
+        // past the last head) and are never stored
+        tma_load_3d(smem + S::Q_OFF + a * 16384, &tmQ, q_full, a * 64, kvh * p.g_real, qrow0);
       for (int it = 0; it < ntiles; ++it) {
         const int st = it & 1;
         const uint32_t ph = (it >> 1) & 1;
@@ -174,10 +177,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int r = threadIdx.x;              // score row = TMEM lane
     const int tq = r / G, g = r % G;
     const int qi = tq0 + tq;
-    const bool row_ok = qi < qlen;
+    const bool row_ok = qi < qlen && g < p.g_real;
     const int pos = pos0 + qi;
     const int lo = (p.window > 0) ? max(0, pos - p.window + 1) : 0;
-    const int head = kvh * G + g;
+    const int head = kvh * p.g_real + g;
     const uint32_t tw = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
     uint8_t* psm = smem + S::P_OFF;
 
@@ -345,8 +348,13 @@ LK_API int lk_attn_prefill(const LkPrefillArgs* args, void* stream) {
   const LkPrefillArgs& a = *args;
   if (a.n_tiles <= 0) return LKH_OK;
   if (a.n_kv <= 0 || a.n_q % a.n_kv || (a.total_kv_pad % 128)) return LKH_BAD_ARG;
-  const int G = a.n_q / a.n_kv;
+  // group sizes that are not a power of two (3, 5, 6, 7: Llama-3.2-3B, Qwen2.5-14B / 32B) run in the next
+  // larger tile shape with the spare head slots idle
+  const int g_real = a.n_q / a.n_kv;
+  const int G = g_real <= 1 ? 1 : g_real <= 2 ? 2 : g_real <= 4 ? 4 : 8;
+  if (g_real > 8) return LKH_BAD_ARG;
   PrefillParams p;
+  p.g_real = g_real;
   p.out = (__nv_bfloat16*)a.out;
   p.sinks = a.sinks;
   p.tile_seq = a.tile_seq; p.tile_q0 = a.tile_q0;

@@ -219,6 +219,13 @@ PRESETS: Dict[str, ModelConfig] = {
     "llama-3.1-8b": ModelConfig(name="llama-3.1-8b", arch="llama", n_layers=32, hidden=4096, n_q=32, n_kv=8,
                                 head_dim=128, intermediate=14336, vocab=128256, rope_theta=5e5, rope_pairing=0,
                                 rope_scaling=_LLAMA3_SCALING, weight_format="q4_k_m", context_length=131072),
+    # shapes of models the reference publishes numbers for (deepseek-r1:32b is a Qwen2.5-32B; qwen3:8b)
+    "qwen2.5-32b": ModelConfig(name="qwen2.5-32b", arch="qwen2", n_layers=64, hidden=5120, n_q=40, n_kv=8, head_dim=128,
+                               intermediate=27648, vocab=152064, rope_theta=1e6, rope_pairing=1, attn_bias=True,
+                               rms_eps=1e-5, weight_format="q4_k_m", context_length=131072),
+    "qwen3-8b": ModelConfig(name="qwen3-8b", arch="qwen3", n_layers=36, hidden=4096, n_q=32, n_kv=8, head_dim=128,
+                            intermediate=12288, vocab=151936, rope_theta=1e6, rope_pairing=1, qk_norm=True,
+                            rms_eps=1e-6, weight_format="q4_k_m", context_length=40960),
     # BASELINE config 5 (draft)
     "llama-3.2-1b": ModelConfig(name="llama-3.2-1b", arch="llama", n_layers=16, hidden=2048, n_q=32, n_kv=8,
                                 head_dim=64, intermediate=8192, vocab=128256, rope_theta=5e5, rope_pairing=0,

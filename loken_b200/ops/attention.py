@@ -61,7 +61,7 @@ def decode(q: torch.Tensor, cache: KVCacheLayer, block_table: torch.Tensor, seq_
     fast = hd == 128 and cache.q8 and block_size == 16
     if fast and DECODE_KERNEL == "tc" and n_q // cache.n_kv in (1, 2, 4, 8):
         check(cuda_lib().lk_attn_decode_tc(C.byref(a), stream()), "lk_attn_decode_tc")
-    elif fast and DECODE_KERNEL in ("tc", "tma"):
+    elif fast and DECODE_KERNEL in ("tc", "tma") and n_q // cache.n_kv in (1, 2, 4, 8):
         check(cuda_lib().lk_attn_decode_tma(C.byref(a), stream()), "lk_attn_decode_tma")
     else:
         check(cuda_lib().lk_attn_decode(C.byref(a), stream()), "lk_attn_decode")
@@ -93,6 +93,7 @@ def plan_prefill(q_lens: Sequence[int], kv_lens: Sequence[int], group: int, devi
                  seq_rows: Optional[Sequence[int]] = None) -> PrefillPlan:
     """q_lens[s] new tokens per sequence, kv_lens[s] total keys (cached prefix + new).
     `group` = query heads per kv head (fixes how many tokens a 128-row tile holds)."""
+    group = 1 if group <= 1 else 2 if group <= 2 else 4 if group <= 4 else 8      # the kernel's tile shapes (head slots)
     tq = 128 // group
     tile_seq, tile_q0, q_start, kv_off, g_seq, g_tok0 = [], [], [], [], [], []
     qs = kv = 0

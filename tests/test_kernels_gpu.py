@@ -235,7 +235,10 @@ def _fill_cache(cache, k, v, slots):
 
 @pytest.mark.parametrize("hd,n_q,n_kv,q8,window,sinks,nsplit", [
     (128, 8, 1, True, 0, False, 1), (128, 8, 2, True, 0, False, 4), (128, 4, 4, False, 0, False, 2),
-    (64, 8, 1, True, 128, True, 3), (64, 16, 2, True, 0, True, 1), (128, 16, 4, True, 100, False, 2)])
+    (64, 8, 1, True, 128, True, 3), (64, 16, 2, True, 0, True, 1), (128, 16, 4, True, 100, False, 2),
+    # groups of 3, 5, 6 and 7 heads (the paged q8 cache with 16-token blocks included: those take this kernel)
+    (128, 6, 2, True, 0, False, 2), (128, 10, 2, True, 0, True, 3), (64, 12, 2, False, 50, False, 1),
+    (128, 14, 2, True, 0, False, 1)])
 def test_attn_decode(hd, n_q, n_kv, q8, window, sinks, nsplit):
     from loken_b200.ops import attention, rows
 
@@ -291,7 +294,9 @@ def test_attn_decode_fp8_out():
 
 @pytest.mark.parametrize("hd,n_q,n_kv,window,sinks", [(128, 8, 1, 0, False), (128, 8, 2, 0, False),
                                                        (128, 4, 4, 0, False), (64, 8, 1, 128, True),
-                                                       (64, 16, 4, 0, True), (128, 16, 2, 200, False)])
+                                                       (64, 16, 4, 0, True), (128, 16, 2, 200, False),
+                                                       # groups of 3, 5 and 6 heads run in the next larger tile shape
+                                                       (128, 6, 2, 0, False), (128, 10, 2, 100, True), (64, 12, 2, 0, False)])
 def test_attn_prefill(hd, n_q, n_kv, window, sinks):
     from loken_b200.ops import attention, rows
 
