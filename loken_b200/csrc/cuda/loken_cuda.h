@@ -89,6 +89,11 @@ int lk_rope_kv(const void* qkv, long long ld, const int* pos, const int* slots, 
                const float* q_norm_w, const float* k_norm_w, float eps, const float* inv_freq, int rope_dim,
                int pairing, float mscale, void* q_out, void* k_cache, void* v_cache, void* k_scale, void* v_scale,
                long long num_slots, int kv_q8, int* status, void* stream);
+// The same with the q / k norm taken over the token's whole projection (OLMoE); `rinv` is [T, 2] f32 scratch.
+int lk_rope_kv_wide(const void* qkv, long long ld, const int* pos, const int* slots, int T, int n_q, int n_kv, int hd,
+                    const float* q_norm_w, const float* k_norm_w, float eps, const float* inv_freq, int rope_dim,
+                    int pairing, float mscale, void* q_out, void* k_cache, void* v_cache, void* k_scale, void* v_scale,
+                    long long num_slots, int kv_q8, int* status, float* rinv, void* stream);
 // Context shift: cache positions move from `src` to `dst` slots (no overlap); key i is turned by delta[i]
 // positions on the way, values are copied.
 // What the activations of a GEMV are computed from, and a residual update it applies on the side.

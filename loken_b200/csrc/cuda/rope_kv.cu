@@ -22,6 +22,32 @@ using namespace lk;
 
 namespace {
 
+// 1 / rms of a token's whole query projection and of its whole key projection: out[t] = {q, k}.
+__global__ void __launch_bounds__(256)
+qk_rinv_kernel(const __nv_bfloat16* __restrict__ qkv, long long ld, int T, int q_cols, int k_cols, float eps,
+               float* __restrict__ out) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const __nv_bfloat16* row = qkv + (long long)t * ld;
+  float sq = 0.f, sk = 0.f;
+  for (int i = threadIdx.x; i < q_cols; i += 256) {
+    const float v = bf2f(row[i]);
+    sq += v * v;
+  }
+  for (int i = threadIdx.x; i < k_cols; i += 256) {
+    const float v = bf2f(row[q_cols + i]);
+    sk += v * v;
+  }
+  sq = block_sum(sq, red);
+  sk = block_sum(sk, red);
+  if (threadIdx.x == 0) {
+    out[(long long)t * 2] = rsqrtf(sq / (float)q_cols + eps);
+    out[(long long)t * 2 + 1] = rsqrtf(sk / (float)k_cols + eps);
+  }
+}
+
 template <int HD>
 __global__ void __launch_bounds__(128)
 rope_kv_kernel(const __nv_bfloat16* __restrict__ qkv, long long ld, const int* __restrict__ pos,
@@ -29,7 +55,7 @@ rope_kv_kernel(const __nv_bfloat16* __restrict__ qkv, long long ld, const int* _
                const float* __restrict__ k_norm_w, float eps, const float* __restrict__ inv_freq, int rope_dim,
                int pairing, float mscale, __nv_bfloat16* __restrict__ q_out, void* __restrict__ k_cache,
                void* __restrict__ v_cache, __half* __restrict__ k_scale, __half* __restrict__ v_scale,
-               long long num_slots, int kv_q8, int* __restrict__ status) {
+               long long num_slots, int kv_q8, int* __restrict__ status, const float* __restrict__ wide_rinv) {
   pdl_launch();      // nothing is written before the wait: the kernel after this one may set up behind it
   pdl_wait();
   constexpr int EPL = HD / 32;  // values per lane
@@ -50,11 +76,19 @@ rope_kv_kernel(const __nv_bfloat16* __restrict__ qkv, long long ld, const int* _
 
   const float* nw = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
   if (nw) {
-    float ss = 0.f;
+    float r;
+    if (wide_rinv) {
+      // the norm runs over all the query (key) heads of the token at once (OLMoE): its scale was computed by
+      // qk_rinv_kernel, the weight has one entry per column of the projection
+      r = wide_rinv[(long long)t * 2 + (is_q ? 0 : 1)];
+      nw += (long long)(is_q ? h : h - n_q) * HD;
+    } else {
+      float ss = 0.f;
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) ss += v[e] * v[e];
-    ss = warp_sum(ss);
-    const float r = rsqrtf(ss / (float)HD + eps);
+      for (int e = 0; e < EPL; ++e) ss += v[e] * v[e];
+      ss = warp_sum(ss);
+      r = rsqrtf(ss / (float)HD + eps);
+    }
 #pragma unroll
     for (int e = 0; e < EPL; ++e) v[e] = v[e] * r * nw[lane * EPL + e];
   }
@@ -321,10 +355,11 @@ LK_API int lk_kv_shift(void* k_cache, void* v_cache, void* k_scale, void* v_scal
   return lkh::launch_status();
 }
 
-LK_API int lk_rope_kv(const void* qkv, long long ld, const int* pos, const int* slots, int T, int n_q, int n_kv,
-                      int hd, const float* q_norm_w, const float* k_norm_w, float eps, const float* inv_freq,
-                      int rope_dim, int pairing, float mscale, void* q_out, void* k_cache, void* v_cache,
-                      void* k_scale, void* v_scale, long long num_slots, int kv_q8, int* status, void* stream) {
+static int rope_kv_impl(const void* qkv, long long ld, const int* pos, const int* slots, int T, int n_q, int n_kv,
+                        int hd, const float* q_norm_w, const float* k_norm_w, float eps, const float* inv_freq,
+                        int rope_dim, int pairing, float mscale, void* q_out, void* k_cache, void* v_cache,
+                        void* k_scale, void* v_scale, long long num_slots, int kv_q8, int* status, void* stream,
+                        const float* wide_rinv) {
   if (T <= 0) return LKH_OK;
   const long long units = (long long)T * (n_q + 2 * n_kv);
   const unsigned grid = (unsigned)((units + 3) / 4);
@@ -333,7 +368,7 @@ LK_API int lk_rope_kv(const void* qkv, long long ld, const int* pos, const int* 
   lkh::launch_pdl(rope_kv_kernel<HD>, dim3(grid), dim3(128), 0, st, (const __nv_bfloat16*)qkv, ld, pos, slots, T, \
                   n_q, n_kv, q_norm_w, k_norm_w, eps, inv_freq, rope_dim, pairing, mscale,                       \
                   (__nv_bfloat16*)q_out, k_cache, v_cache, (__half*)k_scale, (__half*)v_scale, num_slots,        \
-                  kv_q8, status)
+                  kv_q8, status, wide_rinv)
   if (hd == 128) LK_ROPE(128);
   else if (hd == 64) LK_ROPE(64);
   else if (hd == 256) LK_ROPE(256);
@@ -341,6 +376,30 @@ LK_API int lk_rope_kv(const void* qkv, long long ld, const int* pos, const int* 
 #undef LK_ROPE
   lkh::count_launch();
   return lkh::launch_status();
+}
+
+LK_API int lk_rope_kv(const void* qkv, long long ld, const int* pos, const int* slots, int T, int n_q, int n_kv,
+                      int hd, const float* q_norm_w, const float* k_norm_w, float eps, const float* inv_freq,
+                      int rope_dim, int pairing, float mscale, void* q_out, void* k_cache, void* v_cache,
+                      void* k_scale, void* v_scale, long long num_slots, int kv_q8, int* status, void* stream) {
+  return rope_kv_impl(qkv, ld, pos, slots, T, n_q, n_kv, hd, q_norm_w, k_norm_w, eps, inv_freq, rope_dim, pairing, mscale,
+                      q_out, k_cache, v_cache, k_scale, v_scale, num_slots, kv_q8, status, stream, nullptr);
+}
+
+// The same with the q / k norm taken over the token's whole projection (weights of n_q * hd and n_kv * hd entries):
+// `rinv` [T, 2] f32 scratch receives the two scales first.
+LK_API int lk_rope_kv_wide(const void* qkv, long long ld, const int* pos, const int* slots, int T, int n_q, int n_kv,
+                           int hd, const float* q_norm_w, const float* k_norm_w, float eps, const float* inv_freq,
+                           int rope_dim, int pairing, float mscale, void* q_out, void* k_cache, void* v_cache,
+                           void* k_scale, void* v_scale, long long num_slots, int kv_q8, int* status, float* rinv,
+                           void* stream) {
+  if (T <= 0) return LKH_OK;
+  if (!rinv || !q_norm_w || !k_norm_w) return LKH_BAD_ARG;
+  lkh::launch_pdl(qk_rinv_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)qkv, ld, T, n_q * hd,
+                  n_kv * hd, eps, rinv);
+  lkh::count_launch();
+  return rope_kv_impl(qkv, ld, pos, slots, T, n_q, n_kv, hd, q_norm_w, k_norm_w, eps, inv_freq, rope_dim, pairing, mscale,
+                      q_out, k_cache, v_cache, k_scale, v_scale, num_slots, kv_q8, status, stream, rinv);
 }
 
 LK_API int lk_kv_gather(const void* k_cache, const void* v_cache, const void* k_scale, const void* v_scale,

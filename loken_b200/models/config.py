@@ -24,7 +24,7 @@ ARCH_FACTS: Dict[str, dict] = {
                    attn_bias=True, sinks=True, router="softmax_topk", expert_bias=True),
     "gemma3": dict(rope_pairing=1, swa_period=6),
     "mixtral": dict(rope_pairing=0, router="softmax", renorm=True),
-    "olmoe": dict(rope_pairing=1, router="softmax", renorm=False),
+    "olmoe": dict(rope_pairing=1, router="softmax", renorm=False, qk_norm=True, qk_norm_wide=True),
     "phi3": dict(rope_pairing=1),
     "granite": dict(rope_pairing=0),
 }
@@ -60,6 +60,7 @@ class ModelConfig:
     rope_dim: Optional[int] = None
     rope_scaling: RopeScaling = field(default_factory=RopeScaling)
     rope_freq_factors: Optional[List[float]] = None   # `rope_freqs.weight` of Llama-3.1 GGUFs
+    qk_norm_wide: bool = False     # the q / k norm runs over all heads of a token at once (OLMoE), not per head
     rms_eps: float = 1e-5
     qk_norm: bool = False
     tie_embeddings: bool = False
@@ -198,7 +199,8 @@ class ModelConfig:
                   expert_bias=facts.get("expert_bias", False), glu_mode=facts.get("glu_mode", 0),
                   glu_alpha=facts.get("glu_alpha", 1.702), glu_limit=facts.get("glu_limit", 7.0),
                   embedding_scale=float(g("embedding_scale", 1.0) or 1.0),
-                  logit_scale=float(g("logit_scale", 1.0) or 1.0), attn_scale=g("attention.scale"))
+                  logit_scale=float(g("logit_scale", 1.0) or 1.0), attn_scale=g("attention.scale"),
+                  qk_norm_wide=facts.get("qk_norm_wide", False))
         if arch == "granite" and cfg.logit_scale not in (0.0, 1.0):
             cfg.logit_scale = 1.0 / cfg.logit_scale           # these files store the divisor of the logits
         pat = g("attention.sliding_window_pattern")
@@ -226,6 +228,10 @@ PRESETS: Dict[str, ModelConfig] = {
     "qwen3-8b": ModelConfig(name="qwen3-8b", arch="qwen3", n_layers=36, hidden=4096, n_q=32, n_kv=8, head_dim=128,
                             intermediate=12288, vocab=151936, rope_theta=1e6, rope_pairing=1, qk_norm=True,
                             rms_eps=1e-6, weight_format="q4_k_m", context_length=40960),
+    "olmoe-1b-7b": ModelConfig(name="olmoe-1b-7b", arch="olmoe", n_layers=16, hidden=2048, n_q=16, n_kv=16, head_dim=128,
+                               intermediate=1024, vocab=50304, rope_theta=10000.0, rope_pairing=1, qk_norm=True,
+                               qk_norm_wide=True, rms_eps=1e-5, n_experts=64, top_k=8, expert_intermediate=1024,
+                               router="softmax", renorm=False, weight_format="q4_k_m", context_length=4096),
     # BASELINE config 5 (draft)
     "llama-3.2-1b": ModelConfig(name="llama-3.2-1b", arch="llama", n_layers=16, hidden=2048, n_q=32, n_kv=8,
                                 head_dim=64, intermediate=8192, vocab=128256, rope_theta=5e5, rope_pairing=0,

@@ -332,8 +332,8 @@ def export_random_gguf(path: str, cfg: ModelConfig, *, seed: int = 0, std: float
             vec(p + "attn_v.bias", cfg.n_kv * hd, 0.0, std)
             vec(p + "attn_output.bias", H, 0.0, std)
         if cfg.qk_norm:
-            vec(p + "attn_q_norm.weight", hd)
-            vec(p + "attn_k_norm.weight", hd)
+            vec(p + "attn_q_norm.weight", cfg.n_q * hd if cfg.qk_norm_wide else hd)
+            vec(p + "attn_k_norm.weight", cfg.n_kv * hd if cfg.qk_norm_wide else hd)
         if cfg.sinks:
             vec(p + "attn_sinks.weight", cfg.n_q, 0.0, 1.0)
         vec(p + "ffn_norm.weight", H)

@@ -22,11 +22,13 @@ from .weights import LayerWeights, Linear, ModelWeights, make_linear
 
 HF_ARCH = {"LlamaForCausalLM": "llama", "MistralForCausalLM": "mistral", "Qwen2ForCausalLM": "qwen2",
            "Qwen3ForCausalLM": "qwen3", "GptOssForCausalLM": "gpt-oss", "MixtralForCausalLM": "mixtral",
-           "Qwen3MoeForCausalLM": "qwen3moe", "Phi3ForCausalLM": "phi3", "GraniteForCausalLM": "granite"}
+           "Qwen3MoeForCausalLM": "qwen3moe", "Phi3ForCausalLM": "phi3", "GraniteForCausalLM": "granite",
+           "OlmoeForCausalLM": "olmoe"}
 # mixture families that store one tensor per expert and matrix: (router, expert stem, gate, up, down)
 HF_EXPERT_NAMES = {
     "mixtral": ("block_sparse_moe.gate", "block_sparse_moe.experts.{e}.", "w1", "w3", "w2"),
     "qwen3moe": ("mlp.gate", "mlp.experts.{e}.", "gate_proj", "up_proj", "down_proj"),
+    "olmoe": ("mlp.gate", "mlp.experts.{e}.", "gate_proj", "up_proj", "down_proj"),
 }
 
 
@@ -112,7 +114,8 @@ def config_from_hf(cfg: dict, name: str = "hf") -> ModelConfig:
         moe = dict(extra, n_experts=n_exp, top_k=int(cfg.get("num_experts_per_tok", 2)),
                    expert_intermediate=int(cfg.get("moe_intermediate_size") or cfg["intermediate_size"]),
                    router=facts.get("router", "softmax"),
-                   renorm=bool(cfg.get("norm_topk_prob", True)) if arch == "qwen3moe" else facts.get("renorm", True))
+                   renorm=bool(cfg.get("norm_topk_prob", arch == "qwen3moe")) if arch in ("qwen3moe", "olmoe")
+                   else facts.get("renorm", True), qk_norm_wide=facts.get("qk_norm_wide", False))
         if any(int(x) for x in (cfg.get("mlp_only_layers") or [])) or int(cfg.get("decoder_sparse_step", 1) or 1) != 1:
             raise ValueError("checkpoints that mix dense and mixture layers are not read")
     # HF checkpoints store q/k in the half-split (NeoX) layout whatever the family

@@ -113,7 +113,11 @@ def forward_ref(w: ModelWeights, tokens: Sequence[int], *, bf16_stream: bool = T
             qkv = qkv + lw.wqkv.bias
         qkv = rd(qkv).view(T, nq + 2 * nkv, hd)
         q, k, v = qkv[:, :nq], qkv[:, nq:nq + nkv], qkv[:, nq + nkv:]
-        if lw.q_norm is not None:
+        if lw.q_norm is not None and cfg.qk_norm_wide:
+            # over the token's whole projection (OLMoE), one weight per column
+            q = _rms(q.reshape(T, nq * hd), lw.q_norm, cfg.rms_eps).view(T, nq, hd)
+            k = _rms(k.reshape(T, nkv * hd), lw.k_norm, cfg.rms_eps).view(T, nkv, hd)
+        elif lw.q_norm is not None:
             q = _rms(q, lw.q_norm, cfg.rms_eps)
             k = _rms(k, lw.k_norm, cfg.rms_eps)
         q = rd(_rope(q, pos, w.inv_freq, cfg.rope_pairing, rope_dim, w.rope_mscale))

@@ -69,6 +69,7 @@ class Buffers:
         self.h = torch.zeros(cap, H, **bf)
         self.delta = torch.zeros(cap, H, **bf)
         self.delta2 = torch.zeros(min(cap, 8), H, **bf)      # second update buffer of the fused decode layers
+        self.qk_rinv = torch.zeros(cap, 2, dtype=torch.float32, device=device) if cfg.qk_norm_wide else None
         self.qkv = torch.zeros(cap, (nq + 2 * nkv) * hd, **bf)
         self.q = torch.zeros(cap, nq, hd, **bf)
         self.attn = torch.zeros(cap, nq * hd, **bf)
@@ -93,6 +94,8 @@ class DecoderModel:
         self.block_size = block_size
         self.comm = comm
         self.device = weights.embed.device
+        if self.cfg.qk_norm_wide and weights.tp_size > 1:
+            raise NotImplementedError("a q / k norm over all heads of a token needs every head on one rank")
         self.buf = Buffers(self.cfg, weights, max_tokens, self.device)
         self.moe_runner = moe_runner
         self._kg = None    # gathered K / V^T scratch for prefill, grown on demand
@@ -140,7 +143,8 @@ class DecoderModel:
         cache = self.kv[il]
         rows.rope_kv(b.qkv, inp.positions, inp.slots, cache, w.n_q_local, w.inv_freq,
                      rope_dim=cfg.rope_dim or cfg.head_dim, pairing=cfg.rope_pairing, mscale=w.rope_mscale,
-                     q_norm_w=lw.q_norm, k_norm_w=lw.k_norm, eps=cfg.rms_eps, q_out=b.q, rows=T)
+                     q_norm_w=lw.q_norm, k_norm_w=lw.k_norm, eps=cfg.rms_eps, q_out=b.q, rows=T,
+                     wide_rinv=b.qk_rinv if (cfg.qk_norm_wide and lw.q_norm is not None) else None)
         scale = cfg.softmax_scale()
         if inp.mode == "decode":
             use8 = want_fp8 and cfg.head_dim == 128 and b.attn8 is not None

@@ -191,8 +191,9 @@ def random_weights(cfg: ModelConfig, device, seed: int = 0, tp_rank: int = 0, tp
             window=cfg.layer_window(il))
         del wq, wk, wv, wqkv, wo
         if cfg.qk_norm:
-            lw.q_norm = torch.ones(hd, device=device) + _randn(gen, (hd,), 0.02, device)
-            lw.k_norm = torch.ones(hd, device=device) + _randn(gen, (hd,), 0.02, device)
+            wq_, wk_ = (cfg.n_q * hd, cfg.n_kv * hd) if cfg.qk_norm_wide else (hd, hd)
+            lw.q_norm = torch.ones(wq_, device=device) + _randn(gen, (wq_,), 0.02, device)
+            lw.k_norm = torch.ones(wk_, device=device) + _randn(gen, (wk_,), 0.02, device)
         if cfg.sinks:
             lw.sinks = _randn(gen, (cfg.n_q,), 1.0, device)[tp_rank * nql:(tp_rank + 1) * nql].contiguous()
         if cfg.is_moe:

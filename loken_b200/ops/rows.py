@@ -113,13 +113,24 @@ def kv_shift(cache: KVCacheLayer, src: torch.Tensor, dst: torch.Tensor, delta: t
 def rope_kv(qkv: torch.Tensor, pos: torch.Tensor, slots: torch.Tensor, cache: KVCacheLayer, n_q: int,
             inv_freq: torch.Tensor, *, rope_dim: Optional[int] = None, pairing: int = 1, mscale: float = 1.0,
             q_norm_w: Optional[torch.Tensor] = None, k_norm_w: Optional[torch.Tensor] = None, eps: float = 1e-6,
-            q_out: Optional[torch.Tensor] = None, rows: Optional[int] = None):
-    """qkv [T, (n_q + 2 n_kv) * hd] bf16 -> rotated q [T, n_q, hd]; K and V rows stored at `slots`."""
+            q_out: Optional[torch.Tensor] = None, rows: Optional[int] = None, wide_rinv: Optional[torch.Tensor] = None):
+    """qkv [T, (n_q + 2 n_kv) * hd] bf16 -> rotated q [T, n_q, hd]; K and V rows stored at `slots`.  With
+    `wide_rinv` ([T, 2] f32 scratch) the q / k norm runs over the token's whole projection (weights of
+    n_q * hd and n_kv * hd entries) instead of per head."""
     T = rows if rows is not None else qkv.shape[0]
     hd, n_kv = cache.hd, cache.n_kv
     if q_out is None:
         q_out = torch.empty(qkv.shape[0], n_q, hd, dtype=torch.bfloat16, device=qkv.device)
     wsp = Workspace.get(qkv.device)
+    if wide_rinv is not None:
+        assert q_norm_w.numel() == n_q * hd and k_norm_w.numel() == n_kv * hd and wide_rinv.shape[0] >= T
+        check(cuda_lib().lk_rope_kv_wide(ptr(qkv), C.c_longlong(qkv.stride(0)), ptr(pos), ptr(slots), T, n_q, n_kv, hd,
+                                         ptr(q_norm_w), ptr(k_norm_w), _f(eps), ptr(inv_freq),
+                                         rope_dim if rope_dim is not None else hd, pairing, _f(mscale), ptr(q_out),
+                                         ptr(cache.k), ptr(cache.v), ptr(cache.k_scale), ptr(cache.v_scale),
+                                         C.c_longlong(cache.num_slots), int(cache.q8), ptr(wsp.status), ptr(wide_rinv),
+                                         stream()), "lk_rope_kv_wide")
+        return q_out
     check(cuda_lib().lk_rope_kv(ptr(qkv), C.c_longlong(qkv.stride(0)), ptr(pos), ptr(slots), T, n_q, n_kv, hd,
                                 ptr(q_norm_w), ptr(k_norm_w), _f(eps), ptr(inv_freq),
                                 rope_dim if rope_dim is not None else hd, pairing, _f(mscale), ptr(q_out),

@@ -27,6 +27,11 @@ def _mk(arch, fmt, **kw):
     ("gpt-oss", "mxfp4", {}),
     ("llama", "q8_0", {}),
     ("llama", "q4_k_m", {}),
+    # the q / k norm over all heads of a token, routing weights not renormalised
+    ("olmoe", "bf16", dict(n_experts=8, top_k=2, expert_intermediate=128, n_q=4, n_kv=4, head_dim=64)),
+    ("olmoe", "bf16", dict(n_experts=8, top_k=2, expert_intermediate=128, n_q=2, n_kv=2, head_dim=128)),
+    # five query heads per kv head: prefill in the eight-slot tile shape, decode on the SIMT kernel
+    ("qwen2", "bf16", dict(n_q=10, n_kv=2, head_dim=128, hidden=256)),
 ])
 def test_prefill_logits_match_oracle(arch, fmt, kw):
     from loken_b200.models.reference import forward_ref
@@ -40,7 +45,10 @@ def test_prefill_logits_match_oracle(arch, fmt, kw):
     ref = forward_ref(w, prompt)
     eng.add_request(prompt, GREEDY)
     eng.step()
-    got = eng.runner.model.buf.logits[0]
+    got = eng.runner.model.buf.logits[0].clone()
+    for _ in range(3):
+        eng.step()                                   # decode steps on the same path
+    assert eng.runner.wsp.read_status() == 0
     # e4m3 activations carry ~3% rounding per element into every product of the fp8 model, and into the
     # expert products of an MXFP4 model (block-scaled MMA: weights as stored, activations e4m3)
     assert _cos(got, ref[-1]) > (0.99 if fmt in ("fp8_block", "mxfp4") else 0.998)
