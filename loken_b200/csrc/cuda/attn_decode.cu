@@ -46,6 +46,7 @@ struct DecodeParams {
   long long num_slots;
   int n_q, n_kv, max_blocks, block_size, window;
   float scale_log2;         // softmax scale * log2(e)
+  float* parts_out;         // nullable: emit (weighed values, maximum, sum) per head instead of the attention
 };
 
 template <int HD, int G, bool Q8>
@@ -284,6 +285,20 @@ attn_decode_kernel(const DecodeParams p) {
     }
   }
 
+  if (p.parts_out) {
+    // one range of a context held on several GPUs: hand out the part, the caller merges the ranges
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float* dst = p.parts_out + ((long long)row * p.n_q + kvh * G + g) * (HD + 2);
+      if (d < HD) dst[d] = fo[g];
+      if (d == 0) {
+        dst[HD] = fm[g];
+        dst[HD + 1] = fl[g];
+      }
+    }
+    return;
+  }
+
   // ---- sink, normalise, write ----
   __shared__ float red[32];
 #pragma unroll
@@ -361,6 +376,7 @@ LK_API int lk_attn_decode(const LkDecodeArgs* a, void* stream) {
   p.n_q = a->n_q; p.n_kv = a->n_kv; p.max_blocks = a->max_blocks; p.block_size = a->block_size;
   p.window = a->window;
   p.scale_log2 = a->scale * 1.4426950408889634f;
+  p.parts_out = a->parts_out;
   dim3 grid(a->n_kv, a->rows, nsplit);
   cudaStream_t st = (cudaStream_t)stream;
   if (a->hd == 128) return a->kv_q8 ? launch_g<128, true>(p, G, grid, st) : launch_g<128, false>(p, G, grid, st);

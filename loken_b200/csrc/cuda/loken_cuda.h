@@ -157,6 +157,10 @@ typedef struct LkDecodeArgs {
   long long num_slots;
   int rows, n_q, n_kv, hd, max_blocks, block_size, window, kv_q8, nsplit;
   float scale;
+  float* parts_out;         // lk_attn_decode only, optional f32 [rows, n_q, hd + 2]: instead of the attention, what
+                            // this cache contributes to it: the values weighed by exp2(score - max) (not divided),
+                            // then the maximum (log2 units of the scaled scores) and the sum of the weights;
+                            // parts of several caches merge into the attention over all of them
 } LkDecodeArgs;
 long long lk_attn_decode_ws_floats(int rows, int n_q, int n_kv, int hd, int nsplit);
 int lk_attn_decode(const LkDecodeArgs* args, void* stream);

@@ -87,7 +87,7 @@ class DecodeArgs(C.Structure):
         ("counters", vp), ("n_counters", C.c_int), ("status", vp), ("num_slots", ll),
         ("rows", C.c_int), ("n_q", C.c_int), ("n_kv", C.c_int), ("hd", C.c_int), ("max_blocks", C.c_int),
         ("block_size", C.c_int), ("window", C.c_int), ("kv_q8", C.c_int), ("nsplit", C.c_int),
-        ("scale", C.c_float),
+        ("scale", C.c_float), ("parts_out", vp),
     ]
 
 

@@ -33,10 +33,17 @@ def pick_decode_splits(rows: int, n_kv: int, max_ctx: int) -> int:
 def decode(q: torch.Tensor, cache: KVCacheLayer, block_table: torch.Tensor, seq_lens: torch.Tensor, *,
            block_size: int, scale: Optional[float] = None, window: int = 0, sinks: Optional[torch.Tensor] = None,
            row_seq: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-           out_fp8: Optional[Fp8Act] = None, nsplit: int = 1, rows: Optional[int] = None):
-    """q [rows, n_q, hd] bf16 -> out [rows, n_q*hd] bf16 (and/or e4m3 with per-head scales)."""
+           out_fp8: Optional[Fp8Act] = None, nsplit: int = 1, rows: Optional[int] = None,
+           parts_out: Optional[torch.Tensor] = None):
+    """q [rows, n_q, hd] bf16 -> out [rows, n_q*hd] bf16 (and/or e4m3 with per-head scales).  With `parts_out`
+    (f32 [rows, n_q, hd + 2]) nothing is normalised or written to `out`: the tensor receives what this cache
+    contributes to the attention (weighed values, maximum in log2 units, sum of weights), to be merged with the
+    parts of the other ranges of the context (`parallel/context_parallel.py`)."""
     R = rows if rows is not None else q.shape[0]
     n_q, hd = q.shape[1], q.shape[2]
+    if parts_out is not None:
+        assert parts_out.dtype == torch.float32 and tuple(parts_out.shape[1:]) == (n_q, hd + 2) and sinks is None
+        out = parts_out                      # nothing else is written
     if out is None and out_fp8 is None:
         out = torch.empty(q.shape[0], n_q * hd, dtype=torch.bfloat16, device=q.device)
     wsp = Workspace.get(q.device)
@@ -58,6 +65,10 @@ def decode(q: torch.Tensor, cache: KVCacheLayer, block_table: torch.Tensor, seq_
     a.max_blocks, a.block_size, a.window = block_table.shape[1], block_size, window
     a.kv_q8, a.nsplit = int(cache.q8), nsplit
     a.scale = scale if scale is not None else 1.0 / math.sqrt(hd)
+    if parts_out is not None:
+        a.out, a.parts_out = None, ptr(parts_out)
+        check(cuda_lib().lk_attn_decode(C.byref(a), stream()), "lk_attn_decode (parts)")
+        return parts_out
     fast = hd == 128 and cache.q8 and block_size == 16
     if fast and DECODE_KERNEL == "tc" and n_q // cache.n_kv in (1, 2, 4, 8):
         check(cuda_lib().lk_attn_decode_tc(C.byref(a), stream()), "lk_attn_decode_tc")
