@@ -72,6 +72,10 @@ struct GvParams {
   int M, N, K;
   int out_fp32;
   LkGemvPre pre;              // what the activations are computed from (plain rows, a norm, a gated unit)
+  // expert slots (streaming form, one token row per slot): slot s (blockIdx.y) multiplies row s / slot_x_div of x
+  // by the matrix of expert slot_expert[s] of a stack of [N, K] matrices and writes row s of out
+  const int* slot_expert;
+  int slots, slot_x_div, slot_e_lo, slot_e_cnt;
 };
 
 __device__ __forceinline__ void load8f(const __nv_bfloat16* src, float* v) {
@@ -86,8 +90,8 @@ __device__ __forceinline__ void load8f(const __nv_bfloat16* src, float* v) {
 }
 // Values 8 c .. 8 c + 7 of token row m of the residual stream as the norm sees it: x, plus the pending
 // update rounded into bf16 the way the stream stores it.
-__device__ __forceinline__ void residual8(const GvParams& p, int m, int c, float* v) {
-  load8f(p.x + (long long)m * p.ldx + c * 8, v);
+__device__ __forceinline__ void residual8(const GvParams& p, long long x_off, int m, int c, float* v) {
+  load8f(p.x + x_off + (long long)m * p.ldx + c * 8, v);
   if (p.pre.delta) {
     float d[8];
     load8f(reinterpret_cast<const __nv_bfloat16*>(p.pre.delta) + (long long)m * p.pre.ldd + c * 8, d);
@@ -99,9 +103,9 @@ __device__ __forceinline__ void residual8(const GvParams& p, int m, int c, float
 // Eight activations of token row m as the GEMV multiplies them: the rows of x themselves, or
 // RMSNorm(x + delta) * gamma (rinv = 1 / rms of the row), or the gated unit of x = [gate | up]; each rounded
 // to bf16 where the separate kernels store bf16.
-__device__ __forceinline__ void activation8(const GvParams& p, int m, int c, float rinv, float* v) {
+__device__ __forceinline__ void activation8(const GvParams& p, long long x_off, int m, int c, float rinv, float* v) {
   if (p.pre.mode == 1) {
-    residual8(p, m, c, v);
+    residual8(p, x_off, m, c, v);
     const float4* g4 = reinterpret_cast<const float4*>(p.pre.gamma + c * 8);
     const float4 ga = g4[0], gb = g4[1];
     const float g[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
@@ -109,8 +113,8 @@ __device__ __forceinline__ void activation8(const GvParams& p, int m, int c, flo
     for (int e = 0; e < 8; ++e) v[e] = bf2f(f2bf(v[e] * rinv * g[e]));
   } else if (p.pre.mode == 2) {
     float u[8];
-    load8f(p.x + (long long)m * p.ldx + c * 8, v);
-    load8f(p.x + (long long)m * p.ldx + p.K + c * 8, u);
+    load8f(p.x + x_off + (long long)m * p.ldx + c * 8, v);
+    load8f(p.x + x_off + (long long)m * p.ldx + p.K + c * 8, u);
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
       float o;
@@ -124,7 +128,7 @@ __device__ __forceinline__ void activation8(const GvParams& p, int m, int c, flo
       v[e] = bf2f(f2bf(o));
     }
   } else {
-    load8f(p.x + (long long)m * p.ldx + c * 8, v);
+    load8f(p.x + x_off + (long long)m * p.ldx + c * 8, v);
   }
 }
 
@@ -137,8 +141,8 @@ __device__ __forceinline__ void activation8(const GvParams& p, int m, int c, flo
 // update that an earlier kernel of the step left pending (upd_x += upd_delta): every reader of the old rows
 // finished with the kernel before this one.
 template <int FMT, int MT, class SYNC>
-__device__ __forceinline__ void stage_activations(const GvParams& p, uint32_t* xq, float* xd, float* xs, int ngroups,
-                                                  SYNC sync) {
+__device__ __forceinline__ void stage_activations(const GvParams& p, long long x_off, uint32_t* xq, float* xd, float* xs,
+                                                  int ngroups, SYNC sync) {
   __shared__ float s_red[GV_WARPS][8];
   __shared__ float s_rinv[8];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -169,7 +173,7 @@ __device__ __forceinline__ void stage_activations(const GvParams& p, uint32_t* x
 #pragma unroll 4
         for (int c = tid; c < cpr; c += GV_WARPS * 32) {
           float v[8];
-          residual8(p, m, c, v);
+          residual8(p, x_off, m, c, v);
 #pragma unroll
           for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
         }
@@ -198,7 +202,7 @@ __device__ __forceinline__ void stage_activations(const GvParams& p, uint32_t* x
       const int ch = base + u * GV_WARPS * 32 + tid;
       const int m = ch / cpr, c = ch % cpr;
       if (ch < total && m < p.M) {
-        activation8(p, m, c, p.pre.mode == 1 ? s_rinv[m] : 1.f, v[u]);
+        activation8(p, x_off, m, c, p.pre.mode == 1 ? s_rinv[m] : 1.f, v[u]);
       } else {
 #pragma unroll
         for (int e = 0; e < 8; ++e) v[u][e] = 0.f;
@@ -276,7 +280,7 @@ gemv_q_kernel(const GvParams p) {
   float* xd = reinterpret_cast<float*>(gv_smem + (size_t)MT * p.K);            // [MT][K / 32]
   float* xs = xd + MT * ngroups;                                               // [MT][K / 32]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  stage_activations<FMT, MT>(p, xq, xd, xs, ngroups, [] { __syncthreads(); });
+  stage_activations<FMT, MT>(p, 0, xq, xd, xs, ngroups, [] { __syncthreads(); });
 
   // row groups of RW rows per warp, strided over the grid; no barrier from here on
   const int n_rg = (p.N + GV_WARPS * RW - 1) / (GV_WARPS * RW);
@@ -463,6 +467,22 @@ template <int FMT, int MT, int R, int RWP, bool XR>
 __global__ void __launch_bounds__(GS_THREADS)
 gemv_q_stream_kernel(const GvParams p, int S, long long l2_budget, int* status) {
   static_assert(!XR || MT == 1, "activations in registers: one token row");
+  // where this CTA's matrix, token row and output row start (an expert slot moves all of them)
+  const uint8_t* codes = p.codes;
+  const uint8_t* scales = p.scales;
+  const float* bias = p.bias;
+  long long x_off = 0, out_row0 = 0;
+  if (p.slot_expert) {
+    pdl_wait();                 // the expert of a slot is the routing kernel's output: nothing starts before it
+    const int slot = blockIdx.y;
+    const int e = p.slot_expert[slot] - p.slot_e_lo;
+    if (e < 0 || e >= p.slot_e_cnt) return;           // another rank's expert
+    codes += (long long)e * p.N * gs_code_bytes<FMT>(p.K);
+    scales += (long long)e * p.N * gs_scale_bytes<FMT>(p.K);
+    x_off = (long long)(slot / p.slot_x_div) * p.ldx;
+    out_row0 = slot;
+    if (bias) bias += (long long)e * p.N;
+  }
   constexpr int NRG = R / RWP;             // row groups of a stage
   constexpr int KS = GS_WARPS / NRG;       // warps per row group, each takes every KS-th run of 32 groups
   static_assert(R % RWP == 0 && GS_WARPS % NRG == 0, "stage geometry");
@@ -508,8 +528,8 @@ gemv_q_stream_kernel(const GvParams p, int S, long long l2_budget, int* status) 
         // a single-stream step of an 8B Q4_K_M model ran 4 to 5 % slower with the hints than without.
         const long long r0 = (long long)(b0 + S) * R, r1 = min((long long)p.N, (long long)b1 * R);
         const long long rows = min(r1 - r0, l2_budget / (cb + sb));
-        const uint8_t* c0 = p.codes + r0 * cb;
-        const uint8_t* s0 = p.scales + r0 * sb;
+        const uint8_t* c0 = codes + r0 * cb;
+        const uint8_t* s0 = scales + r0 * sb;
         for (long long off = lane * 4096ll; off < rows * cb; off += 32 * 4096)
           l2_prefetch_bulk(c0 + off, (uint32_t)min(4096ll, rows * cb - off));
         for (long long off = lane * 128ll; off < rows * sb; off += 32 * 128) l2_prefetch_line(s0 + off);
@@ -522,8 +542,8 @@ gemv_q_stream_kernel(const GvParams p, int S, long long l2_budget, int* status) 
         if (prof && it == 0) prof[blockIdx.x * 8 + 5] = (long long)globaltimer_ns();
         if (prof && it == nitems - 1) prof[blockIdx.x * 8 + 6] = (long long)globaltimer_ns();
         mbar_expect_tx(&full[s], (uint32_t)(nvalid * (cb + sb)));
-        bulk_g2s(st, p.codes + row0 * cb, (uint32_t)(nvalid * cb), &full[s]);
-        bulk_g2s(st + R * cb, p.scales + row0 * sb, (uint32_t)(nvalid * sb), &full[s]);
+        bulk_g2s(st, codes + row0 * cb, (uint32_t)(nvalid * cb), &full[s]);
+        bulk_g2s(st + R * cb, scales + row0 * sb, (uint32_t)(nvalid * sb), &full[s]);
       }
       __syncwarp();
     }
@@ -534,7 +554,7 @@ gemv_q_stream_kernel(const GvParams p, int S, long long l2_budget, int* status) 
   pdl_wait();
   if (prof && threadIdx.x == 0) prof[blockIdx.x * 8 + 1] = (long long)globaltimer_ns();
   pdl_launch();
-  stage_activations<FMT, MT>(p, xq, xd, xs, ngroups, [] { consumer_sync(); });
+  stage_activations<FMT, MT>(p, x_off, xq, xd, xs, ngroups, [] { consumer_sync(); });
   if (prof && threadIdx.x == 0) prof[blockIdx.x * 8 + 2] = (long long)globaltimer_ns();
 
   const int rgp = warp / KS, ks = warp % KS;
@@ -627,11 +647,11 @@ gemv_q_stream_kernel(const GvParams p, int S, long long l2_budget, int* status) 
       for (int k = 0; k < KS; ++k) v += src[k * (RWP * MT)];
       const long long n = row0 + row;
       if (n < p.N && m < p.M) {
-        const float o = v + (p.bias ? p.bias[n] : 0.f);
+        const float o = v + (bias ? bias[n] : 0.f);
         if (p.out_fp32)
-          reinterpret_cast<float*>(p.out)[(long long)m * p.ldo + n] = o;
+          reinterpret_cast<float*>(p.out)[(out_row0 + m) * p.ldo + n] = o;
         else
-          p.out[(long long)m * p.ldo + n] = f2bf(o);
+          p.out[(out_row0 + m) * p.ldo + n] = f2bf(o);
       }
     }
   }
@@ -645,7 +665,7 @@ gemv_q_stream_kernel(const GvParams p, int S, long long l2_budget, int* status) 
 static int g_gemv_stream = 1;
 
 template <int FMT, int MT, int R, bool XR>
-int launch_gs_x(const GvParams& p, cudaStream_t st, int* status) {
+int launch_gs_x(const GvParams& p, cudaStream_t st, int* status, bool dry) {
   // rows per warp: as many as leave every lane of the warps that share a row group a group of K (R = 8:
   // four rows, four warps per group; shorter stages come with long rows)
   constexpr int RWP = R == 8 ? 4 : R >= 2 ? 2 : 1;
@@ -660,6 +680,7 @@ int launch_gs_x(const GvParams& p, cudaStream_t st, int* status) {
   int S = (int)((budget - fixed) / pitch);
   if (S > 12) S = 12;
   const size_t smem = fixed + (size_t)S * pitch;
+  if (dry) return 0;
   auto kern = gemv_q_stream_kernel<FMT, MT, R, RWP, XR>;
   static bool granted = false;
   if (!granted) {
@@ -669,25 +690,32 @@ int launch_gs_x(const GvParams& p, cudaStream_t st, int* status) {
   }
   const int nblk = (p.N + R - 1) / R;
   const int per_sm = budget > 100 * 1024 ? 1 : 2;
-  const int grid = nblk < 148 * per_sm ? nblk : 148 * per_sm;
-  const long long l2_budget = (g_gemv_stream & 2) ? (64ll << 20) / grid : 0;
-  lkh::launch_pdl(kern, dim3(grid), dim3(GS_THREADS), smem, st, p, S, l2_budget, status);
+  int grid = nblk < 148 * per_sm ? nblk : 148 * per_sm;
+  int grid_y = 1;
+  if (p.slot_expert) {
+    // the slots share the SMs: each gets its part of the CTAs, at least one
+    grid_y = p.slots;
+    const int share = (148 * per_sm) / p.slots;
+    grid = share < 1 ? 1 : (nblk < share ? nblk : share);
+  }
+  const long long l2_budget = ((g_gemv_stream & 2) && !p.slot_expert) ? (64ll << 20) / grid : 0;
+  lkh::launch_pdl(kern, dim3(grid, grid_y), dim3(GS_THREADS), smem, st, p, S, l2_budget, status);
   return 0;
 }
 
 template <int FMT, int MT, int R>
-int launch_gs_r(const GvParams& p, cudaStream_t st, int* status) {
+int launch_gs_r(const GvParams& p, cudaStream_t st, int* status, bool dry) {
   constexpr int RWP = R == 8 ? 4 : R >= 2 ? 2 : 1;
   constexpr int KS = GS_WARPS / (R / RWP);
-  if (MT == 1 && (p.K >> 5) <= 2 * KS * 32) return launch_gs_x<FMT, 1, R, true>(p, st, status);
-  return launch_gs_x<FMT, MT, R, false>(p, st, status);
+  if (MT == 1 && (p.K >> 5) <= 2 * KS * 32) return launch_gs_x<FMT, 1, R, true>(p, st, status, dry);
+  return launch_gs_x<FMT, MT, R, false>(p, st, status, dry);
 }
 
 // Takes the shape when both planes are contiguous and every copy starts and ends on 16 bytes.
 template <int FMT, int MT>
-int launch_gs(const GvParams& p, cudaStream_t st, int* status, bool* taken) {
+int launch_gs(const GvParams& p, cudaStream_t st, int* status, bool* taken, bool dry = false) {
   *taken = false;
-  if (!g_gemv_stream || !status) return 0;
+  if (!g_gemv_stream || (!status && !dry)) return 0;
   // eight consumer warps are too few once every group of weights meets four or more token rows: there the
   // register form (24 warps per SM) is as fast or faster, except for the 8-bit planes at up to four rows
   // (Q6_K 4096 x 14336 at four rows: 25 us here, 33 us there; Q4_K 28672 x 4096: 46 us here, 32 us there)
@@ -707,12 +735,13 @@ int launch_gs(const GvParams& p, cudaStream_t st, int* status, bool* taken) {
   }
   const long long tail = p.N % R;
   if (((R * cb) & 15) || ((R * sb) & 15) || ((tail * cb) & 15) || ((tail * sb) & 15)) return 0;
+  if (p.slot_expert && ((p.N * sb) & 15)) return 0;      // every expert's scale plane starts on 16 bytes
   int rc;
   switch (R) {
-    case 8: rc = launch_gs_r<FMT, MT, 8>(p, st, status); break;
-    case 4: rc = launch_gs_r<FMT, MT, 4>(p, st, status); break;
-    case 2: rc = launch_gs_r<FMT, MT, 2>(p, st, status); break;
-    default: rc = launch_gs_r<FMT, MT, 1>(p, st, status); break;
+    case 8: rc = launch_gs_r<FMT, MT, 8>(p, st, status, dry); break;
+    case 4: rc = launch_gs_r<FMT, MT, 4>(p, st, status, dry); break;
+    case 2: rc = launch_gs_r<FMT, MT, 2>(p, st, status, dry); break;
+    default: rc = launch_gs_r<FMT, MT, 1>(p, st, status, dry); break;
   }
   if (rc < 0) return 0;            // does not fit: the register form takes it
   if (rc == 0) *taken = true;
@@ -946,6 +975,8 @@ LK_API int lk_gemv_q(int fmt, const void* codes, long long c_ld, const void* sca
   p.M = M;
   p.N = N;
   p.K = K;
+  p.slot_expert = nullptr;
+  p.slots = p.slot_x_div = p.slot_e_lo = p.slot_e_cnt = 0;
   memset(&p.pre, 0, sizeof(p.pre));
   if (pre) {
     p.pre = *pre;
@@ -969,6 +1000,58 @@ LK_API int lk_gemv_q(int fmt, const void* codes, long long c_ld, const void* sca
     default: return LKH_BAD_ARG;
   }
   if (rc) return rc;
+  lkh::count_launch();
+  return lkh::launch_status();
+}
+
+// Expert slots: a stack of `n_experts` [N, K] matrices in contiguous planes; slot s multiplies row s / x_div of x
+// (bf16, row pitch ldx; with the gated unit in front: 2K wide) by the matrix of expert slot_expert[s] - e_lo (a slot
+// whose expert is not in [e_lo, e_lo + n_experts) writes nothing) and writes row s of out [slots, N] (+ bias
+// [n_experts, N]).  The expert ids are read on the device, so a routing kernel can come right before this one.
+// dry != 0: launch nothing, return 0 if the shape is taken and LKH_BAD_ARG if not.
+LK_API int lk_gemv_q_slots(int fmt, const void* codes, const void* scales, const void* x, long long ldx, int slots,
+                           int x_div, const int* slot_expert, int e_lo, int n_experts, int N, int K, const float* bias,
+                           void* out, long long ldo, const LkGemvPre* pre, int* status, int dry, void* stream) {
+  if (slots <= 0 || N <= 0) return LKH_OK;
+  if ((K & 31) || ((fmt == GV_W8G16 || fmt == GV_W4) && (K & 255)) || x_div <= 0 || n_experts <= 0) return LKH_BAD_ARG;
+  if (!dry && (!codes || !scales || !x || !out || !slot_expert || !status || (ldx & 7) ||
+               (reinterpret_cast<uintptr_t>(codes) & 15) || (reinterpret_cast<uintptr_t>(x) & 15)))
+    return LKH_BAD_ARG;
+  GvParams p;
+  memset(&p, 0, sizeof(p));
+  p.codes = reinterpret_cast<const uint8_t*>(codes);
+  p.scales = reinterpret_cast<const uint8_t*>(scales);
+  p.x = reinterpret_cast<const __nv_bfloat16*>(x);
+  p.ldx = ldx;
+  p.bias = bias;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.ldo = ldo;
+  p.M = 1;
+  p.N = N;
+  p.K = K;
+  static const int dummy = 0;
+  p.slot_expert = dry ? &dummy : slot_expert;
+  p.slots = slots;
+  p.slot_x_div = x_div;
+  p.slot_e_lo = e_lo;
+  p.slot_e_cnt = n_experts;
+  if (pre) {
+    p.pre = *pre;
+    if (p.pre.mode != 0 && p.pre.mode != 2) return LKH_BAD_ARG;       // a norm in front would need the row's own update
+    if (p.pre.upd_x) return LKH_BAD_ARG;
+  }
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  bool taken = false;
+  int rc;
+  switch (fmt) {
+    case GV_W8: p.c_ld = K; p.s_ld = gs_scale_bytes<GV_W8>(K); rc = launch_gs<GV_W8, 1>(p, st, status, &taken, dry != 0); break;
+    case GV_W8G16: p.c_ld = K; p.s_ld = gs_scale_bytes<GV_W8G16>(K); rc = launch_gs<GV_W8G16, 1>(p, st, status, &taken, dry != 0); break;
+    case GV_W4: p.c_ld = K / 2; p.s_ld = gs_scale_bytes<GV_W4>(K); rc = launch_gs<GV_W4, 1>(p, st, status, &taken, dry != 0); break;
+    default: return LKH_BAD_ARG;
+  }
+  if (rc) return rc;
+  if (!taken) return LKH_BAD_ARG;
+  if (dry) return LKH_OK;
   lkh::count_launch();
   return lkh::launch_status();
 }

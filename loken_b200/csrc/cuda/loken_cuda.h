@@ -123,6 +123,12 @@ void lk_gemv_q_stream(int on);
 // The same planes decoded to bf16 out [rows, K], row pitch ldo elements: the operand of prompt-sized GEMMs.
 int lk_dequant_q(int fmt, const void* codes, long long c_ld, const void* scales, long long s_ld, void* out,
                  long long ldo, int rows, int K, void* stream);
+// Expert slots on the streaming GEMV: slot s multiplies row s / x_div of x by expert slot_expert[s] - e_lo of a stack
+// of n_experts [N, K] matrices (contiguous planes) and writes row s of out [slots, N]; expert ids are read on the
+// device.  dry != 0 only answers whether the shape is taken (0) or not (bad argument).
+int lk_gemv_q_slots(int fmt, const void* codes, const void* scales, const void* x, long long ldx, int slots, int x_div,
+                    const int* slot_expert, int e_lo, int n_experts, int N, int K, const float* bias, void* out,
+                    long long ldo, const LkGemvPre* pre, int* status, int dry, void* stream);
 // Embedding gather from a quantised table (the same planes): rows tokens[0 .. T) decoded to bf16 out [T, H].
 int lk_embed_q(int fmt, const int* tokens, const void* codes, long long c_ld, const void* scales, long long s_ld,
                void* out, int T, int H, int vocab, float scale, void* stream);

@@ -285,8 +285,44 @@ class MoeRunner:
               "lk_ep_combine")
         comm.collectives += 2
 
+    SLOT_MAX_PAIRS = 64      # up to this many (token, expert) pairs a decode step runs its experts as GEMV slots; 0: off
+
+    def _slots_ok(self, moe: MoeWeights, T: int) -> bool:
+        """Decode-size steps of GGUF experts held whole on this rank: the experts run as GEMV slots."""
+        if not (0 < T * self.cfg.top_k <= self.SLOT_MAX_PAIRS) or self.use_mx or (self.comm is not None and self.comm.size > 1):
+            return False
+        ok = getattr(moe, "_slots_ok", None)
+        if ok is None:
+            from ..ops import quant
+
+            ok = moe._slots_ok = bool(moe.e_cnt == self.cfg.n_experts and moe.e_lo == 0
+                                      and quant.gemv_slots_takes(moe.gate_up, moe.e_cnt)
+                                      and quant.gemv_slots_takes(moe.down, moe.e_cnt))
+        return ok
+
+    def forward_slots(self, moe: MoeWeights, h: torch.Tensor, out: torch.Tensor, T: int):
+        """Router, then two launches of the streaming GEMV over (token, expert) slots (the expert of a slot is read
+        on the device; the gated unit runs in front of the down projection), then the weighted sum: four kernels
+        where the planned form takes seven, and no expert's weights are decoded to bf16."""
+        from ..ops import quant
+
+        cfg, pl = self.cfg, self.plan
+        k, P = cfg.top_k, T * cfg.top_k
+        self.route(moe, h, T)
+        ids = pl.ids.view(-1)
+        quant.gemv_slots(h, moe.gate_up, ids, P, k, moe.e_cnt, bias=moe.gate_up_b, out=self.gu[:P])
+        quant.gemv_slots(self.gu[:P], moe.down, ids, P, 1, moe.e_cnt, bias=moe.down_b, out=self.y[:P],
+                         glu=(cfg.glu_mode, cfg.glu_alpha, cfg.glu_limit))
+        if getattr(self, "_ident", None) is None:
+            self._ident = torch.arange(self.y.shape[0], dtype=torch.int32, device=self.device)
+        check(cuda_lib().lk_moe_combine(ptr(self.y), C.c_longlong(self.y.stride(0)), ptr(self._ident), ptr(pl.wts),
+                                        T, k, cfg.hidden, ptr(out), C.c_longlong(out.stride(0)), 0, stream()),
+              "lk_moe_combine")
+
     def forward(self, il: int, moe: MoeWeights, h: torch.Tensor, out: torch.Tensor, T: int):
         """h [T, H] bf16 (normalised hidden states, replicated on every rank) -> out [T, H]."""
+        if self._slots_ok(moe, T):
+            return self.forward_slots(moe, h, out, T)
         self.route(moe, h, T)
         self.make_plan(moe, T)
         self.experts(moe, h, T, out)

@@ -270,6 +270,34 @@ class GemvFront:
         return a
 
 
+def gemv_slots_takes(w, n_experts: int) -> bool:
+    """Can `gemv_slots` run over this stack of `n_experts` matrices ([n_experts * N, K] planes)?"""
+    if not isinstance(w, QuantWeight) or w.aq_fmt not in (AQ_W8, AQ_W8G16, AQ_W4) or w.rows % n_experts:
+        return False
+    if not w.codes.is_cuda or not w.codes.is_contiguous() or not w.scales.is_contiguous():
+        return False
+    rc = cuda_lib().lk_gemv_q_slots(w.aq_fmt, None, None, None, C.c_longlong(0), 1, 1, None, 0, n_experts,
+                                    w.rows // n_experts, w.K, None, None, C.c_longlong(0), None, None, 1, None)
+    return rc == 0
+
+
+def gemv_slots(x: torch.Tensor, w: QuantWeight, slot_expert: torch.Tensor, slots: int, x_div: int, n_experts: int, *,
+               e_lo: int = 0, bias: Optional[torch.Tensor] = None, out: torch.Tensor, glu: Optional[tuple] = None):
+    """Decode-size mixture products on the streaming GEMV: slot s takes row s // x_div of x (bf16; with `glu` the row
+    is [gate | up], 2K wide) times the matrix of expert slot_expert[s] of the stack `w` ([n_experts * N, K] planes,
+    see `gemv_slots_takes`) into row s of out [slots, N].  slot_expert is an int32 device tensor: the routing kernel
+    can be the launch right before this one, nothing is planned or permuted on the way."""
+    N = w.rows // n_experts
+    assert slot_expert.dtype == torch.int32 and slot_expert.numel() >= slots and out.shape[1] == N and out.stride(1) == 1
+    assert x.stride(1) == 1 and x.shape[1] == (2 * w.K if glu is not None else w.K)
+    pre = GemvFront(glu=glu).pack(1) if glu is not None else None
+    check(cuda_lib().lk_gemv_q_slots(w.aq_fmt, ptr(w.codes), ptr(w.scales), ptr(x), C.c_longlong(x.stride(0)), slots, x_div,
+                                     ptr(slot_expert), e_lo, n_experts, N, w.K, ptr(bias), ptr(out),
+                                     C.c_longlong(out.stride(0)), C.byref(pre) if pre is not None else None,
+                                     ptr(Workspace.get(x.device).status), 0, stream()), "lk_gemv_q_slots")
+    return out
+
+
 def linear_gguf(x: torch.Tensor, w: QuantWeight, *, bias: Optional[torch.Tensor] = None,
                 out: Optional[torch.Tensor] = None, splits: int = 0, out_fp32: bool = False,
                 front: Optional[GemvFront] = None) -> torch.Tensor:

@@ -174,3 +174,50 @@ def _front_case(quant, rows, fmt, M, N, K):
         assert torch.equal(res[:M], (res0[:M].float() + delta.float()).bfloat16()) and torch.equal(res[M:], res0[M:])
     with pytest.raises(ValueError):
         quant.linear_gguf(torch.zeros(9, K, device=DEV, dtype=torch.bfloat16), q, front=quant.GemvFront(norm=gamma))
+
+
+@pytest.mark.parametrize("fmt", ["q8_0", "q4_k_m"])
+@pytest.mark.parametrize("arch", ["gpt-oss", "olmoe"])
+@pytest.mark.parametrize("T", [1, 3, 8])
+def test_decode_size_mixture_layers_run_their_experts_as_gemv_slots(arch, fmt, T):
+    """Up to 64 (token, expert) pairs the experts of a GGUF mixture layer run as slots of the streaming GEMV (the
+    expert of a slot read on the device, the gated unit in front of the down projection): same result as the
+    planned grouped GEMMs, within the int8 noise of the activations, and as the fp32 definition."""
+    import dataclasses
+
+    from loken_b200.models.config import tiny
+    from loken_b200.models.moe import MoeRunner, dequant_experts, random_moe
+    from loken_b200.models.reference import moe_ref
+    from loken_b200.ops._lib import Workspace
+
+    cfg = dataclasses.replace(tiny(arch, weight_format=fmt), n_experts=8, top_k=4, hidden=512, expert_intermediate=256,
+                              n_layers=1)
+    gen = torch.Generator(device=DEV).manual_seed(T)
+    moe = random_moe(cfg, gen, DEV, 0.05)
+
+    class W:
+        pass
+    w, lay = W(), W()
+    w.embed = torch.zeros(1, device=DEV)
+    lay.moe = moe
+    w.layers = [lay]
+    run = MoeRunner(cfg, w, 16)
+    assert run._slots_ok(moe, T) and not run._slots_ok(moe, 17)
+    h = torch.randn(16, cfg.hidden, device=DEV).bfloat16()
+    got = torch.zeros(16, cfg.hidden, device=DEV, dtype=torch.bfloat16)
+    plan = torch.zeros_like(got)
+    run.forward(0, moe, h, got, T)
+    old = MoeRunner.SLOT_MAX_PAIRS
+    try:
+        MoeRunner.SLOT_MAX_PAIRS = 0
+        run.forward(0, moe, h, plan, T)
+    finally:
+        MoeRunner.SLOT_MAX_PAIRS = old
+    torch.cuda.synchronize()
+    assert Workspace.get(torch.device(DEV)).read_status() == 0
+    want = moe_ref(h[:T].float(), moe, cfg)
+    scale = want.abs().max().item()
+    # two chained products on int8 activations (the reference's bar for one is 2e-2 of the largest output)
+    assert (got[:T].float() - want).abs().max().item() < 5e-2 * scale
+    assert (got[:T].float() - plan[:T].float()).abs().max().item() < 5e-2 * scale
+    assert (got[T:] == 0).all()
