@@ -12,7 +12,10 @@
     loken pull NAME                       fetch a model into the daemon's stores (streams progress; resumable)
     loken swap PATH [--id NAME]           replace the resident model
     loken launch AGENT [-m MODEL] [--config] [-- ARGS]      run a coding agent against the daemon
-Commands that need a hub catalogue (popular, draft-head, calibrate) say that this build has none.
+    loken popular                         a few models to start with
+    loken calibrate MODEL -n NAME -t FILE...   have the daemon record a calibration for `convert`
+    loken draft-head SOURCE OUT           write a model's multi-token-prediction head (its `mtp.*` tensors) as a
+                                          companion file the daemon can attach (`loken draft attach --method head`)
 """
 from __future__ import annotations
 
@@ -142,9 +145,77 @@ def build_parser() -> argparse.ArgumentParser:
     la.add_argument("-m", "--model")
     la.add_argument("--config", action="store_true", help="print or write the configuration and start nothing")
     la.add_argument("args", nargs="*", help="arguments handed to the agent, after --")
-    for name in ("popular", "draft-head", "calibrate"):
-        sub.add_parser(name).add_argument("args", nargs="*")
+    sub.add_parser("popular")
+    ca = sub.add_parser("calibrate")
+    ca.add_argument("model", help="the checkpoint: a path or a name in the model stores")
+    ca.add_argument("-n", "--name", required=True, help="the record's name, which convert refers to")
+    ca.add_argument("-t", "--text", required=True, nargs="+", help="text files to calibrate on, read here and sent")
+    ca.add_argument("--excerpt", type=int, help="characters taken from each text")
+    ca.add_argument("--tokens", type=int, help="tokens in all")
+    dh = sub.add_parser("draft-head")
+    dh.add_argument("source", help="a checkpoint directory (safetensors) or a GGUF file that carries mtp.* tensors")
+    dh.add_argument("output", help="OUT.gguf, or a directory for a safetensors companion")
     return ap
+
+
+POPULAR = (
+    ("Qwen/Qwen3-0.6B", "small enough for a laptop CPU"),
+    ("Qwen/Qwen3-8B", "general purpose, one GPU with room to spare"),
+    ("meta-llama/Llama-3.1-8B-Instruct", "the common baseline; Q4_K_M files are everywhere"),
+    ("openai/gpt-oss-120b", "a mixture model in MXFP4: one B200, or eight with expert parallelism"),
+    ("meta-llama/Llama-3.3-70B-Instruct", "block-fp8 on one B200, tensor-parallel for latency"),
+)
+
+
+def extract_draft_head(source: str, output: str) -> dict:
+    """Collects a checkpoint's multi-token-prediction tensors (`mtp.*`, with or without a `model.` prefix) and
+    writes them as a companion: OUT.gguf (tensor names without the prefix, `general.type = draft-head`) or a
+    directory holding `head.safetensors`.  Both are what `serve/draft_head.py: load_draft_head` reads."""
+    import glob
+    import os
+
+    import numpy as np
+
+    tensors = {}
+    if os.path.isdir(source):
+        from safetensors import safe_open
+
+        for f in sorted(glob.glob(os.path.join(source, "*.safetensors"))):
+            with safe_open(f, framework="pt", device="cpu") as h:
+                for k in h.keys():
+                    name = k.removeprefix("model.")
+                    if name.startswith("mtp."):
+                        tensors[name[4:]] = h.get_tensor(k).float().numpy()
+    else:
+        from ..formats import gguf as G
+
+        r = G.GGUFReader(source)
+        try:
+            for k, ti in r.tensors.items():
+                if k.startswith("mtp."):
+                    tensors[k[4:]] = ti.to_float()
+        finally:
+            r.close()
+    if not tensors:
+        raise ValueError(f"{source} carries no mtp.* tensors")
+    if output.endswith(".gguf"):
+        from ..formats import gguf as G
+
+        w = G.GGUFWriter(output)
+        w.add_meta("general.type", "draft-head")
+        w.add_meta("general.name", os.path.basename(os.path.normpath(source)) + " (mtp)")
+        for k, v in tensors.items():
+            w.add_tensor(k, np.ascontiguousarray(v, dtype=np.float32), G.F32 if v.ndim < 2 else G.BF16)
+        w.close()
+    else:
+        import torch
+        from safetensors.torch import save_file
+
+        os.makedirs(output, exist_ok=True)
+        save_file({k: torch.from_numpy(np.ascontiguousarray(v)).bfloat16() if v.ndim >= 2 else torch.from_numpy(v.copy())
+                   for k, v in tensors.items()}, os.path.join(output, "head.safetensors"))
+    return {"source": source, "output": output, "tensors": len(tensors),
+            "bytes": int(sum(v.size for v in tensors.values()) * 2)}
 
 
 def main(argv=None, out=sys.stdout) -> int:
@@ -215,6 +286,32 @@ def main(argv=None, out=sys.stdout) -> int:
             cfg = dataclasses.replace(cfg, n_layers=args.layers)
         export_random_gguf(args.output, cfg, seed=args.seed)
         p(f"wrote {args.output}")
+    elif args.cmd == "popular":
+        p("A few models to start with, by their Hugging Face ids:")
+        for name, why in POPULAR:
+            p(f"  {name}\n      {why}")
+        p("`loken pull NAME` fetches one; any GGUF file or safetensors directory loads with `loken load PATH`.")
+    elif args.cmd == "calibrate":
+        texts = []
+        for path in args.text:
+            with open(path, encoding="utf-8", errors="replace") as f:
+                texts.append(f.read())
+        body = {"model": args.model, "name": args.name, "texts": texts}
+        if args.excerpt:
+            body["excerpt"] = args.excerpt
+        if args.tokens:
+            body["tokens"] = args.tokens
+        last = None
+        for ev in cl.ndjson("/api/calibrate", body):
+            last = ev
+            p(json.dumps(ev))
+        return 0 if last is not None and "error" not in last else 1
+    elif args.cmd == "draft-head":
+        try:
+            p(json.dumps(extract_draft_head(args.source, args.output), indent=1))
+        except (ValueError, OSError) as e:
+            p(f"loken draft-head: {e}")
+            return 1
     elif args.cmd == "swap":
         p(json.dumps(cl.json("POST", "/api/swap", {"model": args.path, "id": args.id}), indent=1))
     elif args.cmd == "pull":
@@ -260,8 +357,7 @@ def main(argv=None, out=sys.stdout) -> int:
         else:
             p(json.dumps(cl.json("POST", "/api/draft/detach", {"model": args.model})))
     else:
-        p(f"loken {args.cmd}: this build has no hub catalogue; `loken pull NAME` fetches a named model and "
-          f"`loken load PATH` loads a file")
+        p(f"loken {args.cmd}: unknown command")
         return 1
     return 0
 

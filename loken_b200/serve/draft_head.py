@@ -71,12 +71,22 @@ def load_draft_head(directory: str, cfg, device) -> DraftHeadWeights:
     from ..models.weights import LayerWeights, make_linear
 
     t: Dict[str, torch.Tensor] = {}
+    if os.path.isfile(directory) and directory.endswith(".gguf"):
+        # the companion `loken draft-head` writes: the checkpoint's mtp.* tensors under their own names
+        from ..formats import gguf as G
+
+        r = G.GGUFReader(directory)
+        try:
+            for k, ti in r.tensors.items():
+                t[k.removeprefix("mtp.")] = torch.from_numpy(ti.to_float().copy())
+        finally:
+            r.close()
     for f in sorted(glob.glob(os.path.join(directory, "*.safetensors"))):
         with safe_open(f, framework="pt", device="cpu") as h:
             for k in h.keys():
-                t[k.removeprefix("model.")] = h.get_tensor(k)
+                t[k.removeprefix("model.").removeprefix("mtp.")] = h.get_tensor(k)
     if not t:
-        raise FileNotFoundError(f"no .safetensors files in {directory}")
+        raise FileNotFoundError(f"no .safetensors files (and no .gguf companion) at {directory}")
     kind = "mtp" if "eh_proj.weight" in t else "eagle"
     fc = t["eh_proj.weight" if kind == "mtp" else "fc.weight"]
     H = cfg.hidden
