@@ -32,7 +32,10 @@ using namespace lk;
 namespace {
 
 constexpr int GV_WARPS = 8;
-enum { GV_W8 = 1, GV_W8G16 = 2, GV_W4 = 3 };
+// GV_W4G: nibbles like GV_W4, per 128 values one f16 scale and one f16 minimum (= zero point x scale): AWQ's
+// 4-bit weights with groups of 128 (w = (q - zero) * scale), repacked at load (ops/quant.py: from_awq)
+enum { GV_W8 = 1, GV_W8G16 = 2, GV_W4 = 3, GV_W4G = 5 };
+template <int FMT> __host__ __device__ constexpr bool gv_nibbles() { return FMT == GV_W4 || FMT == GV_W4G; }
 
 __device__ __forceinline__ int dp4a_s8(uint32_t a, uint32_t b, int c) {
   int d;
@@ -229,7 +232,7 @@ __device__ __forceinline__ void stage_activations(const GvParams& p, long long x
 #pragma unroll
       for (int e = 0; e < 8; ++e) q8[e] = __float2int_rn(v[u][e] * id) & 0xFF;
       uint2 w;
-      if (FMT == GV_W4) {
+      if (gv_nibbles<FMT>()) {
         w.x = q8[0] | (q8[2] << 8) | (q8[4] << 16) | (q8[6] << 24);
         w.y = q8[1] | (q8[3] << 8) | (q8[5] << 16) | (q8[7] << 24);
       } else {
@@ -259,7 +262,7 @@ gemv_q_kernel(const GvParams p) {
   {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_rg = (p.N + GV_WARPS * RW - 1) / (GV_WARPS * RW);
-    const uint32_t code_bytes = FMT == GV_W4 ? p.K >> 1 : p.K;
+    const uint32_t code_bytes = gv_nibbles<FMT>() ? p.K >> 1 : p.K;
     for (int rg = blockIdx.x; rg < n_rg; rg += gridDim.x) {
       const int row0 = (rg * GV_WARPS + warp) * RW;
       if (row0 >= p.N) continue;
@@ -341,11 +344,18 @@ gemv_q_kernel(const GvParams p) {
           }
         } else {
           const uint4 c0 = __ldcs(reinterpret_cast<const uint4*>(p.codes + (long long)n * p.c_ld + (k >> 1)));
-          const uint8_t* rec = p.scales + (long long)n * p.s_ld + (k >> 8) * 20;
-          const int j = (k & 255) >> 5;
-          const uint32_t dd = *reinterpret_cast<const uint32_t*>(rec);          // d and dmin: records are 4-byte aligned
-          const float d = __half2float(__ushort_as_half((unsigned short)(dd & 0xFFFF))) * (float)rec[4 + j];
-          const float mn = __half2float(__ushort_as_half((unsigned short)(dd >> 16))) * (float)rec[12 + j];
+          float d, mn;
+          if (FMT == GV_W4G) {
+            const uint32_t dd = *reinterpret_cast<const uint32_t*>(p.scales + (long long)n * p.s_ld + (k >> 7) * 4);
+            d = __half2float(__ushort_as_half((unsigned short)(dd & 0xFFFF)));
+            mn = __half2float(__ushort_as_half((unsigned short)(dd >> 16)));
+          } else {
+            const uint8_t* rec = p.scales + (long long)n * p.s_ld + (k >> 8) * 20;
+            const int j = (k & 255) >> 5;
+            const uint32_t dd = *reinterpret_cast<const uint32_t*>(rec);        // d and dmin: records are 4-byte aligned
+            d = __half2float(__ushort_as_half((unsigned short)(dd & 0xFFFF))) * (float)rec[4 + j];
+            mn = __half2float(__ushort_as_half((unsigned short)(dd >> 16))) * (float)rec[12 + j];
+          }
           const uint32_t cw[4] = {c0.x, c0.y, c0.z, c0.w};
 #pragma unroll
           for (int m = 0; m < MT; ++m) {
@@ -423,11 +433,18 @@ __device__ __forceinline__ void row_dot(const uint8_t* crow, const uint8_t* srow
     }
   } else {
     const uint4 c0 = *reinterpret_cast<const uint4*>(crow + g * 16);
-    const uint8_t* rec = srow + (g >> 3) * 20;
-    const int j = g & 7;
-    const uint32_t dd = *reinterpret_cast<const uint32_t*>(rec);
-    const float d = __half2float(__ushort_as_half((unsigned short)(dd & 0xFFFF))) * (float)rec[4 + j];
-    const float mn = __half2float(__ushort_as_half((unsigned short)(dd >> 16))) * (float)rec[12 + j];
+    float d, mn;
+    if (FMT == GV_W4G) {
+      const uint32_t dd = *reinterpret_cast<const uint32_t*>(srow + (g >> 2) * 4);
+      d = __half2float(__ushort_as_half((unsigned short)(dd & 0xFFFF)));
+      mn = __half2float(__ushort_as_half((unsigned short)(dd >> 16)));
+    } else {
+      const uint8_t* rec = srow + (g >> 3) * 20;
+      const int j = g & 7;
+      const uint32_t dd = *reinterpret_cast<const uint32_t*>(rec);
+      d = __half2float(__ushort_as_half((unsigned short)(dd & 0xFFFF))) * (float)rec[4 + j];
+      mn = __half2float(__ushort_as_half((unsigned short)(dd >> 16))) * (float)rec[12 + j];
+    }
     const uint32_t cw[4] = {c0.x, c0.y, c0.z, c0.w};
 #pragma unroll
     for (int m = 0; m < MT; ++m) {
@@ -446,10 +463,10 @@ constexpr int GS_WARPS = 8;                 // consumer warps
 constexpr int GS_THREADS = (GS_WARPS + 1) * 32;
 
 template <int FMT>
-__host__ __device__ constexpr int gs_code_bytes(int vals) { return FMT == GV_W4 ? vals / 2 : vals; }
+__host__ __device__ constexpr int gs_code_bytes(int vals) { return gv_nibbles<FMT>() ? vals / 2 : vals; }
 template <int FMT>
 __host__ __device__ constexpr int gs_scale_bytes(int vals) {
-  return FMT == GV_W8 ? vals / 16 : FMT == GV_W8G16 ? vals / 256 * 18 : vals / 256 * 20;
+  return FMT == GV_W8 ? vals / 16 : FMT == GV_W8G16 ? vals / 256 * 18 : FMT == GV_W4G ? vals / 128 * 4 : vals / 256 * 20;
 }
 
 __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -719,7 +736,7 @@ int launch_gs(const GvParams& p, cudaStream_t st, int* status, bool* taken, bool
   // eight consumer warps are too few once every group of weights meets four or more token rows: there the
   // register form (24 warps per SM) is as fast or faster, except for the 8-bit planes at up to four rows
   // (Q6_K 4096 x 14336 at four rows: 25 us here, 33 us there; Q4_K 28672 x 4096: 46 us here, 32 us there)
-  if (MT > 4 || (MT == 4 && FMT == GV_W4)) return 0;
+  if (MT > 4 || (MT == 4 && gv_nibbles<FMT>())) return 0;
   const long long cb = gs_code_bytes<FMT>(p.K), sb = gs_scale_bytes<FMT>(p.K);
   if (p.c_ld != cb || p.s_ld != sb || (reinterpret_cast<uintptr_t>(p.scales) & 15)) return 0;
   // rows per stage: eight or four when a ring of three such stages fits half of an SM's shared memory (two
@@ -874,9 +891,16 @@ dequant_q_kernel(const uint8_t* __restrict__ codes, long long c_ld, const uint8_
       }
     } else {
       const uint4 c0 = __ldg(reinterpret_cast<const uint4*>(c + (k >> 1)));
-      const uint8_t* rec = s + (k >> 8) * 20;
-      const int j = (k & 255) >> 5;
-      const float d = h2f(rec) * (float)rec[4 + j], mn = h2f(rec + 2) * (float)rec[12 + j];
+      float d, mn;
+      if (FMT == GV_W4G) {
+        d = h2f(s + (k >> 7) * 4);
+        mn = h2f(s + (k >> 7) * 4 + 2);
+      } else {
+        const uint8_t* rec = s + (k >> 8) * 20;
+        const int j = (k & 255) >> 5;
+        d = h2f(rec) * (float)rec[4 + j];
+        mn = h2f(rec + 2) * (float)rec[12 + j];
+      }
       const uint32_t cw[4] = {c0.x, c0.y, c0.z, c0.w};
 #pragma unroll
       for (int q = 0; q < 4; ++q)
@@ -908,7 +932,9 @@ dequant_q_kernel(const uint8_t* __restrict__ codes, long long c_ld, const uint8_
 LK_API int lk_dequant_q(int fmt, const void* codes, long long c_ld, const void* scales, long long s_ld, void* out,
                         long long ldo, int rows, int K, void* stream) {
   if (rows <= 0 || K <= 0) return LKH_OK;
-  if (!codes || !scales || !out || (K & 31) || (ldo & 7) || ((fmt == GV_W8G16 || fmt == GV_W4) && (K & 255))) return LKH_BAD_ARG;
+  if (!codes || !scales || !out || (K & 31) || (ldo & 7) || ((fmt == GV_W8G16 || fmt == GV_W4) && (K & 255)) ||
+      (fmt == GV_W4G && (K & 127)))
+    return LKH_BAD_ARG;
   if ((reinterpret_cast<uintptr_t>(codes) & 15) || (c_ld & 15) || (reinterpret_cast<uintptr_t>(out) & 15)) return LKH_BAD_ARG;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const uint8_t* c = reinterpret_cast<const uint8_t*>(codes);
@@ -921,6 +947,7 @@ LK_API int lk_dequant_q(int fmt, const void* codes, long long c_ld, const void* 
     case GV_W8: lkh::launch_pdl(dequant_q_kernel<GV_W8>, grid, dim3(256), 0, st, c, c_ld, s, s_ld, o, ldo, rows, K); break;
     case GV_W8G16: lkh::launch_pdl(dequant_q_kernel<GV_W8G16>, grid, dim3(256), 0, st, c, c_ld, s, s_ld, o, ldo, rows, K); break;
     case GV_W4: lkh::launch_pdl(dequant_q_kernel<GV_W4>, grid, dim3(256), 0, st, c, c_ld, s, s_ld, o, ldo, rows, K); break;
+    case GV_W4G: lkh::launch_pdl(dequant_q_kernel<GV_W4G>, grid, dim3(256), 0, st, c, c_ld, s, s_ld, o, ldo, rows, K); break;
     default: return LKH_BAD_ARG;
   }
   lkh::count_launch();
@@ -960,6 +987,7 @@ LK_API int lk_gemv_q(int fmt, const void* codes, long long c_ld, const void* sca
   if (M <= 0 || N <= 0) return LKH_OK;
   if (M > 8 || !codes || !scales || !x || !out || (K & 31) || (ldx & 7)) return LKH_BAD_ARG;
   if ((fmt == GV_W8G16 || fmt == GV_W4) && (K & 255)) return LKH_BAD_ARG;
+  if (fmt == GV_W4G && ((K & 127) || (s_ld & 3) || (reinterpret_cast<uintptr_t>(scales) & 3))) return LKH_BAD_ARG;
   if ((reinterpret_cast<uintptr_t>(codes) & 15) || (c_ld & 15) || (reinterpret_cast<uintptr_t>(x) & 15)) return LKH_BAD_ARG;
   GvParams p;
   p.codes = reinterpret_cast<const uint8_t*>(codes);
@@ -997,6 +1025,7 @@ LK_API int lk_gemv_q(int fmt, const void* codes, long long c_ld, const void* sca
     case GV_W8: rc = dispatch_gv<GV_W8>(p, M, st, status); break;
     case GV_W8G16: rc = dispatch_gv<GV_W8G16>(p, M, st, status); break;
     case GV_W4: rc = dispatch_gv<GV_W4>(p, M, st, status); break;
+    case GV_W4G: rc = dispatch_gv<GV_W4G>(p, M, st, status); break;
     default: return LKH_BAD_ARG;
   }
   if (rc) return rc;

@@ -177,17 +177,45 @@ def _fp8_linear(sh: _Shards, stems, rows, device, col: Optional[slice] = None, b
 AWQ_ORDER = (0, 2, 4, 6, 1, 3, 5, 7)     # nibble i of a packed int32 holds output column 8 j + AWQ_ORDER[i]
 
 
+def awq_unpack(t: torch.Tensor) -> torch.Tensor:
+    """int32 [rows, n / 8] -> int32 [rows, n]: eight 4-bit values per word in AWQ's column order."""
+    rows, packed = t.shape
+    out = torch.empty(rows, packed * 8, dtype=torch.int32)
+    t = t.to(torch.int32)
+    for i, col in enumerate(AWQ_ORDER):
+        out[:, col::8] = (t >> (4 * i)) & 0xF
+    return out
+
+
+def awq_planes(sh: "_Shards", stems, rows, device, bias=None) -> Optional[Linear]:
+    """AWQ tensors with groups of 128 kept as 4-bit planes (`ops/quant.py: from_awq`): up to eight token rows run
+    as the dp4a GEMV on the stored codes, more are decoded once per call for the bf16 GEMM.  None when a tensor is
+    not AWQ or its groups are not 128 wide."""
+    from ..ops import quant as Q
+
+    qs, zs, ss = [], [], []
+    for stem, sl in zip(stems, rows):
+        if not sh.has(stem + ".qweight"):
+            return None
+        q = awq_unpack(sh.get(stem + ".qweight").cpu())               # [in, out]
+        z = awq_unpack(sh.get(stem + ".qzeros").cpu())                # [in / g, out]
+        s = sh.get(stem + ".scales").cpu()                            # [in / g, out]
+        if q.shape[0] // z.shape[0] != 128 or q.shape[0] % 128:
+            return None
+        q, z, s = q.t(), z.t(), s.t()                                 # rows = output features
+        if sl is not None:
+            q, z, s = q[sl], z[sl], s[sl]
+        qs.append(q)
+        zs.append(z)
+        ss.append(s)
+    w = Q.from_awq(torch.cat(qs, 0).contiguous(), torch.cat(zs, 0).contiguous(), torch.cat(ss, 0).contiguous(), device)
+    return Linear("gguf", w, bias, w.rows, w.K)
+
+
 def awq_dequant(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
     """AutoAWQ "gemm" tensors -> float weight [out, in]: qweight int32 [in, out / 8], qzeros int32
     [in / g, out / 8], scales f16 [in / g, out]; w = (q - zero) * scale with 4-bit q and zero."""
-    def unpack(t: torch.Tensor) -> torch.Tensor:
-        rows, packed = t.shape
-        out = torch.empty(rows, packed * 8, dtype=torch.int32)
-        t = t.to(torch.int32)
-        for i, col in enumerate(AWQ_ORDER):
-            out[:, col::8] = (t >> (4 * i)) & 0xF
-        return out
-
+    unpack = awq_unpack
     q = unpack(qweight.cpu())
     z = unpack(qzeros.cpu())
     n_in, n_out = q.shape
@@ -198,8 +226,8 @@ def awq_dequant(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.Tenso
 
 def _float_rows(sh: _Shards, stem: str, sl, col=None) -> torch.Tensor:
     if not sh.has(stem + ".weight") and sh.has(stem + ".qweight"):
-        # AWQ int4: expanded here and stored as bf16 (or block-fp8 with requant); this tree has no
-        # kernel that multiplies by AWQ's packed layout directly
+        # AWQ int4 expanded to floats: the path of tensor-parallel shards, of another target format and of
+        # group sizes other than 128 (otherwise `awq_planes` keeps the 4-bit codes)
         w = awq_dequant(sh.get(stem + ".qweight"), sh.get(stem + ".qzeros"), sh.get(stem + ".scales"))
         if sl is not None:
             w = w[sl]
@@ -316,6 +344,10 @@ def load_hf(directory: str, device, *, tp_rank: int = 0, tp_size: int = 1, requa
     res_mul = float(hf.get("residual_multiplier", 1.0) or 1.0) if cfg.arch == "granite" else 1.0
 
     def linear(stems, rows, col=None, bias=None, mul: float = 1.0):
+        if requant is None and tp_size == 1 and col is None and mul == 1.0 and sh.has(stems[0] + ".qweight"):
+            lin = awq_planes(sh, stems, rows, device, bias)
+            if lin is not None:
+                return lin
         fp8 = all(sh.has(s + ".weight") and sh.get(s + ".weight").dtype == torch.float8_e4m3fn for s in stems)
         if fp8 and requant in (None, "fp8_block") and mul == 1.0:
             lin = _fp8_linear(sh, stems, rows, device, col, bias)

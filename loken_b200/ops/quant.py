@@ -25,6 +25,8 @@ from ._lib import GemmArgs, GemvPre, Workspace, check, cuda_lib, ptr, stream
 from .gemm import KIND_BF16, NUM_SMS
 
 AQ_W8, AQ_W8G16, AQ_W4, AQ_MX4 = 1, 2, 3, 4
+AQ_W4G128 = 5         # AWQ: nibbles, per 128 values one f16 scale and one f16 minimum (zero point x scale)
+GEMV_FORMATS = (AQ_W8, AQ_W8G16, AQ_W4, AQ_W4G128)
 MX_NATIVE = True      # MXFP4 on the block-scaled MMA (False: expanded to bf16 by the dequant warps)
 FMT_OF_TYPE = {gguf.Q8_0: AQ_W8, gguf.Q6_K: AQ_W8G16, gguf.Q4_K: AQ_W4, gguf.MXFP4: AQ_MX4}
 TYPE_OF_NAME = {"q8_0": gguf.Q8_0, "q4_k": gguf.Q4_K, "q6_k": gguf.Q6_K, "mxfp4": gguf.MXFP4}
@@ -149,10 +151,27 @@ def scale_weight_(q: QuantWeight, mul: float) -> QuantWeight:
     return q
 
 
+def from_awq(qvals: torch.Tensor, zeros: torch.Tensor, scales: torch.Tensor, device) -> QuantWeight:
+    """AWQ's 4-bit weights as device planes: qvals int [out, in] (0..15), zeros int [out, in / 128], scales
+    [out, in / 128]; w = (q - zero) * scale.  Codes keep their values (two per byte, the even one in the low
+    nibble); a group's record is (scale, zero x scale) in f16, so w = scale * q - minimum as in the K formats."""
+    rows, K = qvals.shape
+    assert K % 128 == 0 and tuple(zeros.shape) == (rows, K // 128) == tuple(scales.shape)
+    codes = _nibble_pack_t(qvals.to(torch.uint8))
+    s16 = scales.half()
+    rec = torch.stack([s16, (zeros.float() * s16.float()).half()], -1).contiguous()        # [rows, K/128, 2] f16
+    return QuantWeight(AQ_W4G128, -1, rows, K, codes.contiguous().to(device),
+                       rec.view(torch.uint8).view(rows, K // 128 * 4).contiguous().to(device))
+
+
 def dequantize_weight(q: QuantWeight) -> torch.Tensor:
     """fp32 [rows, K]: what the kernel multiplies by before its bf16 rounding."""
     rows, K = q.rows, q.K
     c, s = q.codes, q.scales
+    if q.aq_fmt == AQ_W4G128:
+        v = torch.stack([c & 0xF, c >> 4], dim=2).view(rows, K // 128, 128).float()
+        rec = s.view(rows, K // 128, 4).contiguous().view(torch.float16).float()            # [rows, K/128, 2]
+        return (v * rec[:, :, 0:1] - rec[:, :, 1:2]).view(rows, K)
     if q.aq_fmt == AQ_W8:
         d = s.view(torch.float16).float()
         return (c.view(torch.int8).float().view(rows, K // 32, 32) * d[:, :, None]).view(rows, K)
@@ -231,7 +250,7 @@ def embed_gguf(tokens: torch.Tensor, table: QuantWeight, out: Optional[torch.Ten
 
 def gemv_takes(M: int, w, x_stride: int = 0) -> bool:
     """Does a product of M token rows with `w` run as the dp4a GEMV (the form that can take a `GemvFront`)?"""
-    return (isinstance(w, QuantWeight) and 0 < M <= GEMV_MAX_M and w.aq_fmt in (AQ_W8, AQ_W8G16, AQ_W4)
+    return (isinstance(w, QuantWeight) and 0 < M <= GEMV_MAX_M and w.aq_fmt in GEMV_FORMATS
             and x_stride % 8 == 0 and (1 if M == 1 else 2 if M == 2 else 4 if M <= 4 else 8) * w.K * 1.25 <= 200 * 1024)
 
 
@@ -329,8 +348,9 @@ def linear_gguf(x: torch.Tensor, w: QuantWeight, *, bias: Optional[torch.Tensor]
                                    C.byref(front.pack(M)) if front is not None else None,
                                    ptr(Workspace.get(x.device).status), stream()), "lk_gemv_q")
         return out
-    if DEQUANT_ONCE_MIN_M and M >= DEQUANT_ONCE_MIN_M and w.aq_fmt in (AQ_W8, AQ_W8G16, AQ_W4) and K % 8 == 0 \
-            and out.stride(0) % 8 == 0:
+    if w.aq_fmt == AQ_W4G128 or (DEQUANT_ONCE_MIN_M and M >= DEQUANT_ONCE_MIN_M and w.aq_fmt in GEMV_FORMATS
+                                 and K % 8 == 0 and out.stride(0) % 8 == 0):
+        # (the AWQ planes have no dequantising-warp form: beyond the GEMV's eight rows they are always decoded once)
         return _linear_dequant_once(x, w, bias, out, out_fp32)
     wsp = Workspace.get(x.device)
     bn = _pick_bn(M)

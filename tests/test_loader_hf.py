@@ -51,3 +51,44 @@ def test_awq_tensors_expand_to_the_weights_they_encode():
     w = awq_dequant(pack(q), pack(z), s)
     want = ((q - z.repeat_interleave(group, 0)).float() * s.float().repeat_interleave(group, 0)).t()
     assert w.shape == (n_out, n_in) and torch.equal(w, want)
+
+
+def test_awq_tensors_stay_4_bit_planes_on_one_rank():
+    """Groups of 128: the codes keep their values in the plane format of the dp4a GEMV; decoding the planes gives
+    exactly the weights the tensors encode."""
+    from loken_b200.models.loader_hf import AWQ_ORDER, awq_dequant, awq_planes
+    from loken_b200.ops import quant
+
+    g = torch.Generator().manual_seed(7)
+    n_in, n_out = 256, 64
+
+    def pack(t):
+        out = torch.zeros(t.shape[0], t.shape[1] // 8, dtype=torch.int64)
+        for i, col in enumerate(AWQ_ORDER):
+            out |= t[:, col::8].to(torch.int64) << (4 * i)
+        return out.to(torch.int32)
+
+    class Sh:
+        def __init__(self):
+            self.t = {}
+            for stem in ("a", "b"):
+                q = torch.randint(0, 16, (n_in, n_out), generator=g, dtype=torch.int32)
+                z = torch.randint(0, 16, (n_in // 128, n_out), generator=g, dtype=torch.int32)
+                s = (torch.rand(n_in // 128, n_out, generator=g) * 0.02 + 0.001).half()
+                self.t.update({stem + ".qweight": pack(q), stem + ".qzeros": pack(z), stem + ".scales": s})
+
+        def has(self, n):
+            return n in self.t
+
+        def get(self, n):
+            return self.t[n]
+
+    sh = Sh()
+    lin = awq_planes(sh, ["a", "b"], [None, slice(16, 48)], torch.device("cpu"))
+    assert lin.kind == "gguf" and lin.weight.aq_fmt == quant.AQ_W4G128 and (lin.weight.rows, lin.weight.K) == (96, 256)
+    want = torch.cat([awq_dequant(sh.get("a.qweight"), sh.get("a.qzeros"), sh.get("a.scales")),
+                      awq_dequant(sh.get("b.qweight"), sh.get("b.qzeros"), sh.get("b.scales"))[16:48]], 0)
+    got = quant.dequantize_weight(lin.weight)
+    # the minimum is stored as zero x scale in f16: one more rounding than (q - zero) * scale
+    assert (got - want).abs().max().item() <= 2e-3 * want.abs().max().item()
+    assert awq_planes(sh, ["a", "missing"], [None, None], torch.device("cpu")) is None

@@ -221,3 +221,37 @@ def test_decode_size_mixture_layers_run_their_experts_as_gemv_slots(arch, fmt, T
     assert (got[:T].float() - want).abs().max().item() < 5e-2 * scale
     assert (got[:T].float() - plan[:T].float()).abs().max().item() < 5e-2 * scale
     assert (got[T:] == 0).all()
+
+
+@pytest.mark.parametrize("N,K", [(520, 2048), (300, 1280)])
+def test_awq_planes_run_the_gemv_and_the_decode_once_gemm(N, K):
+    """AWQ's 4-bit weights (groups of 128: scale and zero point) as device planes: up to eight token rows on the
+    dp4a GEMV (both forms), more rows decoded once per call for the bf16 GEMM."""
+    from loken_b200.ops import quant
+    from loken_b200.ops._lib import Workspace, cuda_lib
+
+    g = torch.Generator(device=DEV).manual_seed(N)
+    qv = torch.randint(0, 16, (N, K), generator=g, device=DEV, dtype=torch.int32)
+    z = torch.randint(0, 16, (N, K // 128), generator=g, device=DEV, dtype=torch.int32)
+    s = (torch.rand(N, K // 128, generator=g, device=DEV) * 0.02 + 0.001).half()
+    w = quant.from_awq(qv, z, s, DEV)
+    wd = quant.dequantize_weight(w)
+    assert (wd - (qv - z.repeat_interleave(128, 1)).float() * s.float().repeat_interleave(128, 1)).abs().max() < 2e-3
+    x = (torch.randn(300, K, device=DEV) * 0.5).bfloat16()
+    bias = torch.randn(N, device=DEV) * 0.1
+    ref = x.float() @ wd.t() + bias
+    for M in (1, 3, 8):
+        outs = []
+        for ring in (1, 0):
+            try:
+                cuda_lib().lk_gemv_q_stream(ring)
+                outs.append(quant.linear_gguf(x[:M], w, bias=bias))
+            finally:
+                cuda_lib().lk_gemv_q_stream(1)
+        for o in outs:
+            assert rel_err(o, ref[:M]) < 2e-2
+        assert rel_err(outs[0], outs[1]) < 1e-2
+    for M in (20, 300):
+        assert rel_err(quant.linear_gguf(x[:M], w, bias=bias), ref[:M]) < 1e-2
+    torch.cuda.synchronize()
+    assert Workspace.get(torch.device(DEV)).read_status() == 0
