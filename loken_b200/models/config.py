@@ -228,6 +228,10 @@ PRESETS: Dict[str, ModelConfig] = {
     "qwen3-8b": ModelConfig(name="qwen3-8b", arch="qwen3", n_layers=36, hidden=4096, n_q=32, n_kv=8, head_dim=128,
                             intermediate=12288, vocab=151936, rope_theta=1e6, rope_pairing=1, qk_norm=True,
                             rms_eps=1e-6, weight_format="q4_k_m", context_length=40960),
+    "qwen3-30b-a3b": ModelConfig(name="qwen3-30b-a3b", arch="qwen3moe", n_layers=48, hidden=2048, n_q=32, n_kv=4,
+                                 head_dim=128, intermediate=6144, vocab=151936, rope_theta=1e6, rope_pairing=1, qk_norm=True,
+                                 rms_eps=1e-6, n_experts=128, top_k=8, expert_intermediate=768, router="softmax",
+                                 renorm=True, weight_format="q4_k_m", context_length=40960),
     "olmoe-1b-7b": ModelConfig(name="olmoe-1b-7b", arch="olmoe", n_layers=16, hidden=2048, n_q=16, n_kv=16, head_dim=128,
                                intermediate=1024, vocab=50304, rope_theta=10000.0, rope_pairing=1, qk_norm=True,
                                qk_norm_wide=True, rms_eps=1e-5, n_experts=64, top_k=8, expert_intermediate=1024,
