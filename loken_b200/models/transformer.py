@@ -241,6 +241,36 @@ class DecoderModel:
                 and quant.gemv_takes(T, lw.w_down.weight, b.gu.stride(0))
                 and all(l.kind == "gguf" for l in (lw.wqkv, lw.wo, lw.w_gate_up, lw.w_down)))
 
+    def _fused_attn_ok(self, lw, T: int, shard: bool) -> bool:
+        """A mixture layer on one rank whose attention matrices run as quantised GEMVs at this many rows."""
+        if not FUSE_GEMV_FRONT or shard or not self.cfg.is_moe or lw.moe is None or (self.comm is not None and self.comm.size > 1):
+            return False
+        from ..ops import quant
+
+        b = self.buf
+        return (lw.wqkv.kind == "gguf" and lw.wo.kind == "gguf" and quant.gemv_takes(T, lw.wqkv.weight, b.x.stride(0))
+                and quant.gemv_takes(T, lw.wo.weight, b.attn.stride(0)))
+
+    def _layer_fused_attn_moe(self, il: int, inp: StepInputs, T: int, pend: Optional[torch.Tensor]) -> torch.Tensor:
+        """The attention half as in `_layer_fused` (norm in front of the q/k/v GEMV, the pending update folded in by
+        the o-projection GEMV); the feed-forward norm stays a kernel, since the router and the experts both read
+        its rows.  The mixture's output is the update pending on x."""
+        from ..ops import quant
+
+        cfg, b = self.cfg, self.buf
+        lw = self.w.layers[il]
+        F = quant.GemvFront
+        quant.linear_gguf(b.x[:T], lw.wqkv.weight, bias=lw.wqkv.bias, out=b.qkv[:T],
+                          front=F(norm=lw.attn_norm, eps=cfg.rms_eps, delta=pend))
+        self._attention(il, inp, T, False)
+        d1 = b.delta2 if pend is not b.delta2 else b.delta
+        quant.linear_gguf(b.attn[:T], lw.wo.weight, bias=lw.wo.bias, out=d1[:T],
+                          front=F(update=(b.x, pend)) if pend is not None else None)
+        rows.add_rmsnorm(b.x, lw.ffn_norm, cfg.rms_eps, delta=d1, out=b.h, rows=T)
+        out = b.delta if d1 is not b.delta else b.delta2
+        self.moe_runner.forward(il, lw.moe, b.h, out, T)
+        return out
+
     def _layer_fused(self, il: int, inp: StepInputs, T: int, pend: Optional[torch.Tensor]) -> torch.Tensor:
         """One dense layer as four GEMVs, rope + cache write and attention: five kernels fewer than the
         separate form.  Each norm runs in front of its GEMV on (x + the update still pending); the GEMV
@@ -281,6 +311,9 @@ class DecoderModel:
             nvtx.mark(f"layer {il}", level=2)
             if T <= b.delta2.shape[0] and not self._delta_local and self._fused_front_ok(lw, T, shard):
                 delta = self._layer_fused(il, inp, T, delta)
+                continue
+            if T <= b.delta2.shape[0] and not self._delta_local and self._fused_attn_ok(lw, T, shard):
+                delta = self._layer_fused_attn_moe(il, inp, T, delta)
                 continue
             # attention block
             self._norm(b.x, lw.attn_norm, delta, T, lw.wqkv.wants_fp8, shard, local=self._delta_local)

@@ -32,6 +32,9 @@ def _mk(arch, fmt, **kw):
     ("olmoe", "bf16", dict(n_experts=8, top_k=2, expert_intermediate=128, n_q=2, n_kv=2, head_dim=128)),
     # five query heads per kv head: prefill in the eight-slot tile shape, decode on the SIMT kernel
     ("qwen2", "bf16", dict(n_q=10, n_kv=2, head_dim=128, hidden=256)),
+    # quantised mixture layers: decode steps run the attention half with fused fronts and the experts as GEMV slots
+    ("olmoe", "q8_0", dict(n_experts=8, top_k=2, expert_intermediate=256, n_q=4, n_kv=4, head_dim=64)),
+    ("qwen3moe", "q4_k_m", dict(n_experts=8, top_k=2, expert_intermediate=256, n_q=4, n_kv=2, head_dim=128, hidden=512)),
 ])
 def test_prefill_logits_match_oracle(arch, fmt, kw):
     from loken_b200.models.reference import forward_ref
@@ -46,9 +49,14 @@ def test_prefill_logits_match_oracle(arch, fmt, kw):
     eng.add_request(prompt, GREEDY)
     eng.step()
     got = eng.runner.model.buf.logits[0].clone()
+    sid = next(iter(eng.seqs))
     for _ in range(3):
-        eng.step()                                   # decode steps on the same path
+        eng.step()                                   # decode steps: the single-row paths of every family
     assert eng.runner.wsp.read_status() == 0
+    # the logits of the last decode step against the oracle over the prompt plus what was generated before it
+    out_toks = list(eng.seqs[sid].output)
+    ref_dec = forward_ref(w, prompt + out_toks[:-1])[-1]
+    assert _cos(eng.runner.model.buf.logits[0], ref_dec) > (0.985 if fmt in ("fp8_block", "mxfp4") else 0.995)
     # e4m3 activations carry ~3% rounding per element into every product of the fp8 model, and into the
     # expert products of an MXFP4 model (block-scaled MMA: weights as stored, activations e4m3)
     assert _cos(got, ref[-1]) > (0.99 if fmt in ("fp8_block", "mxfp4") else 0.998)
