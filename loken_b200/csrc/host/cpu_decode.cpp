@@ -686,6 +686,209 @@ LKH_API int lkcpu_decode(void* h, int token, int pos, float* logits) {
 LKH_API int lkcpu_level(void* h) { return h ? ((Model*)h)->level : -1; }
 LKH_API int lkcpu_threads(void* h) { return h ? ((Model*)h)->pool->size() : -1; }
 
+// ------------------------------------------------------------------------------ experts on the host
+// (token, expert) pairs of a mixture layer computed on the host cores, over expert matrices held in host memory
+// in the DEVICE plane layouts (ops/quant.py: codes plane + scale-record plane), so the same pinned buffers serve
+// the copy into a GPU slot and this path.  Used for experts that are not resident on the GPU at decode size:
+// computing a pair here reads the expert's bytes once from host memory instead of sending them over the bus
+// (reference: src/inference/moe_cuda_cpu/, the expert tier's "compute misses beside the card").
+//   fmt 0  bf16 rows
+//   fmt 1  Q8_0: int8 codes, one f16 scale per 32 values
+//   fmt 2  Q6_K: int8 codes (centred), per 256 values f16 d + sixteen int8 scales (one per 16 values)
+//   fmt 3  Q4_K: nibbles (value k in byte k / 2, the even one low), per 256 values f16 d, f16 dmin, eight
+//          6-bit scales and eight 6-bit minima as bytes
+// Activations are quantised per 32 values (d = amax / 127); for Q4_K their codes are stored even values first,
+// then odd ones, per group, to line up with the nibbles.
+namespace {
+
+struct PlaneAct {
+  std::vector<int8_t> q;      // [K] (per group of 32: natural order, or evens then odds)
+  std::vector<float> d, sum;  // [K / 32]: scale, and d * sum of the codes
+};
+
+void quant_plane_act(const float* x, int K, bool split, PlaneAct& a) {
+  const int ng = K / 32;
+  a.q.resize(K);
+  a.d.resize(ng);
+  a.sum.resize(ng);
+  for (int g = 0; g < ng; ++g) {
+    float amax = 0.f;
+    for (int j = 0; j < 32; ++j) amax = std::max(amax, fabsf(x[g * 32 + j]));
+    const float d = amax / 127.f, id = d ? 1.f / d : 0.f;
+    int s = 0;
+    for (int j = 0; j < 32; ++j) {
+      const int q = (int)lroundf(x[g * 32 + j] * id);
+      s += q;
+      const int at = split ? ((j & 1) ? 16 + (j >> 1) : (j >> 1)) : j;
+      a.q[g * 32 + at] = (int8_t)q;
+    }
+    a.d[g] = d;
+    a.sum[g] = d * (float)s;
+  }
+}
+
+#if defined(__x86_64__)
+__attribute__((target("avx2"))) static inline int32_t dot32_s8(const int8_t* w, const int8_t* x) {
+  const __m256i a = _mm256_loadu_si256((const __m256i*)w), c = _mm256_loadu_si256((const __m256i*)x);
+  const __m256i p16 = _mm256_maddubs_epi16(_mm256_sign_epi8(a, a), _mm256_sign_epi8(c, a));
+  return hsum_i32(_mm256_madd_epi16(p16, _mm256_set1_epi16(1)));
+}
+__attribute__((target("avx2"))) static inline void dot16x2_s8(const int8_t* w, const int8_t* x, int32_t* lo, int32_t* hi) {
+  const __m256i a = _mm256_loadu_si256((const __m256i*)w), c = _mm256_loadu_si256((const __m256i*)x);
+  const __m256i p32 = _mm256_madd_epi16(_mm256_maddubs_epi16(_mm256_sign_epi8(a, a), _mm256_sign_epi8(c, a)),
+                                        _mm256_set1_epi16(1));
+  __m128i l = _mm256_castsi256_si128(p32), h = _mm256_extracti128_si256(p32, 1);
+  l = _mm_add_epi32(l, _mm_shuffle_epi32(l, 0x4E));
+  l = _mm_add_epi32(l, _mm_shuffle_epi32(l, 0xB1));
+  h = _mm_add_epi32(h, _mm_shuffle_epi32(h, 0x4E));
+  h = _mm_add_epi32(h, _mm_shuffle_epi32(h, 0xB1));
+  *lo = _mm_cvtsi128_si32(l);
+  *hi = _mm_cvtsi128_si32(h);
+}
+// sixteen bytes of nibbles against evens-then-odds activation codes
+__attribute__((target("avx2"))) static inline int32_t dot32_nib(const uint8_t* w, const int8_t* x) {
+  const __m128i b = _mm_loadu_si128((const __m128i*)w);
+  const __m128i m4 = _mm_set1_epi8(0xF);
+  const __m256i q = _mm256_set_m128i(_mm_and_si128(_mm_srli_epi16(b, 4), m4), _mm_and_si128(b, m4));
+  const __m256i c = _mm256_loadu_si256((const __m256i*)x);
+  return hsum_i32(_mm256_madd_epi16(_mm256_maddubs_epi16(q, c), _mm256_set1_epi16(1)));
+}
+#endif
+
+// one row of a plane matrix times a quantised (or, for bf16, float) activation
+float plane_row_dot(int fmt, const uint8_t* codes, const uint8_t* scales, int K, const PlaneAct& a, const float* xf, int level) {
+  const int ng = K / 32;
+  float acc = 0.f;
+  (void)level;
+  if (fmt == 0) {
+    const uint16_t* w = (const uint16_t*)codes;
+    for (int k = 0; k < K; ++k) acc += bf16_to_f32(w[k]) * xf[k];
+    return acc;
+  }
+  if (fmt == 1) {
+    const uint16_t* dw = (const uint16_t*)scales;
+    for (int g = 0; g < ng; ++g) {
+      int32_t s = 0;
+#if defined(__x86_64__)
+      if (level >= 2) s = dot32_s8((const int8_t*)codes + g * 32, a.q.data() + g * 32);
+      else
+#endif
+        for (int j = 0; j < 32; ++j) s += (int32_t)((const int8_t*)codes)[g * 32 + j] * a.q[g * 32 + j];
+      acc += f16_to_f32(dw[g]) * a.d[g] * (float)s;
+    }
+    return acc;
+  }
+  if (fmt == 2) {
+    for (int g = 0; g < ng; ++g) {
+      const uint8_t* rec = scales + (g >> 3) * 18;
+      const float d = f16_to_f32(*(const uint16_t*)rec);
+      const int8_t* sc = (const int8_t*)rec + 2 + (g & 7) * 2;
+      int32_t lo = 0, hi = 0;
+#if defined(__x86_64__)
+      if (level >= 2) dot16x2_s8((const int8_t*)codes + g * 32, a.q.data() + g * 32, &lo, &hi);
+      else
+#endif
+        for (int j = 0; j < 16; ++j) {
+          lo += (int32_t)((const int8_t*)codes)[g * 32 + j] * a.q[g * 32 + j];
+          hi += (int32_t)((const int8_t*)codes)[g * 32 + 16 + j] * a.q[g * 32 + 16 + j];
+        }
+      acc += d * a.d[g] * ((float)sc[0] * (float)lo + (float)sc[1] * (float)hi);
+    }
+    return acc;
+  }
+  // fmt 3
+  for (int g = 0; g < ng; ++g) {
+    const uint8_t* rec = scales + (g >> 3) * 20;
+    const int j = g & 7;
+    const float d = f16_to_f32(*(const uint16_t*)rec) * (float)rec[4 + j];
+    const float mn = f16_to_f32(*(const uint16_t*)(rec + 2)) * (float)rec[12 + j];
+    int32_t s = 0;
+#if defined(__x86_64__)
+    if (level >= 2) s = dot32_nib(codes + g * 16, a.q.data() + g * 32);
+    else
+#endif
+      for (int b = 0; b < 16; ++b) {
+        s += (int32_t)(codes[g * 16 + b] & 0xF) * a.q[g * 32 + b];
+        s += (int32_t)(codes[g * 16 + b] >> 4) * a.q[g * 32 + 16 + b];
+      }
+    acc += d * a.d[g] * (float)s - mn * a.sum[g];
+  }
+  return acc;
+}
+
+size_t plane_code_bytes(int fmt, int K) { return fmt == 0 ? (size_t)K * 2 : fmt == 3 ? (size_t)K / 2 : (size_t)K; }
+size_t plane_scale_bytes(int fmt, int K) {
+  return fmt == 0 ? 0 : fmt == 1 ? (size_t)K / 16 : fmt == 2 ? (size_t)K / 256 * 18 : (size_t)K / 256 * 20;
+}
+
+}  // namespace
+
+// out[t] += w * down_e(glu(gate_up_e(x[t]))) for every pair (t = pair_tok[p], e = pair_expert[p], w = pair_w[p]).
+// gate_up stacks 2I rows per expert (gate rows, then up rows) of width H, down stacks H rows of width I; planes are
+// contiguous.  x and out are f32 [T, H]; biases f32 [E, 2I] / [E, H] or null.  Returns 0, or -1 for a bad argument.
+LKH_API int lkcpu_moe_pairs(int fmt_gu, const void* gu_codes, const void* gu_scales, int fmt_dn, const void* dn_codes,
+                            const void* dn_scales, const float* gu_bias, const float* dn_bias, int H, int I,
+                            const float* x, const int* pair_tok, const int* pair_expert, const float* pair_w, int n_pairs,
+                            int glu_mode, float alpha, float limit, float* out, int threads, int max_level) {
+  if (n_pairs <= 0) return 0;
+  if (!gu_codes || !dn_codes || !x || !out || !pair_tok || !pair_expert || !pair_w || (H % 32) || (I % 32)) return -1;
+  for (int f : {fmt_gu, fmt_dn})
+    if (f < 0 || f > 3 || (f >= 2 && ((f == fmt_gu ? H : I) % 256))) return -1;
+  if ((fmt_gu && !gu_scales) || (fmt_dn && !dn_scales)) return -1;
+  int level = lkc_cpu_level();
+  if (max_level >= 0 && max_level < level) level = max_level;
+  Pool pool(threads);
+  const size_t gcb = plane_code_bytes(fmt_gu, H), gsb = plane_scale_bytes(fmt_gu, H);
+  const size_t dcb = plane_code_bytes(fmt_dn, I), dsb = plane_scale_bytes(fmt_dn, I);
+  std::vector<float> gu((size_t)n_pairs * 2 * I), y((size_t)n_pairs * H);
+  std::vector<PlaneAct> ax(n_pairs), aa(n_pairs);
+  std::vector<std::vector<float>> act(n_pairs);
+  for (int p = 0; p < n_pairs; ++p) quant_plane_act(x + (size_t)pair_tok[p] * H, H, fmt_gu == 3, ax[p]);
+  const int chunk = 64;
+  const int gch = (2 * I + chunk - 1) / chunk;
+  pool.run(n_pairs * gch, [&](int task) {
+    const int p = task / gch, c = task % gch;
+    const size_t e = (size_t)pair_expert[p];
+    const uint8_t* cw = (const uint8_t*)gu_codes + e * 2 * I * gcb;
+    const uint8_t* sw = gu_scales ? (const uint8_t*)gu_scales + e * 2 * I * gsb : nullptr;
+    const float* xf = x + (size_t)pair_tok[p] * H;
+    const int r1 = std::min(2 * I, (c + 1) * chunk);
+    for (int r = c * chunk; r < r1; ++r)
+      gu[(size_t)p * 2 * I + r] = plane_row_dot(fmt_gu, cw + r * gcb, sw ? sw + r * gsb : nullptr, H, ax[p], xf, level) +
+                                  (gu_bias ? gu_bias[e * 2 * I + r] : 0.f);
+  });
+  for (int p = 0; p < n_pairs; ++p) {
+    act[p].resize(I);
+    const float* g = gu.data() + (size_t)p * 2 * I;
+    for (int i = 0; i < I; ++i) {
+      if (glu_mode == 0) {
+        act[p][i] = g[i] / (1.f + expf(-g[i])) * g[I + i];
+      } else {
+        const float gg = std::min(g[i], limit), uu = std::min(std::max(g[I + i], -limit), limit);
+        act[p][i] = gg / (1.f + expf(-alpha * gg)) * (1.f + uu);
+      }
+    }
+    quant_plane_act(act[p].data(), I, fmt_dn == 3, aa[p]);
+  }
+  const int dch = (H + chunk - 1) / chunk;
+  pool.run(n_pairs * dch, [&](int task) {
+    const int p = task / dch, c = task % dch;
+    const size_t e = (size_t)pair_expert[p];
+    const uint8_t* cw = (const uint8_t*)dn_codes + e * H * dcb;
+    const uint8_t* sw = dn_scales ? (const uint8_t*)dn_scales + e * H * dsb : nullptr;
+    const int r1 = std::min(H, (c + 1) * chunk);
+    for (int r = c * chunk; r < r1; ++r)
+      y[(size_t)p * H + r] = plane_row_dot(fmt_dn, cw + r * dcb, sw ? sw + r * dsb : nullptr, I, aa[p], act[p].data(), level) +
+                             (dn_bias ? dn_bias[e * H + r] : 0.f);
+  });
+  for (int p = 0; p < n_pairs; ++p) {          // in pair order: the sum of a token's pairs does not depend on threads
+    float* o = out + (size_t)pair_tok[p] * H;
+    const float w = pair_w[p];
+    for (int r = 0; r < H; ++r) o[r] += w * y[(size_t)p * H + r];
+  }
+  return 0;
+}
+
 // Test hooks: the dot at a forced SIMD level, and a pooled GEMV.
 LKH_API float lkcpu_dot_q8_0(const void* x, const void* y, int nblocks, int level) {
   int have = lkc_cpu_level();

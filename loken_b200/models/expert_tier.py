@@ -10,9 +10,11 @@ than there are slots is processed in rounds, each round accumulating into the ou
 Slot policy, after the reference's expert tier (`src/inference/generic_transformer/expert_tier.rs:1-28`,
 `:97-113`): every expert has a heat that decays (x0.7 every 10 tokens) and grows by its routed
 count; a missing expert that is needed now always gets a slot, evicting the coldest slot that is
-not needed in this round.  The reference additionally computes misses on the host beside the
-card; here the copy over PCIe/NVLink-C2C is always taken, with the next layer's likely experts
-prefetched from this layer's heat table while the current layer computes.
+not needed in this round.  As in the reference, misses of a decode-size step are computed on the host
+cores beside the card (`cpu/moe_host.py`, over the same pinned planes the copies read): a pair's expert is
+read once from host memory instead of crossing the bus, the resident experts' pairs run on the GPU as
+usual, and the hottest missing expert is promoted into the coldest idle slot behind the step.  Larger
+steps take the copies, in rounds.
 """
 from __future__ import annotations
 
@@ -38,6 +40,7 @@ class TierStats:
     misses: int = 0
     rounds: int = 0
     bytes_copied: int = 0
+    host_pairs: int = 0          # (token, expert) pairs computed on the host cores
 
     def hit_rate(self) -> Optional[float]:
         n = self.hits + self.misses
@@ -58,6 +61,13 @@ class TieredLayer:
         self.host_dn = [pin(p) for p in _rows_of(moe.down, 0, self.E * rows_dn)]
         self.host_gub = pin(moe.gate_up_b) if moe.gate_up_b is not None else None
         self.host_dnb = pin(moe.down_b) if moe.down_b is not None else None
+        # the same pinned buffers as stacks the host kernel reads
+        as_w = lambda w, parts: parts[0] if isinstance(w, torch.Tensor) else quant.QuantWeight(
+            w.aq_fmt, w.ggml_type, w.rows, w.K, parts[0], parts[1])
+        self.host_gu_w, self.host_dn_w = as_w(moe.gate_up, self.host_gu), as_w(moe.down, self.host_dn)
+        from ..cpu.moe_host import plane_format
+
+        self.host_ok = plane_format(self.host_gu_w) is not None and plane_format(self.host_dn_w) is not None
 
         def slot_stack(w, rows):
             if isinstance(w, torch.Tensor):
@@ -114,8 +124,13 @@ class TieredMoeRunner(MoeRunner):
     """`MoeRunner` whose expert stacks are slot caches over host memory."""
     plans_on_host = True        # the round plan reads the router's choices on the host: no CUDA-graph capture
 
-    def __init__(self, cfg, weights, cap: int, comm=None, slots: int = 8):
+    HOST_PAIRS_MAX = 64          # up to this many pairs a step's misses are computed on the host; 0: always copy
+
+    def __init__(self, cfg, weights, cap: int, comm=None, slots: int = 8, host_threads: int = 0):
         super().__init__(cfg, weights, cap, comm)
+        import os
+
+        self.host_threads = host_threads or max(1, min(32, (os.cpu_count() or 8) // 2))
         I, H = cfg.expert_intermediate, cfg.hidden
         self.layers: Dict[int, TieredLayer] = {}
         for il, lw in enumerate(weights.layers):
@@ -149,6 +164,9 @@ class TieredMoeRunner(MoeRunner):
             tl.heat[e] += c
         needed = sorted(counts, key=lambda e: -counts[e])
         S = tl.S
+        if self.HOST_PAIRS_MAX and T * cfg.top_k <= self.HOST_PAIRS_MAX and tl.host_ok \
+                and (self.comm is None or self.comm.size == 1):
+            return self._forward_with_host_misses(tl, h, out, T, ids, counts)
         first = True
         for r0 in range(0, len(needed), S):
             chunk = needed[r0:r0 + S]
@@ -183,7 +201,66 @@ class TieredMoeRunner(MoeRunner):
             self.comm.all_reduce(out, T)
         del C
 
+    def _forward_with_host_misses(self, tl: TieredLayer, h: torch.Tensor, out: torch.Tensor, T: int, ids: torch.Tensor,
+                                  counts: Dict[int, int]):
+        """A decode-size step: pairs of resident experts on the GPU (one round, nothing copied for it), pairs of
+        missing experts on the host cores; then the hottest missing expert takes the coldest idle slot."""
+        from ..cpu.moe_host import moe_pairs
+        from ..ops._lib import check, cuda_lib, ptr, stream
+        from .moe import pick_group_bn
+
+        cfg, pl, S = self.cfg, self.plan, tl.S
+        cur = torch.cuda.current_stream(self.device)
+        cur.wait_stream(self.copy_stream)                       # a promotion of an earlier step may still be landing
+        resident = [e for e in counts if e in tl.expert_slot]
+        missing = [e for e in counts if e not in tl.expert_slot]
+        self.stats.hits += len(resident)
+        self.stats.misses += len(missing)
+        if resident:
+            tbl = [S] * tl.E
+            for e in resident:
+                tbl[e] = tl.expert_slot[e]
+            tl.table.copy_(torch.tensor(tbl, dtype=torch.int32), non_blocking=False)
+            torch.index_select(tl.table, 0, pl.ids[:T].flatten().long(), out=self.ids_slot[:T].view(-1))
+            P = T * cfg.top_k
+            pl.bn = pick_group_bn(P, S, not isinstance(tl.dev.gate_up, torch.Tensor))
+            check(cuda_lib().lk_moe_plan(ptr(self.ids_slot), P, S + 1, 0, S, pl.bn, pl.max_tiles, ptr(pl.offsets),
+                                         ptr(pl.pair_row), ptr(pl.tile_expert), ptr(pl.tile_row0), ptr(pl.tile_rows),
+                                         ptr(pl.ntiles), ptr(self.wsp.status), stream()), "lk_moe_plan")
+            self.experts(tl.dev, h, T, out, accumulate=False)
+            self.stats.rounds += 1
+        else:
+            out[:T].zero_()
+        if not missing:
+            return
+        miss = set(missing)
+        wts = pl.wts[:T].cpu()
+        x = h[:T].float().cpu()
+        tok, exp, w = [], [], []
+        for t in range(T):
+            for j in range(cfg.top_k):
+                e = int(ids[t, j])
+                if e in miss:
+                    tok.append(t)
+                    exp.append(e)
+                    w.append(float(wts[t, j]))
+        y = torch.zeros(T, cfg.hidden, dtype=torch.float32)
+        moe_pairs(tl.host_gu_w, tl.host_dn_w, x, tok, exp, w, H=cfg.hidden, I=cfg.expert_intermediate, out=y,
+                  gu_bias=tl.host_gub, dn_bias=tl.host_dnb, glu=(cfg.glu_mode, cfg.glu_alpha, cfg.glu_limit),
+                  threads=self.host_threads)
+        out[:T] += y.to(self.device).to(out.dtype)
+        self.stats.host_pairs += len(tok)
+        # promotion: the hottest missing expert replaces the coldest slot that this step did not use, if it is hotter
+        idle = [s for s in range(S) if tl.slot_expert[s] not in counts]
+        if idle:
+            hot = max(missing, key=lambda e: tl.heat[e])
+            victim = min(idle, key=lambda s: tl.heat[tl.slot_expert[s]])
+            if tl.heat[hot] > tl.heat[tl.slot_expert[victim]]:
+                self.copy_stream.wait_stream(cur)               # the slot may still be read by an earlier launch
+                self.stats.bytes_copied += tl.load(hot, victim, self.copy_stream)
+
     def status(self) -> dict:
         tl = next(iter(self.layers.values()))
         return {"slots": tl.S, "experts": tl.E, "hit_rate": self.stats.hit_rate(), "rounds": self.stats.rounds,
-                "bytes_copied": self.stats.bytes_copied, "expert_bytes": tl.expert_bytes()}
+                "bytes_copied": self.stats.bytes_copied, "expert_bytes": tl.expert_bytes(),
+                "host_pairs": self.stats.host_pairs}
