@@ -19,7 +19,7 @@ import torch
 
 from .engine import _lib
 
-_FMT_OF_AQ = {1: 1, 2: 2, 3: 3}          # ops/quant.py: AQ_W8, AQ_W8G16 (Q6_K), AQ_W4 (Q4_K)
+_FMT_OF_AQ = {1: 1, 2: 2, 3: 3, 4: 4}    # ops/quant.py: AQ_W8, AQ_W8G16 (Q6_K), AQ_W4 (Q4_K), AQ_MX4
 
 
 def plane_format(w) -> Optional[int]:
@@ -27,7 +27,9 @@ def plane_format(w) -> Optional[int]:
     if isinstance(w, torch.Tensor):
         return 0 if w.dtype == torch.bfloat16 and w.is_contiguous() and not w.is_cuda else None
     f = _FMT_OF_AQ.get(getattr(w, "aq_fmt", None))
-    if f is None or w.codes.is_cuda or not w.codes.is_contiguous() or not w.scales.is_contiguous():
+    if f is None or w.codes.is_cuda or not w.codes.is_contiguous() or w.scales.stride(1) != 1:
+        return None
+    if f != 4 and not w.scales.is_contiguous():
         return None
     return f
 
@@ -56,7 +58,8 @@ def moe_pairs(gate_up, down, x: torch.Tensor, pair_tok: Sequence[int], pair_expe
     rc = _lib().lkcpu_moe_pairs(fg, _p(gc), _p(gs), fd, _p(dc), _p(ds), _p(gb), _p(db), H, I, _p(x),
                                 tok.ctypes.data_as(C.c_void_p), exp.ctypes.data_as(C.c_void_p),
                                 wts.ctypes.data_as(C.c_void_p), n, int(glu[0]), C.c_float(glu[1]), C.c_float(glu[2]),
-                                _p(out), threads, max_level)
+                                _p(out), threads, max_level,
+                                C.c_longlong(gs.stride(0) if fg == 4 else 0), C.c_longlong(ds.stride(0) if fd == 4 else 0))
     if rc != 0:
         raise ValueError(f"lkcpu_moe_pairs refused its arguments (rc {rc})")
     del fp

@@ -697,6 +697,8 @@ LKH_API int lkcpu_threads(void* h) { return h ? ((Model*)h)->pool->size() : -1; 
 //   fmt 2  Q6_K: int8 codes (centred), per 256 values f16 d + sixteen int8 scales (one per 16 values)
 //   fmt 3  Q4_K: nibbles (value k in byte k / 2, the even one low), per 256 values f16 d, f16 dmin, eight
 //          6-bit scales and eight 6-bit minima as bytes
+//   fmt 4  MXFP4: E2M1 nibbles in the same order, one E8M0 exponent byte per 32 values (the scale plane's row
+//          pitch is passed: it is padded for the block-scaled MMA)
 // Activations are quantised per 32 values (d = amax / 127); for Q4_K their codes are stored even values first,
 // then odd ones, per group, to line up with the nibbles.
 namespace {
@@ -796,6 +798,18 @@ float plane_row_dot(int fmt, const uint8_t* codes, const uint8_t* scales, int K,
     }
     return acc;
   }
+  if (fmt == 4) {
+    // codes are E2M1 values times two (the LUT of formats.h); 2^(e - 127) / 2 puts them back
+    for (int g = 0; g < ng; ++g) {
+      int32_t s = 0;
+      for (int b = 0; b < 16; ++b) {
+        s += (int32_t)kMxfp4Lut[codes[g * 16 + b] & 0xF] * a.q[g * 32 + b];
+        s += (int32_t)kMxfp4Lut[codes[g * 16 + b] >> 4] * a.q[g * 32 + 16 + b];
+      }
+      acc += 0.5f * e8m0_to_f32(scales[g]) * a.d[g] * (float)s;
+    }
+    return acc;
+  }
   // fmt 3
   for (int g = 0; g < ng; ++g) {
     const uint8_t* rec = scales + (g >> 3) * 20;
@@ -816,9 +830,10 @@ float plane_row_dot(int fmt, const uint8_t* codes, const uint8_t* scales, int K,
   return acc;
 }
 
-size_t plane_code_bytes(int fmt, int K) { return fmt == 0 ? (size_t)K * 2 : fmt == 3 ? (size_t)K / 2 : (size_t)K; }
+size_t plane_code_bytes(int fmt, int K) { return fmt == 0 ? (size_t)K * 2 : fmt >= 3 ? (size_t)K / 2 : (size_t)K; }
 size_t plane_scale_bytes(int fmt, int K) {
-  return fmt == 0 ? 0 : fmt == 1 ? (size_t)K / 16 : fmt == 2 ? (size_t)K / 256 * 18 : (size_t)K / 256 * 20;
+  return fmt == 0 ? 0 : fmt == 1 ? (size_t)K / 16 : fmt == 2 ? (size_t)K / 256 * 18 : fmt == 4 ? (size_t)K / 32
+                                                                                               : (size_t)K / 256 * 20;
 }
 
 }  // namespace
@@ -829,21 +844,22 @@ size_t plane_scale_bytes(int fmt, int K) {
 LKH_API int lkcpu_moe_pairs(int fmt_gu, const void* gu_codes, const void* gu_scales, int fmt_dn, const void* dn_codes,
                             const void* dn_scales, const float* gu_bias, const float* dn_bias, int H, int I,
                             const float* x, const int* pair_tok, const int* pair_expert, const float* pair_w, int n_pairs,
-                            int glu_mode, float alpha, float limit, float* out, int threads, int max_level) {
+                            int glu_mode, float alpha, float limit, float* out, int threads, int max_level,
+                            long long gu_scale_pitch, long long dn_scale_pitch) {
   if (n_pairs <= 0) return 0;
   if (!gu_codes || !dn_codes || !x || !out || !pair_tok || !pair_expert || !pair_w || (H % 32) || (I % 32)) return -1;
-  for (int f : {fmt_gu, fmt_dn})
-    if (f < 0 || f > 3 || (f >= 2 && ((f == fmt_gu ? H : I) % 256))) return -1;
+  if (fmt_gu < 0 || fmt_gu > 4 || fmt_dn < 0 || fmt_dn > 4) return -1;
+  if (((fmt_gu == 2 || fmt_gu == 3) && (H % 256)) || ((fmt_dn == 2 || fmt_dn == 3) && (I % 256))) return -1;
   if ((fmt_gu && !gu_scales) || (fmt_dn && !dn_scales)) return -1;
   int level = lkc_cpu_level();
   if (max_level >= 0 && max_level < level) level = max_level;
   Pool pool(threads);
-  const size_t gcb = plane_code_bytes(fmt_gu, H), gsb = plane_scale_bytes(fmt_gu, H);
-  const size_t dcb = plane_code_bytes(fmt_dn, I), dsb = plane_scale_bytes(fmt_dn, I);
+  const size_t gcb = plane_code_bytes(fmt_gu, H), gsb = gu_scale_pitch > 0 ? (size_t)gu_scale_pitch : plane_scale_bytes(fmt_gu, H);
+  const size_t dcb = plane_code_bytes(fmt_dn, I), dsb = dn_scale_pitch > 0 ? (size_t)dn_scale_pitch : plane_scale_bytes(fmt_dn, I);
   std::vector<float> gu((size_t)n_pairs * 2 * I), y((size_t)n_pairs * H);
   std::vector<PlaneAct> ax(n_pairs), aa(n_pairs);
   std::vector<std::vector<float>> act(n_pairs);
-  for (int p = 0; p < n_pairs; ++p) quant_plane_act(x + (size_t)pair_tok[p] * H, H, fmt_gu == 3, ax[p]);
+  for (int p = 0; p < n_pairs; ++p) quant_plane_act(x + (size_t)pair_tok[p] * H, H, fmt_gu >= 3, ax[p]);
   const int chunk = 64;
   const int gch = (2 * I + chunk - 1) / chunk;
   pool.run(n_pairs * gch, [&](int task) {
@@ -868,7 +884,7 @@ LKH_API int lkcpu_moe_pairs(int fmt_gu, const void* gu_codes, const void* gu_sca
         act[p][i] = gg / (1.f + expf(-alpha * gg)) * (1.f + uu);
       }
     }
-    quant_plane_act(act[p].data(), I, fmt_dn == 3, aa[p]);
+    quant_plane_act(act[p].data(), I, fmt_dn >= 3, aa[p]);
   }
   const int dch = (H + chunk - 1) / chunk;
   pool.run(n_pairs * dch, [&](int task) {

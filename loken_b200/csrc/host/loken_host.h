@@ -65,11 +65,13 @@ LKH_API int lkcpu_threads(void* h);
 LKH_API float lkcpu_dot_q8_0(const void* x, const void* y, int nblocks, int level);
 LKH_API int lkcpu_gemv_q8_0(const void* w, const float* x, float* out, int N, int K, int threads, int level);
 // (token, expert) pairs of a mixture layer on the host cores over expert stacks in the device plane layouts
-// (fmt 0 bf16, 1 Q8_0, 2 Q6_K, 3 Q4_K): out[t] += w * down_e(glu(gate_up_e(x[t]))).
+// (fmt 0 bf16, 1 Q8_0, 2 Q6_K, 3 Q4_K, 4 MXFP4; scale pitches in bytes, 0 = the format's own row size):
+// out[t] += w * down_e(glu(gate_up_e(x[t]))).
 LKH_API int lkcpu_moe_pairs(int fmt_gu, const void* gu_codes, const void* gu_scales, int fmt_dn, const void* dn_codes,
                             const void* dn_scales, const float* gu_bias, const float* dn_bias, int H, int I,
                             const float* x, const int* pair_tok, const int* pair_expert, const float* pair_w, int n_pairs,
-                            int glu_mode, float alpha, float limit, float* out, int threads, int max_level);
+                            int glu_mode, float alpha, float limit, float* out, int threads, int max_level,
+                            long long gu_scale_pitch, long long dn_scale_pitch);
 LKH_API int lkcpu_gemv_any(int type, const void* w, const float* x, float* out, int N, int K, int threads, int level);
 
 // ---- wire codec (wire.cpp) ----
