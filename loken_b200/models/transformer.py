@@ -233,6 +233,8 @@ class DecoderModel:
         and the residual adds then ride inside those GEMVs (ops/quant.py: GemvFront)."""
         if not FUSE_GEMV_FRONT or shard or self.cfg.is_moe or lw.w_gate_up is None:
             return False
+        if self.comm is not None and self.comm.size > 1:
+            return False                # row-parallel layers are summed over the ranks between the GEMVs
         from ..ops import quant
 
         b = self.buf
