@@ -418,6 +418,22 @@ def ops_router(ctx: ServerContext):
             raise ApiError(400, f"cannot start the segment: {e}")
         return {"status": "started", "port": srv.addr[1], "host": srv.addr[0], **run.status()}
 
+    @r.post("/api/cluster/plan")
+    async def cluster_plan(req: Request):
+        """Where to cut a layer stack over nodes (`cluster/cut_plan.py: plan_from_request` documents the body).
+        Nodes that are not named take their link prices from what this node has measured about its peers.
+        409 when no arrangement fits: the caller picks fewer layers, another format or one node."""
+        from ..cluster.cut_plan import plan_from_request
+
+        body = await req.json()
+        try:
+            plan = plan_from_request(body)
+        except (ValueError, KeyError, TypeError) as e:
+            raise ApiError(400, f"cannot plan: {e}")
+        if plan is None:
+            raise ApiError(409, "no arrangement of these layers fits these nodes over these links")
+        return plan.to_json()
+
     @r.post("/api/swap")
     async def swap(req: Request):
         """Replace the resident model: the named one (or every resident language model when none is

@@ -152,6 +152,8 @@ def build_parser() -> argparse.ArgumentParser:
     ca.add_argument("-t", "--text", required=True, nargs="+", help="text files to calibrate on, read here and sent")
     ca.add_argument("--excerpt", type=int, help="characters taken from each text")
     ca.add_argument("--tokens", type=int, help="tokens in all")
+    pc = sub.add_parser("plan-cut", help="where to cut a layer stack over nodes; computed here, no server needed")
+    pc.add_argument("spec", help="a JSON file: layers, layer_bytes, nodes, links, objective (see cluster/cut_plan.py)")
     dh = sub.add_parser("draft-head")
     dh.add_argument("source", help="a checkpoint directory (safetensors) or a GGUF file that carries mtp.* tensors")
     dh.add_argument("output", help="OUT.gguf, or a directory for a safetensors companion")
@@ -306,6 +308,21 @@ def main(argv=None, out=sys.stdout) -> int:
             last = ev
             p(json.dumps(ev))
         return 0 if last is not None and "error" not in last else 1
+    elif args.cmd == "plan-cut":
+        from ..cluster.cut_plan import plan_from_request
+
+        try:
+            with open(args.spec) as f:
+                plan = plan_from_request(json.load(f))
+        except (ValueError, KeyError, TypeError, OSError) as e:
+            p(f"loken plan-cut: {e}")
+            return 2
+        if plan is None:
+            p("loken plan-cut: no arrangement of these layers fits these nodes over these links")
+            return 1
+        for sgm in plan.segments:
+            p(f"{sgm.node:20s} layers {sgm.lo:3d} .. {sgm.hi - 1:3d}  ({len(sgm)})")
+        p(f"crossings {plan.crossing_ms:.3f} ms per token, objective {plan.total_ms:.3f}" + ("" if plan.exact else "  (fixed node order: not exact)"))
     elif args.cmd == "draft-head":
         try:
             p(json.dumps(extract_draft_head(args.source, args.output), indent=1))

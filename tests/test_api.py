@@ -177,6 +177,12 @@ def test_auth_rate_limit_and_ops():
     assert len(alloc.evictable) == 0 and len(alloc.free_list) == 100
     assert c2.get("/api/cluster/state").json()["self_state"]["free_kv_blocks"] == 100
     assert c2.get("/api/inflight").json()["requests"] == []
+    spec = {"layers": 8, "layer_bytes": "1G", "nodes": [{"id": "a", "bytes": "5G"}, {"id": "b", "bytes": "5G"}],
+            "links": [{"from": "a", "to": "b", "ms": 0.7}]}
+    plan = c2.post("/api/cluster/plan", json=spec).json()
+    assert [s["to"] - s["from"] for s in plan["segments"]] in ([4, 4], [3, 5], [5, 3]) and plan["crossing_ms"] == 0.7
+    assert c2.post("/api/cluster/plan", json=dict(spec, layers=20)).status_code == 409
+    assert c2.post("/api/cluster/plan", json={"nodes": []}).status_code == 400
     assert c2.get("/api/stage_perf").json() == {"stages": []}
 
 
