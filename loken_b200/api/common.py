@@ -199,6 +199,7 @@ def params_from_openai(body: dict, llm: LLM, chat: bool) -> GenerationParams:
         cache_salt=body.get("cache_salt"),
         context_shift=bool(body.get("context_shift", False)),
         num_keep=max(0, int(body.get("num_keep", 1))),
+        resume_position=int(body.get("resume_position") or 0),
     )
     if p.max_tokens is not None:
         p.max_tokens = int(p.max_tokens)

@@ -37,6 +37,12 @@ class ServerSettings:
     gate_queue: int = 1024
     prefill_peer: Optional[str] = None      # base URL of a node that reads long prompts for this one
     prefill_peer_min_tokens: int = 512
+    # requests go to the peer that is predicted to finish them sooner (cluster/routing.py, cluster/forward.py);
+    # an answer a peer left unfinished is continued here only when both nodes hold the same bytes, unless
+    # `resume_unverified` allows it anyway
+    route_requests: bool = False
+    resume_unverified: bool = False
+    node_id: Optional[str] = None
 
 
 class ServerContext:
@@ -56,6 +62,32 @@ class ServerContext:
         self.fetch_prefill = _fetch_prefill      # replaceable (tests, another transport)
         self.catalogue = None                    # store.catalogue.Catalogue when model stores are configured
         self.opener = None                       # transport of pulls (store.download.Opener); None = requests
+        from ..cluster.routing import RateMeter
+
+        self.rate = RateMeter()                  # this node's decode rate, published by the gossip
+        self.membership = None
+        self.router = None                       # cluster.routing.Router once a membership exists and routing is on
+        self.open_peer_stream = None             # transport of forwarded requests; None = HTTP (cluster/forward.py)
+
+    def _route(self, llm: LLM, ids, params: GenerationParams):
+        """The peer that should answer this request, or None for this node."""
+        if not self.settings.route_requests or self.membership is None:
+            return None
+        from ..cluster import forward
+        from ..cluster.routing import Router
+
+        if not forward.forwardable(ids, params):
+            return None
+        if self.router is None or self.router.m is not self.membership:
+            self.router = Router(self.membership)
+        expected = int(params.max_tokens or 256)
+        load = float(len(llm.worker.tickets))
+        try:
+            c = self.router.choose(llm.model_id, expected, load, self.rate.rate, local_serves=True,
+                                   conversation=params.cache_salt)
+        except LookupError:
+            return None
+        return c if c.addr is not None else None
 
     def _prefill_on_peer(self, llm: LLM, ids: List[int], params: GenerationParams) -> bool:
         """Disaggregated prefill: a long prompt is read by the configured peer and its cache imported
@@ -95,9 +127,21 @@ class ServerContext:
         n_out = 0
         reason = None
         self.inflight[request_id] = {"model": llm.model_id, "prompt_tokens": len(ids), "started": time.time()}
+        peer = None
         try:
-            peered = self._prefill_on_peer(llm, ids, params)
-            ticket = llm.submit(ids, params)
+            peer = self._route(llm, ids, params)
+            if peer is not None:
+                from ..cluster import forward
+
+                peered = True
+                self.metrics.count("requests_forwarded")
+                kw = {"open_stream": self.open_peer_stream} if self.open_peer_stream is not None else {}
+                ticket = forward.RemoteTicket(llm, ids, params, peer.addr, on_peer_failed=lambda _a, n=peer.node_id: self._peer_failed(n),
+                                              resume_unverified=self.settings.resume_unverified,
+                                              timeout_s=self.settings.request_timeout_s, **kw)
+            else:
+                peered = self._prefill_on_peer(llm, ids, params)
+                ticket = llm.submit(ids, params)
             for ev in llm.events_of(ticket, params, self.settings.request_timeout_s):
                 if first is None and ev.token_ids:
                     first = time.perf_counter() - t0
@@ -109,5 +153,12 @@ class ServerContext:
         finally:
             self.gate.release(started)
             self.inflight.pop(request_id, None)
-            self.metrics.observe_request(llm.model_id, len(ids), n_out, first, time.perf_counter() - t0,
-                                         reason or "disconnect")
+            total = time.perf_counter() - t0
+            if peer is None and first is not None and n_out > 1:
+                self.rate.observe(n_out - 1, total - first)         # decode rate of this node: tokens after the first
+            self.metrics.observe_request(llm.model_id, len(ids), n_out, first, total, reason or "disconnect")
+
+    def _peer_failed(self, node_id: str):
+        self.metrics.count("requests_taken_back")
+        if self.router is not None:
+            self.router.failed(node_id)

@@ -88,7 +88,7 @@ def ops_router(ctx: ServerContext):
         models = ctx.registry.list()
         free = sum(m.engine.alloc.free_blocks() for m in models)
         return {"models": [m.model_id for m in models], "load": float(sum(len(m.worker.tickets) for m in models)),
-                "tok_per_s": 0.0, "free_kv_blocks": int(free)}
+                "tok_per_s": float(ctx.rate.rate), "free_kv_blocks": int(free)}
 
     def _membership():
         if getattr(ctx, "membership", None) is None:
@@ -96,7 +96,7 @@ def ops_router(ctx: ServerContext):
 
             from ..cluster.membership import Membership
 
-            ctx.membership = Membership(getattr(ctx.settings, "node_id", None) or socket.gethostname())
+            ctx.membership = Membership(ctx.settings.node_id or socket.gethostname())
         return ctx.membership
 
     ctx.describe = _describe
@@ -417,6 +417,26 @@ def ops_router(ctx: ServerContext):
         except (ValueError, FileNotFoundError, KeyError) as e:
             raise ApiError(400, f"cannot start the segment: {e}")
         return {"status": "started", "port": srv.addr[1], "host": srv.addr[0], **run.status()}
+
+    @r.post("/api/cluster/generate")
+    async def cluster_generate(req: Request):
+        """Tokens for a peer that keeps the text layer of the request: the engine's step outputs as JSON lines
+        (`cluster/forward.py`).  Never forwarded again: this route submits to this node's engine."""
+        from fastapi.responses import StreamingResponse
+
+        from ..cluster import forward
+
+        body = await req.json()
+        llm = ctx.registry.get(body.get("model"))
+        try:
+            ids = [int(t) for t in body["prompt"]]
+            params = forward.params_from_wire(body.get("params") or {})
+        except (KeyError, TypeError, ValueError) as e:
+            raise ApiError(400, f"bad forwarded request: {e}")
+        if not ids or len(ids) >= llm.engine.max_ctx:
+            raise ApiError(400, "the forwarded prompt is empty or longer than the context window")
+        gen = forward.serve_raw(llm, ids, params, node_id=_membership().self_id, timeout_s=ctx.settings.request_timeout_s)
+        return StreamingResponse(gen, media_type="application/x-ndjson")
 
     @r.post("/api/cluster/plan")
     async def cluster_plan(req: Request):

@@ -120,7 +120,9 @@ def serve(cfg, requant=None) -> int:
                                    allowed_origins=s.allowed_origins, rate_limit_rps=s.rate_limit_rps,
                                    rate_limit_burst=s.rate_limit_burst, max_body_bytes=s.max_body_mb << 20,
                                    request_timeout_s=s.request_timeout_s, gate_slots=i.max_seqs,
-                                   prefill_peer=i.prefill_peer), cluster=cfg.cluster, catalogue=catalogue)
+                                   prefill_peer=i.prefill_peer, route_requests=cfg.cluster.route_requests,
+                                   resume_unverified=cfg.cluster.resume_unverified, node_id=cfg.cluster.node_id),
+          cluster=cfg.cluster, catalogue=catalogue)
     return 0
 
 

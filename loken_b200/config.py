@@ -9,7 +9,7 @@ the reference derives from measurement and a B200 node wants stated):
                  (reference | balanced | fast), kv_format, max_seqs, max_ctx, max_prefill_tokens,
                  kv_disk_dir, prefill_peer, draft_model, draft_k, lora, models_dir, expert_slots
     [energy]     enabled, grid_g_co2_per_kwh
-    [cluster]    node_id, listen, peers, heartbeat_ms, suspect_phi, name, discovery
+    [cluster]    node_id, listen, peers, heartbeat_ms, suspect_phi, name, discovery, route_requests, resume_unverified
 
 Keys that older files carry and that no longer mean anything load fine and are reported
 (`config.rs:134`); unknown keys are reported as well, never fatal.  `LOKEN_API_KEY` adds an API key,
@@ -90,6 +90,8 @@ class ClusterSection:
     suspect_phi: float = 8.0
     name: str = "loken"         # discovery ignores announcements that name another cluster
     discovery: bool = False     # announce on, and listen to, the multicast group (cluster/discovery.py)
+    route_requests: bool = False     # a request goes to the peer predicted to finish it sooner (cluster/forward.py)
+    resume_unverified: bool = False  # continue an answer a peer left unfinished although its weights are not known to be the same
 
 
 @dataclass

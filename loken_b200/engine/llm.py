@@ -265,6 +265,21 @@ class LLM:
         self.worker = EngineWorker(engine)
         self.worker.start()
         self.requests_served = 0
+        self._digest: Optional[str] = None
+
+    @property
+    def weights_digest(self) -> str:
+        """What identifies the bytes this model runs on, for a peer that wants to continue one of its answers
+        (`serve/replay.py`): a fingerprint of the file or checkpoint directory, computed on first use; empty
+        when nothing is known (then no other node may resume this node's answers, nor this node theirs)."""
+        if self._digest is None:
+            from ..serve.replay import path_fingerprint
+
+            try:
+                self._digest = path_fingerprint(self.path) if self.path else ""
+            except OSError:
+                self._digest = ""
+        return self._digest
 
     # ---- construction ----
     @classmethod
@@ -354,6 +369,7 @@ class LLM:
         eng = LLMEngine(cfg, device=dev, seed=seed, tp_rank=tp_rank, tp_size=tp_size, comm=comm, **engine_kw)
         llm = cls(wrap(eng), ByteTokenizer(cfg.vocab), model_id or model, {"general.architecture": cfg.arch})
         llm.control_group, llm.watchdog = group, watchdog
+        llm._digest = f"init:{model}:{cfg.weight_format}:{cfg.n_layers}:{seed}"      # random weights are a function of these
         return llm
 
     def close(self):
@@ -409,6 +425,10 @@ class LLM:
         return t
 
     def abort(self, ticket: _Ticket):
+        cancel = getattr(ticket, "cancel", None)       # a request a peer is answering (`cluster/forward.py`)
+        if cancel is not None:
+            cancel()
+            return
         self.worker.abort(ticket)
 
     def on_engine_thread(self, fn, timeout_s: float = 120.0):

@@ -51,6 +51,9 @@ class SamplingParams:
     # (the cache is shifted and its keys re-phased) instead of ending with "length"
     context_shift: bool = False
     num_keep: int = 1
+    # a generation resumed on another node: how many of its tokens were already sampled (they arrive as part of
+    # the prompt); the draw for token N depends on (seed, N) alone, so the stream continues where it stopped
+    resume_position: int = 0
 
     @property
     def greedy(self) -> bool:
@@ -77,13 +80,17 @@ class SamplingParams:
             raise ParamError("min_p must be in [0, 1)")
         if self.repeat_penalty <= 0:
             raise ParamError("repeat_penalty must be > 0")
+        if self.resume_position < 0:
+            raise ParamError("resume_position must be >= 0")
         return self
 
-    def rng(self, seq_index: int = 0) -> random.Random:
-        """One generator per request: a seeded request is reproducible, an unseeded one gets a
-        fresh seed."""
+    def rng(self, seq_index: int = 0):
+        """One generator per request: a seeded request is reproducible, an unseeded one gets a fresh seed.
+        The uniform for a token is a function of (seed, its index in the output) only (`serve/replay.py`)."""
+        from .replay import PositionRng, _mix
+
         seed = self.seed if self.seed is not None else random.SystemRandom().getrandbits(63)
-        return random.Random(seed + seq_index)
+        return PositionRng(seed if seq_index == 0 else _mix(seed, 0, seq_index), self.resume_position)
 
 
 def openai_penalty(frequency: Optional[float], presence: Optional[float], repetition: Optional[float] = None,

@@ -42,6 +42,7 @@ class FakeEngine:
         self.fail_steps = fail_steps
         self.step_delay = step_delay
         self.prompts: List[List[int]] = []
+        self.params_seen: list = []
         self.embeds: list = []
 
     def add_request(self, prompt, params: Optional[SamplingParams] = None, salt: int = 0) -> int:
@@ -52,6 +53,7 @@ class FakeEngine:
         self.next_id += 1
         self.seqs[sid] = FakeSeq(sid, prompt, params, list(self.reply.encode()) + [257])
         self.prompts.append(list(prompt))
+        self.params_seen.append(params)
         self.embeds.append(getattr(prompt, "embeds", None))
         return sid
 
@@ -95,7 +97,9 @@ class FakeEngine:
         for s in list(self.seqs.values()):
             if s.state != "running":
                 continue
-            tok = s.reply[len(s.output)]
+            # a resumed request continues the script where its first part stopped
+            at = getattr(s.params, "resume_position", 0) + len(s.output)
+            tok = s.reply[min(at, len(s.reply) - 1)]
             s.output.append(tok)
             o = StepOutput(s.seq_id, [tok])
             if s.params.logprobs:
@@ -104,7 +108,7 @@ class FakeEngine:
                 o.finished, o.finish_reason = True, "stop"
             elif s.params.max_tokens is not None and len(s.output) >= s.params.max_tokens:
                 o.finished, o.finish_reason = True, "length"
-            elif len(s.output) >= len(s.reply):
+            elif at + 1 >= len(s.reply):
                 o.finished, o.finish_reason = True, "length"
             if o.finished:
                 s.state = "finished"
