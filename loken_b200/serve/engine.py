@@ -73,7 +73,8 @@ class LLMEngine:
                  block_size: int = 16, max_seqs: int = 256, max_prefill_tokens: int = 8192, max_ctx: int = 8192,
                  kv_memory_fraction: float = 0.85, seed: int = 0, eos_token_ids: Optional[List[int]] = None,
                  use_graphs: bool = True, enable_prefix_cache: bool = True, moe_runner_factory=None,
-                 lookahead: int = 0, pipeline=None):
+                 lookahead: int = 0, pipeline=None, kv_disk_dir: Optional[str] = None, kv_disk_host_mb: int = 256,
+                 kv_disk_max_gb: float = 0.0):
         self.cfg = get_config(model) if isinstance(model, str) else model
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         if weights is None:
@@ -119,6 +120,18 @@ class LLMEngine:
         self.next_id = 0
         self.stats = EngineStats()
         self.spec = None            # a serve.speculative.Speculator while a drafter is attached
+        # the cache's disk tier: finished sequences leave their full 256-token blocks, new prompts find them
+        # (one engine, one cache: under tensor parallelism every rank holds a shard and the tier stays off)
+        self.disk = None
+        if kv_disk_dir and tp_size == 1 and pipeline is None:
+            from .kv_disk import KvDiskTier
+            from .kv_persist import DiskPersistence
+
+            tier = KvDiskTier(kv_disk_dir, compress=False, max_bytes=int(kv_disk_max_gb * (1 << 30)) or None,
+                              host_bytes=int(kv_disk_host_mb) << 20)
+            self.disk = DiskPersistence(self.runner, self.alloc, tier)
+            self.sched.on_finish = lambda seq, n: (self.disk.save(seq.seq_id, seq.tokens, n, seq.salt)
+                                                   if getattr(seq, "prompt_embeds", None) is None and seq.shifts == 0 else 0)
         self.grammar_factory = None  # callable((kind, source)) -> session; set by whoever owns the tokenizer
 
     # ---- requests ----
@@ -158,6 +171,8 @@ class LLMEngine:
             seq.grammar = self.grammar_factory(params.grammar)
         self.seqs[sid] = seq
         self.rngs[sid] = params.rng(0)
+        if self.disk is not None and embeds is None:
+            self.disk.restore(seq.tokens, salt)       # rows this prompt left on disk in an earlier life join the prefix cache
         self.sched.add_request(seq)
         return sid
 

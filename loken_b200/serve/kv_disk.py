@@ -48,12 +48,21 @@ def unpack_container(blob: bytes) -> bytes:
 
 
 class KvDiskTier:
-    def __init__(self, directory: str, compress: bool = False, max_bytes: Optional[int] = None):
+    """`host_bytes` > 0 keeps the most recently written or read block files in host memory as well
+    (`serve/kv_tiers.py`: a host tier in front of the directory, written through, every block verified
+    against its digest when it comes back), so a conversation that returns soon is restored without a read."""
+
+    def __init__(self, directory: str, compress: bool = False, max_bytes: Optional[int] = None, host_bytes: int = 0):
         self.dir = directory
         self.compress = compress
         self.max_bytes = max_bytes
         os.makedirs(os.path.join(directory, "blocks"), exist_ok=True)
         os.makedirs(os.path.join(directory, "manifests"), exist_ok=True)
+        self.tiers = None
+        if host_bytes > 0:
+            from .kv_tiers import DirStore, Tier, TieredKv
+
+            self.tiers = TieredKv({Tier.DISK: DirStore(os.path.join(directory, "blocks"), ".kv")}, host_bytes, write_through=True)
 
     def _block_path(self, h: int) -> str:
         return os.path.join(self.dir, "blocks", f"{h:016x}.kv")
@@ -74,10 +83,14 @@ class KvDiskTier:
             planes = read_block(b * DISK_BLOCK, (b + 1) * DISK_BLOCK)
             head = json.dumps([[list(p.shape), str(p.dtype)] for p in planes]).encode()
             body = struct.pack("<I", len(head)) + head + b"".join(np.ascontiguousarray(p).tobytes() for p in planes)
-            tmp = self._block_path(h) + ".tmp"
-            with open(tmp, "wb") as f:
-                f.write(pack_container(body, self.compress))
-            os.replace(tmp, self._block_path(h))
+            blob = pack_container(body, self.compress)
+            if self.tiers is not None:
+                self.tiers.admit(h, blob)           # host memory and, written through, the block file
+            else:
+                tmp = self._block_path(h) + ".tmp"
+                with open(tmp, "wb") as f:
+                    f.write(blob)
+                os.replace(tmp, self._block_path(h))
             written += 1
         man = {"key": key, "tokens": [int(t) for t in tokens[:len(hashes) * DISK_BLOCK]], "salt": salt,
                "blocks": [f"{h:016x}" for h in hashes]}
@@ -105,9 +118,12 @@ class KvDiskTier:
             if not self.has_block(h):
                 break
             try:
-                with open(self._block_path(h), "rb") as f:
-                    body = unpack_container(f.read())
-            except (ValueError, OSError, zlib.error):
+                if self.tiers is not None:
+                    body = unpack_container(self.tiers.promote(h))
+                else:
+                    with open(self._block_path(h), "rb") as f:
+                        body = unpack_container(f.read())
+            except (ValueError, OSError, zlib.error, KeyError, RuntimeError):
                 break
             (hl,) = struct.unpack_from("<I", body)
             desc = json.loads(body[4:4 + hl])

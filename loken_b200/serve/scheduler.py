@@ -98,6 +98,7 @@ class Scheduler:
         self.max_running = max_running
         self.max_prefill_tokens = max_prefill_tokens
         self.lookahead = lookahead          # extra slots a decode needs per step (speculative rows)
+        self.on_finish = None               # callable(seq, cached positions), run before a finished sequence's blocks are freed
         self.waiting: Deque[Sequence] = deque()
         self.running: List[Sequence] = []   # admission order: oldest first
         self.finished: List[Sequence] = []
@@ -219,6 +220,8 @@ class Scheduler:
             n = min(seq.computed, seq.total_len)
             self.alloc.seqs[seq.seq_id].length = min(self.alloc.seqs[seq.seq_id].length, max(n, 0))
             self.alloc.commit_prefix(seq.seq_id, seq.tokens[:n], seq.salt)
+            if self.on_finish is not None and n > 0:
+                self.on_finish(seq, n)          # the cache's disk tier reads the rows while the blocks are still owned
             self.alloc.free(seq.seq_id)
         self.finished.append(seq)
 

@@ -202,6 +202,28 @@ def test_beam_search_over_the_engine():
 
 
 
+def test_disk_tier_restores_a_returning_prompt_after_a_restart(tmp_path):
+    """A finished request leaves its full 256-token blocks in the directory; a new engine over the same directory
+    starts the same prompt from them and decodes the same tokens."""
+    from loken_b200.serve.engine import LLMEngine
+    from loken_b200.serve.params import SamplingParams
+
+    cfg, w = _mk("llama", "bf16")
+    mk = lambda **kw: LLMEngine(cfg, weights=w, num_blocks=128, max_seqs=4, max_prefill_tokens=1024, max_ctx=1024, **kw)
+    g = torch.Generator().manual_seed(9)
+    prompt = torch.randint(0, cfg.vocab, (600,), generator=g).tolist()
+    sp = SamplingParams(temperature=0.0, top_k=0, top_p=1.0, max_tokens=6, ignore_eos=True)
+    a = mk(kv_disk_dir=str(tmp_path))
+    first = a.generate([prompt], sp)[0]
+    assert first.cached_tokens == 0 and a.disk.saved_blocks == 2
+    b = mk(kv_disk_dir=str(tmp_path))                                     # "restart": an empty device cache
+    again = b.generate([prompt], sp)[0]
+    assert again.cached_tokens == 512 and b.disk.restored_tokens == 512
+    assert again.output == first.output
+    assert mk().generate([prompt], sp)[0].output == first.output          # and the same as an engine without the tier
+    assert b.alloc.free_blocks() == 128
+
+
 def test_kv_handover_between_two_engines():
     """Engine A reads the prompt and exports its cache; engine B imports it, finds the prompt in its
     prefix cache and decodes the tokens B would have produced on its own."""
