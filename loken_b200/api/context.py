@@ -65,6 +65,7 @@ class ServerContext:
         from ..cluster.routing import RateMeter
 
         self.rate = RateMeter()                  # this node's decode rate, published by the gossip
+        self.layer_cost = {}                     # model -> what a layer costs here (POST /api/cluster/measure), published too
         self.membership = None
         self.router = None                       # cluster.routing.Router once a membership exists and routing is on
         self.open_peer_stream = None             # transport of forwarded requests; None = HTTP (cluster/forward.py)

@@ -270,11 +270,23 @@ def router(ctx: ServerContext) -> APIRouter:
         # a new name for a loaded model; sampling defaults of a Modelfile are not stored
         body = await req.json()
         name, base = body.get("model") or body.get("name"), body.get("from")
-        if not name or not base:
-            raise ApiError(400, "model and from are required")
-        if body.get("files") or body.get("adapters"):
-            raise ApiError(400, "creating a model from uploaded blobs is not supported; load the file with POST /load")
+        if not name or not (base or body.get("files")):
+            raise ApiError(400, "model, and from (a model here) or files (uploaded blobs), are required")
+        if body.get("adapters"):
+            raise ApiError(400, "adapters are merged at load (POST /load with lora); a model is not created from them")
         cat = _catalogue()
+        files = body.get("files") or {}
+        if files:
+            # a model from a blob uploaded through /api/blobs: `files` maps a file name to its digest
+            if cat is None:
+                raise ApiError(400, "no model store is configured to build a model in")
+            ggufs = [(fn, dg) for fn, dg in files.items() if str(fn).endswith(".gguf")] or list(files.items())
+            bp = _find_blob(cat, str(ggufs[0][1]))
+            if bp is None:
+                raise ApiError(400, f"blob {ggufs[0][1]} was not uploaded (HEAD /api/blobs/<digest> says so)")
+            cat.ollama.create(name, bp, template=body.get("template"), system=body.get("system"),
+                              params=body.get("parameters") or None, license=body.get("license"))
+            return {"status": "success"}
         src = cat.resolve(base) if cat is not None else None
         if src is not None and src.source in ("ollama", "gguf"):
             # a new manifest over the same weights blob, with its own template / system prompt / parameters
@@ -284,6 +296,68 @@ def router(ctx: ServerContext) -> APIRouter:
             return {"status": "success"}
         ctx.registry.alias(base, name)
         return {"status": "success"}
+
+    def _find_blob(cat, digest: str):
+        import os
+
+        from ..store.catalogue import blob_path
+
+        for store in cat.ollama.dirs:
+            bp = blob_path(store, digest)
+            if os.path.exists(bp):
+                return bp
+        return None
+
+    def _check_digest(digest: str) -> str:
+        import re
+
+        if not re.fullmatch(r"sha256:[0-9a-f]{64}", digest or ""):
+            raise ApiError(400, "a blob is named sha256:<64 hex digits>")
+        return digest
+
+    @r.head("/api/blobs/{digest}")
+    async def blob_head(digest: str):
+        """200 when the blob is in a store, 404 when it has to be uploaded."""
+        from fastapi import Response
+
+        cat = _catalogue()
+        found = cat is not None and _find_blob(cat, _check_digest(digest)) is not None
+        return Response(status_code=200 if found else 404)
+
+    @r.post("/api/blobs/{digest}")
+    async def blob_post(digest: str, req: Request):
+        """Uploads a blob: streamed to a partial file in the first store, hashed as it arrives, kept only when
+        the hash is the name it was sent under.  201 when stored, 200 when it was there already."""
+        import hashlib
+        import os
+
+        from fastapi import Response
+
+        from ..store.catalogue import blob_path
+
+        cat = _catalogue()
+        if cat is None or not cat.ollama.dirs:
+            raise ApiError(400, "no model store is configured to keep blobs in")
+        _check_digest(digest)
+        if _find_blob(cat, digest) is not None:
+            return Response(status_code=200)
+        store = cat.ollama.dirs[0]
+        os.makedirs(os.path.join(store, "blobs"), exist_ok=True)
+        bp = blob_path(store, digest)
+        tmp = bp + f".upload-{os.getpid()}"
+        h = hashlib.sha256()
+        try:
+            with open(tmp, "wb") as f:
+                async for chunk in req.stream():
+                    h.update(chunk)
+                    f.write(chunk)
+            if "sha256:" + h.hexdigest() != digest:
+                raise ApiError(400, "the uploaded bytes do not have the digest they were sent under")
+            os.replace(tmp, bp)
+        finally:
+            if os.path.exists(tmp):
+                os.remove(tmp)
+        return Response(status_code=201)
 
     @r.post("/api/pull")
     async def pull(req: Request):

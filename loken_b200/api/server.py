@@ -88,7 +88,18 @@ def ops_router(ctx: ServerContext):
         models = ctx.registry.list()
         free = sum(m.engine.alloc.free_blocks() for m in models)
         return {"models": [m.model_id for m in models], "load": float(sum(len(m.worker.tickets) for m in models)),
-                "tok_per_s": float(ctx.rate.rate), "free_kv_blocks": int(free)}
+                "tok_per_s": float(ctx.rate.rate), "free_kv_blocks": int(free), "layer_cost": dict(ctx.layer_cost),
+                "card_bytes_free": int(_card_bytes_free())}
+
+    def _card_bytes_free() -> int:
+        try:
+            import torch
+
+            if not torch.cuda.is_available():
+                return 0
+            return int(sum(torch.cuda.mem_get_info(i)[0] for i in range(torch.cuda.device_count())))
+        except Exception:
+            return 0
 
     def _membership():
         if getattr(ctx, "membership", None) is None:
@@ -117,6 +128,155 @@ def ops_router(ctx: ServerContext):
         d = _describe()
         return m.gossip_payload(f"http://{ctx.settings.host}:{ctx.settings.port}", d["models"], d["load"],
                                 d["tok_per_s"], d["free_kv_blocks"])
+
+    @r.get("/api/cluster/peers")
+    async def cluster_peers():
+        """Who this node sees (`docs/CLUSTER.md:44` of the reference): `clustered` and one record per peer."""
+        m = _membership()
+        st = m.state()
+        me = {"node_id": m.self_id, "endpoint": f"http://{ctx.settings.host}:{ctx.settings.port}", "alive": True, "phi": 0.0,
+              "rtt_ms": 0.0, "is_self": True, "state": _describe()}
+        peers = [{"node_id": p["id"], "endpoint": p["addr"], "alive": p["alive"] and not p["excluded"], "phi": p["phi"],
+                  "rtt_ms": p["rtt_ms"], "is_self": False,
+                  "state": {k: p[k] for k in ("models", "load", "tok_per_s", "layer_cost", "card_bytes_free")}} for p in st["peers"]]
+        return {"clustered": bool(peers), "peers": [me] + peers}
+
+    @r.post("/api/cluster/prefix")
+    async def cluster_prefix(req: Request):
+        """How much of a prompt this node already holds in its prefix cache.  Only this node can answer: it
+        tokenises for its own model and looks in its own cache.  A model that is not resident answers 0."""
+        body = await req.json()
+        name = body.get("model")
+        if name and name not in ctx.registry.models and name not in ctx.registry.aliases:
+            return {"cached_tokens": 0}          # by its exact name: the default model's cache says nothing about another model
+        try:
+            llm = ctx.registry.get(name)
+        except ApiError:
+            return {"cached_tokens": 0}
+        prompt = body.get("prompt", "")
+        ids = [int(t) for t in prompt] if isinstance(prompt, list) else llm.tokenize(str(prompt))
+        if not ids:
+            return {"cached_tokens": 0}
+        salt = 0
+        if body.get("cache_salt"):
+            from ..engine.llm import GenerationParams
+
+            salt = llm._salt(GenerationParams(cache_salt=str(body["cache_salt"])))
+        alloc = llm.engine.alloc
+        return {"cached_tokens": len(alloc.match_prefix(ids, salt)[0]) * alloc.block_size, "prompt_tokens": len(ids)}
+
+    @r.post("/api/cluster/measure")
+    async def cluster_measure(req: Request):
+        """What a layer of `model` costs on this node, measured now and published with the next gossip round:
+        `card_ms` (one decode row through one layer on the device), `host_ms` (0: this build runs no layer of a
+        device-resident model on the host) and `card_bytes` (one layer's weights and its share of the cache).  A
+        head that plans a pipeline cut asks it of a peer that has no figure for the model yet."""
+        from starlette.concurrency import run_in_threadpool
+
+        body = await req.json()
+        llm = ctx.registry.get(body.get("model"))
+        rows = await run_in_threadpool(llm.on_engine_thread, lambda eng: eng.layer_perf(1))
+        per_layer = [float(r["ms"]) for r in rows if str(r.get("stage", "")).startswith("layer")]
+        if not per_layer:
+            raise ApiError(500, "the engine reported no per-layer times")
+        cfg = llm.cfg
+        bits = {"bf16": 16.0, "fp8": 8.25, "q8_0": 8.5, "q6_k": 6.5625, "q4_k": 4.5, "q4_k_m": 4.85, "mxfp4": 4.25}.get(cfg.weight_format, 16.0)
+        from ..cluster.cut_plan import layer_bytes_of
+
+        cost = {"card_ms": sum(per_layer) / len(per_layer), "host_ms": 0.0,
+                "card_bytes": int(layer_bytes_of(cfg, weight_bits=bits, kv_tokens=int(body.get("context", 0)))[0]),
+                "layers": cfg.n_layers}
+        ctx.layer_cost[llm.model_id] = cost
+        return cost
+
+    @r.get("/api/multi-device/status")
+    async def multi_device_status():
+        """How each resident model is spread over devices: parallel degrees, this rank's device, cache blocks."""
+        out = []
+        for m in ctx.registry.list():
+            eng = getattr(m.engine, "_e", m.engine)
+            w = getattr(eng, "weights", None)
+            out.append({"model": m.model_id, "device": str(getattr(eng, "device", "cpu")),
+                        "tp": int(getattr(w, "tp_size", 1) or 1), "tp_rank": int(getattr(w, "tp_rank", 0) or 0),
+                        "ep": int(getattr(w, "ep_size", 1) or 1), "layers": m.cfg.n_layers,
+                        "layer_range": list(getattr(w, "layer_range", None) or (0, m.cfg.n_layers)),
+                        "kv_blocks": int(eng.alloc.num_blocks), "kv_blocks_free": int(eng.alloc.free_blocks()),
+                        "kv_block_tokens": int(eng.alloc.block_size),
+                        "disk_tier": eng.disk.stats() if getattr(eng, "disk", None) is not None else None})
+        return {"models": out}
+
+    @r.get("/api/distributed/stats")
+    async def distributed_stats():
+        from ..place.devices import list_devices
+
+        devs = list_devices(nvml=getattr(ctx, "nvml", None))
+        return {"devices": len(devs), "memory_total": sum(d.get("memory_total") or 0 for d in devs),
+                "memory_free": sum(d.get("memory_free") or 0 for d in devs), "models": [m.model_id for m in ctx.registry.list()],
+                "node": _membership().self_id, "peers_alive": len(_membership().alive())}
+
+    @r.get("/api/distributed/recommend")
+    async def distributed_recommend():
+        """The largest model of the stores that fits what is free on this node's devices (weights plus a tenth
+        for cache and workspaces)."""
+        from ..place.devices import list_devices
+
+        free = sum(d.get("memory_free") or 0 for d in list_devices(nvml=getattr(ctx, "nvml", None)))
+        best = None
+        if ctx.catalogue is not None:
+            for e in ctx.catalogue.list():
+                need = int(e.size * 1.1)
+                if need <= free and (best is None or e.size > best.size):
+                    best = e
+        return {"memory_free": free, "model": best.name if best else None, "size": int(best.size) if best else 0}
+
+    @r.post("/api/models/validate")
+    async def models_validate(req: Request):
+        """Checks a model's file: tensor table, payload sizes, required metadata (`loken validate`)."""
+        from ..cli.loken import validate_gguf
+
+        body = await req.json()
+        path = _model_file(body)
+        try:
+            return validate_gguf(path)
+        except (OSError, ValueError) as e:
+            raise ApiError(400, f"cannot read {path}: {e}")
+
+    @r.post("/api/models/repair")
+    async def models_repair(req: Request):
+        """Validates, and fetches the model again from where its store entry came from when the file is damaged
+        (nothing can be rebuilt from a damaged file itself)."""
+        from ..cli.loken import validate_gguf
+
+        body = await req.json()
+        path = _model_file(body)
+        try:
+            rep = validate_gguf(path)
+        except (OSError, ValueError) as e:
+            rep = {"file": path, "ok": False, "problems": [str(e)]}
+        rep["repaired"] = False
+        if not rep["ok"]:
+            rep["action"] = f"fetch it again: POST /api/pull {{\"model\": \"{body.get('model', '')}\"}}"
+        return rep
+
+    def _model_file(body: dict) -> str:
+        import os
+
+        name = body.get("path") or body.get("model")
+        if not name:
+            raise ApiError(400, "model (a name in the stores) or path is required")
+        if os.path.exists(str(name)):
+            return str(name)
+        if ctx.catalogue is not None:
+            e = ctx.catalogue.find(str(name))
+            if e is not None and e.path:
+                return e.path
+        try:
+            m = ctx.registry.get(str(name))
+            if m.path:
+                return m.path
+        except ApiError:
+            pass
+        raise ApiError(404, f"no file is known for {name}")
 
     @r.get("/api/distributed/devices")
     async def devices():
@@ -438,6 +598,31 @@ def ops_router(ctx: ServerContext):
         gen = forward.serve_raw(llm, ids, params, node_id=_membership().self_id, timeout_s=ctx.settings.request_timeout_s)
         return StreamingResponse(gen, media_type="application/x-ndjson")
 
+    def _plan_inputs(body: dict) -> dict:
+        """A plan over this node and the peers it sees, from what each measured and published for `model`
+        (`POST /api/cluster/measure`): a layer's time and bytes, the room on the cards, the timed round trips."""
+        model = str(body["model"])
+        mine = ctx.layer_cost.get(model)
+        if mine is None:
+            raise ApiError(409, f"this node has no layer cost for {model}: POST /api/cluster/measure first")
+        m = _membership()
+        nodes = [{"id": m.self_id, "bytes": body.get("self_bytes", _card_bytes_free()), "layer_ms": mine["card_ms"],
+                  "host_ms": mine.get("host_ms", 0.0)}]
+        links = []
+        for p in m.alive():
+            c = p.layer_cost.get(model)
+            if c is None or p.rtt_ms is None:
+                continue          # a peer that has not measured the model, or was never timed, takes no layers
+            nodes.append({"id": p.node_id, "bytes": p.card_bytes_free, "layer_ms": c["card_ms"], "host_ms": c.get("host_ms", 0.0)})
+            links.append({"from": m.self_id, "to": p.node_id, "ms": p.rtt_ms / 2.0})
+        mine_links = list(links)
+        for i, a in enumerate(mine_links):
+            for b in mine_links[i + 1:]:
+                # two peers were never timed against each other from here: priced as the way through this node
+                links.append({"from": a["to"], "to": b["to"], "ms": a["ms"] + b["ms"]})
+        return dict(body, nodes=nodes, links=links, layers=int(mine.get("layers", 0)), layer_bytes=int(mine["card_bytes"]),
+                    objective=body.get("objective", "time"), first=m.self_id)
+
     @r.post("/api/cluster/plan")
     async def cluster_plan(req: Request):
         """Where to cut a layer stack over nodes (`cluster/cut_plan.py: plan_from_request` documents the body).
@@ -446,6 +631,8 @@ def ops_router(ctx: ServerContext):
         from ..cluster.cut_plan import plan_from_request
 
         body = await req.json()
+        if not body.get("nodes") and body.get("model"):
+            body = _plan_inputs(body)
         try:
             plan = plan_from_request(body)
         except (ValueError, KeyError, TypeError) as e:
@@ -534,7 +721,8 @@ def create_app(registry: ModelRegistry, settings: Optional[ServerSettings] = Non
         rid = request.headers.get("x-request-id") or new_request_id()
         try:
             cl = request.headers.get("content-length")
-            if cl and int(cl) > ctx.settings.max_body_bytes:
+            # a model blob is streamed to disk, never held in memory: the body limit is for JSON bodies
+            if cl and int(cl) > ctx.settings.max_body_bytes and not path.startswith("/api/blobs/"):
                 raise ApiError(413, f"request body is limited to {ctx.settings.max_body_bytes} bytes")
             key = None
             if path not in OPEN_PATHS and request.method != "OPTIONS":

@@ -361,13 +361,13 @@ def layer_bytes_of(cfg, weight_bits: float = 16.0, kv_tokens: int = 0, kv_bytes_
     """Bytes of each layer of a decoder described by `cfg` (weights at `weight_bits` per value, plus the cache
     of `kv_tokens` positions), for planning before any file is read."""
     hd = cfg.head_dim
-    attn = cfg.hidden * (cfg.n_heads + 2 * cfg.n_kv_heads) * hd + cfg.n_heads * hd * cfg.hidden
-    if getattr(cfg, "is_moe", False):
-        ffn = cfg.n_experts * 3 * cfg.hidden * cfg.ffn_dim + cfg.hidden * cfg.n_experts
+    attn = cfg.hidden * (cfg.n_q + 2 * cfg.n_kv) * hd + cfg.n_q * hd * cfg.hidden
+    if cfg.n_experts > 0:
+        ffn = cfg.n_experts * 3 * cfg.hidden * cfg.expert_intermediate + cfg.hidden * cfg.n_experts
     else:
-        ffn = 3 * cfg.hidden * cfg.ffn_dim
+        ffn = 3 * cfg.hidden * cfg.intermediate
     w = int((attn + ffn) * weight_bits / 8) + 2 * cfg.hidden * 2
-    kv = int(2 * cfg.n_kv_heads * hd * kv_tokens * kv_bytes_per_value)
+    kv = int(2 * cfg.n_kv * hd * kv_tokens * kv_bytes_per_value)
     return [w + kv] * cfg.n_layers
 
 

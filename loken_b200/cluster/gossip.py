@@ -9,6 +9,7 @@ its phi-accrual detector simply stops getting heartbeats and `Membership.alive` 
 from __future__ import annotations
 
 import threading
+import time
 from typing import Callable, Dict, List, Optional
 
 from .membership import Membership
@@ -27,7 +28,8 @@ def fold(m: Membership, payload: dict):
     nodes it names are learnt (address only: they have to be heard from themselves to count)."""
     m.observe(payload["id"], payload.get("addr", ""), models=payload.get("models"), load=payload.get("load"),
               tok_per_s=payload.get("tok_per_s"), free_kv_blocks=payload.get("free_kv_blocks"),
-              incarnation=int(payload.get("incarnation", 0)))
+              incarnation=int(payload.get("incarnation", 0)), layer_cost=payload.get("layer_cost"),
+              card_bytes_free=payload.get("card_bytes_free"))
     return [k for k in payload.get("known", []) if k.get("id") not in m.peers and k.get("id") != m.self_id]
 
 
@@ -44,21 +46,25 @@ class GossipLoop:
     def payload(self) -> dict:
         d = self.describe()
         return self.m.gossip_payload(self.self_addr, d.get("models", []), d.get("load", 0.0), d.get("tok_per_s", 0.0),
-                                     d.get("free_kv_blocks", 0))
+                                     d.get("free_kv_blocks", 0), d.get("layer_cost"), d.get("card_bytes_free", 0))
 
     def round(self):
         """One gossip round: every known address is told our state and asked for its own."""
         mine = self.payload()
         for addr in list(self.addrs):
+            t0 = time.perf_counter()
             try:
                 theirs = self.post(addr.rstrip("/") + "/api/cluster/gossip", mine, max(self.interval_s, 0.2))
             except Exception:
                 self.failures[addr] = self.failures.get(addr, 0) + 1
                 continue
+            rtt = (time.perf_counter() - t0) * 1e3
             self.failures[addr] = 0
             for k in fold(self.m, theirs):
                 if k.get("addr"):
                     self.addrs.setdefault(k["addr"], k["addr"])
+            if theirs.get("id"):
+                self.m.timed(theirs["id"], rtt)
         self.m.tick()
 
     def start(self):

@@ -63,6 +63,9 @@ class Peer:
     incarnation: int = 0
     detector: PhiAccrual = None
     excluded_until_round: int = -1
+    rtt_ms: Optional[float] = None     # round trip of this node's gossip call to the peer (smoothed)
+    layer_cost: Dict[str, dict] = field(default_factory=dict)   # model -> {card_ms, host_ms, card_bytes} as the peer measured it
+    card_bytes_free: int = 0           # device memory the peer could give to weights
 
 
 class Membership:
@@ -74,7 +77,7 @@ class Membership:
         self.round = 0
 
     def observe(self, node_id: str, addr: str, *, models=None, load=None, tok_per_s=None, free_kv_blocks=None,
-                incarnation: int = 0):
+                incarnation: int = 0, layer_cost=None, card_bytes_free=None):
         """A heartbeat / gossip entry about `node_id` arrived."""
         if node_id == self.self_id:
             return
@@ -92,7 +95,17 @@ class Membership:
             p.tok_per_s = float(tok_per_s)
         if free_kv_blocks is not None:
             p.free_kv_blocks = int(free_kv_blocks)
+        if isinstance(layer_cost, dict):
+            p.layer_cost = {str(k): dict(v) for k, v in layer_cost.items() if isinstance(v, dict)}
+        if card_bytes_free is not None:
+            p.card_bytes_free = int(card_bytes_free)
         p.detector.heartbeat()
+
+    def timed(self, node_id: str, rtt_ms: float, alpha: float = 0.3):
+        """A call to `node_id` took this long: the smoothed figure prices links (`cluster/cut_plan.py`)."""
+        p = self.peers.get(node_id)
+        if p is not None and rtt_ms >= 0:
+            p.rtt_ms = rtt_ms if p.rtt_ms is None else p.rtt_ms + alpha * (rtt_ms - p.rtt_ms)
 
     def tick(self):
         """One gossip round passed."""
@@ -109,10 +122,12 @@ class Membership:
     def state(self) -> dict:
         return {"self": self.self_id, "round": self.round, "peers": [
             {"id": p.node_id, "addr": p.addr, "models": p.models, "load": p.load, "tok_per_s": p.tok_per_s,
-             "phi": round(p.detector.phi(), 3), "alive": p.detector.available(),
+             "phi": round(p.detector.phi(), 3), "alive": p.detector.available(), "rtt_ms": p.rtt_ms,
+             "layer_cost": p.layer_cost, "card_bytes_free": p.card_bytes_free,
              "excluded": p.excluded_until_round >= self.round} for p in self.peers.values()]}
 
-    def gossip_payload(self, self_addr: str, models, load, tok_per_s, free_kv_blocks) -> dict:
+    def gossip_payload(self, self_addr: str, models, load, tok_per_s, free_kv_blocks, layer_cost=None,
+                       card_bytes_free: int = 0) -> dict:
         return {"id": self.self_id, "addr": self_addr, "models": list(models), "load": load, "tok_per_s": tok_per_s,
-                "free_kv_blocks": free_kv_blocks,
+                "free_kv_blocks": free_kv_blocks, "layer_cost": layer_cost or {}, "card_bytes_free": int(card_bytes_free),
                 "known": [{"id": p.node_id, "addr": p.addr, "incarnation": p.incarnation} for p in self.alive()]}

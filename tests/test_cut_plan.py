@@ -139,7 +139,9 @@ def test_residency_cut():
 def test_inputs_from_the_cluster():
     from types import SimpleNamespace as NS
 
-    cfg = NS(head_dim=128, hidden=4096, n_heads=32, n_kv_heads=8, ffn_dim=14336, n_layers=32, is_moe=False, n_experts=0)
+    from loken_b200.models.config import get_config
+
+    cfg = get_config("llama-3.1-8b")
     lb = layer_bytes_of(cfg, weight_bits=4.5, kv_tokens=4096)
     assert len(lb) == 32 and 100e6 < lb[0] < 200e6
     peers = [NS(node_id="p1", rtt_ms=0.4, link_gbps=12.5), NS(node_id="p2", rtt_ms=2.0, link_gbps=1.0), NS(node_id="p3", rtt_ms=None, link_gbps=None)]
