@@ -132,13 +132,22 @@ def config_from_hf(cfg: dict, name: str = "hf") -> ModelConfig:
 
 
 class _Shards:
+    """The tensors of a checkpoint directory by name: safetensors shards, or (older repositories)
+    `pytorch_model*.bin` files read without unpickling code (`formats/pth.py`)."""
+
     def __init__(self, directory: str):
         from safetensors import safe_open
 
         self.files = sorted(glob.glob(os.path.join(directory, "*.safetensors")))
-        if not self.files:
-            raise FileNotFoundError(f"no .safetensors files in {directory}")
-        self.handles = [safe_open(f, framework="pt", device="cpu") for f in self.files]
+        if self.files:
+            self.handles = [safe_open(f, framework="pt", device="cpu") for f in self.files]
+        else:
+            from ..formats.pth import PthReader
+
+            self.files = sorted(glob.glob(os.path.join(directory, "pytorch_model*.bin")))
+            if not self.files:
+                raise FileNotFoundError(f"no .safetensors or pytorch_model*.bin files in {directory}")
+            self.handles = [PthReader(f) for f in self.files]
         self.where: Dict[str, int] = {}
         for i, h in enumerate(self.handles):
             for k in h.keys():
