@@ -160,6 +160,69 @@ class _Shards:
         return self.handles[self.where[name]].get_tensor(name)
 
 
+def config_from_native_params(p: dict) -> dict:
+    """A vendor's own release (`params.json` beside `consolidated*.safetensors`) as the configuration dict the
+    library layout carries: the text model is the llama family's (reference: `src/inference/load/awq_loader.rs:246-321`).
+    A `yarn` block becomes the rope block (`beta` / `alpha` are the fast / slow betas)."""
+    for k in ("dim", "n_layers", "n_heads", "hidden_dim", "vocab_size"):
+        if k not in p:
+            raise ValueError(f"params.json: missing {k}")
+    hf = {"architectures": ["MistralForCausalLM"], "model_type": "mistral", "hidden_size": int(p["dim"]),
+          "num_hidden_layers": int(p["n_layers"]), "num_attention_heads": int(p["n_heads"]),
+          "num_key_value_heads": int(p.get("n_kv_heads") or p["n_heads"]), "intermediate_size": int(p["hidden_dim"]),
+          "vocab_size": int(p["vocab_size"]), "rope_theta": float(p.get("rope_theta", 10000.0)),
+          "rms_norm_eps": float(p.get("norm_eps", 1e-5)), "tie_word_embeddings": bool(p.get("tied_embeddings", False)),
+          "max_position_embeddings": int(p.get("max_seq_len") or p.get("max_position_embeddings") or 32768)}
+    if p.get("head_dim"):
+        hf["head_dim"] = int(p["head_dim"])
+    if p.get("sliding_window"):
+        hf["sliding_window"] = int(p["sliding_window"])
+    y = p.get("yarn")
+    if isinstance(y, dict):
+        hf["rope_parameters"] = {"rope_type": "yarn", "rope_theta": hf["rope_theta"], "factor": float(y.get("factor", 1.0)),
+                                 "original_max_position_embeddings": int(y.get("original_max_position_embeddings", 8192)),
+                                 "beta_fast": float(y.get("beta", 32.0)), "beta_slow": float(y.get("alpha", 1.0)), "mscale": 1.0,
+                                 "mscale_all_dim": 0.0 if y.get("apply_scale") else 1.0}
+    return hf
+
+
+_NATIVE_NAMES = (("model.embed_tokens.", "tok_embeddings."), ("model.norm.", "norm."), ("lm_head.", "output."),
+                 (".self_attn.q_proj.", ".attention.wq."), (".self_attn.k_proj.", ".attention.wk."),
+                 (".self_attn.v_proj.", ".attention.wv."), (".self_attn.o_proj.", ".attention.wo."),
+                 (".mlp.gate_proj.", ".feed_forward.w1."), (".mlp.up_proj.", ".feed_forward.w3."),
+                 (".mlp.down_proj.", ".feed_forward.w2."), (".input_layernorm.", ".attention_norm."),
+                 (".post_attention_layernorm.", ".ffn_norm."), ("model.layers.", "layers."))
+
+
+class _NativeShards(_Shards):
+    """`consolidated*.safetensors` under the names the rest of the loader asks for."""
+
+    def __init__(self, directory: str):
+        from safetensors import safe_open
+
+        self.files = sorted(glob.glob(os.path.join(directory, "consolidated*.safetensors")))
+        if not self.files:
+            raise FileNotFoundError(f"params.json without consolidated*.safetensors in {directory}")
+        self.handles = [safe_open(f, framework="pt", device="cpu") for f in self.files]
+        self.where = {}
+        for i, h in enumerate(self.handles):
+            for k in h.keys():
+                self.where[k] = i
+
+    @staticmethod
+    def _native(name: str) -> str:
+        for lib, nat in _NATIVE_NAMES:
+            name = name.replace(lib, nat)
+        return name
+
+    def has(self, name: str) -> bool:
+        return self._native(name) in self.where
+
+    def get(self, name: str) -> torch.Tensor:
+        n = self._native(name)
+        return self.handles[self.where[n]].get_tensor(n)
+
+
 def _fp8_linear(sh: _Shards, stems, rows, device, col: Optional[slice] = None, bias=None) -> Optional[Linear]:
     """Stacks row slices of block-fp8 tensors; None when a slice does not fall on tile boundaries."""
     datas, scales = [], []
@@ -322,14 +385,21 @@ def load_hf(directory: str, device, *, tp_rank: int = 0, tp_size: int = 1, requa
             kv_format: Optional[str] = None):
     """-> (ModelWeights, hf config dict).  Under tensor parallelism a mixture model's experts are split
     over the same ranks (expert-parallel degree = tensor-parallel degree)."""
-    with open(os.path.join(directory, "config.json")) as f:
-        hf = json.load(f)
+    native = not os.path.exists(os.path.join(directory, "config.json")) and os.path.exists(os.path.join(directory, "params.json"))
+    if native:
+        with open(os.path.join(directory, "params.json")) as f:
+            hf = config_from_native_params(json.load(f))
+    else:
+        with open(os.path.join(directory, "config.json")) as f:
+            hf = json.load(f)
     cfg = config_from_hf(hf, os.path.basename(os.path.normpath(directory)))
+    if native:
+        cfg.rope_pairing = 0        # the vendor's own files keep q / k rows in adjacent-pair order
     if kv_format:
         cfg.kv_format = kv_format
     if requant and not cfg.is_moe:
         cfg.weight_format = requant
-    sh = _Shards(directory)
+    sh = _NativeShards(directory) if native else _Shards(directory)
     hd, H = cfg.head_dim, cfg.hidden
     nql = cfg.n_q // tp_size
     nkvl = max(1, cfg.n_kv // tp_size)

@@ -102,3 +102,58 @@ def test_logits_match_transformers(tmp_path, family):
     top2 = want.topk(2, dim=1).values
     clear = (top2[:, 0] - top2[:, 1]) > 0.05 * want.abs().amax(1)
     assert torch.equal(got.argmax(1)[clear], want.argmax(1)[clear])
+
+
+def test_native_vendor_layout_matches_transformers(tmp_path):
+    """`params.json` + `consolidated.safetensors` (the vendor's own release: q / k rows in adjacent-pair order,
+    its own tensor names) gives the logits of the same model in the library layout."""
+    import json
+
+    from safetensors.torch import save_file
+
+    from loken_b200.models import loader_hf
+    from loken_b200.models.reference import forward_ref
+
+    torch.manual_seed(5)
+    hc, cls = _tiny("Mistral")
+    model = cls(hc).float().eval()
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.dim() >= 2:
+                p.normal_(0.0, 0.08)
+    sd = model.state_dict()
+    hd = hc.hidden_size // hc.num_attention_heads
+
+    def unpermute(w, heads):      # the library's half-split row order back to adjacent pairs
+        return w.view(heads, 2, hd // 2, w.shape[1]).transpose(1, 2).reshape(w.shape)
+
+    out = {"tok_embeddings.weight": sd["model.embed_tokens.weight"], "norm.weight": sd["model.norm.weight"],
+           "output.weight": sd["lm_head.weight"]}
+    for i in range(hc.num_hidden_layers):
+        a, b = f"model.layers.{i}.", f"layers.{i}."
+        out[b + "attention.wq.weight"] = unpermute(sd[a + "self_attn.q_proj.weight"], hc.num_attention_heads)
+        out[b + "attention.wk.weight"] = unpermute(sd[a + "self_attn.k_proj.weight"], hc.num_key_value_heads)
+        out[b + "attention.wv.weight"] = sd[a + "self_attn.v_proj.weight"]
+        out[b + "attention.wo.weight"] = sd[a + "self_attn.o_proj.weight"]
+        out[b + "feed_forward.w1.weight"] = sd[a + "mlp.gate_proj.weight"]
+        out[b + "feed_forward.w3.weight"] = sd[a + "mlp.up_proj.weight"]
+        out[b + "feed_forward.w2.weight"] = sd[a + "mlp.down_proj.weight"]
+        out[b + "attention_norm.weight"] = sd[a + "input_layernorm.weight"]
+        out[b + "ffn_norm.weight"] = sd[a + "post_attention_layernorm.weight"]
+    save_file({k: v.contiguous().bfloat16() for k, v in out.items()}, str(tmp_path / "consolidated.safetensors"))
+    (tmp_path / "params.json").write_text(json.dumps({
+        "dim": hc.hidden_size, "n_layers": hc.num_hidden_layers, "n_heads": hc.num_attention_heads,
+        "n_kv_heads": hc.num_key_value_heads, "hidden_dim": hc.intermediate_size, "vocab_size": hc.vocab_size,
+        "norm_eps": hc.rms_norm_eps, "rope_theta": float(getattr(hc, "rope_theta", None) or hc.rope_parameters["rope_theta"])}))
+    w, hf = loader_hf.load_hf(str(tmp_path), torch.device("cpu"))
+    assert w.cfg.rope_pairing == 0 and hf["model_type"] == "mistral"
+    toks = torch.randint(0, hc.vocab_size, (40,), generator=torch.Generator().manual_seed(2)).tolist()
+    with torch.no_grad():
+        want = model(torch.tensor([toks])).logits[0].float()
+    got = forward_ref(w, toks).float()
+    assert torch.nn.functional.cosine_similarity(got, want, dim=1).min().item() > 0.998
+    with pytest.raises(ValueError):
+        loader_hf.config_from_native_params({"dim": 8})
+    y = loader_hf.config_from_native_params({"dim": 64, "n_layers": 1, "n_heads": 2, "hidden_dim": 128, "vocab_size": 100,
+                                             "yarn": {"factor": 4.0, "beta": 16.0, "alpha": 2.0, "apply_scale": True}})
+    assert y["rope_parameters"]["beta_fast"] == 16.0 and y["rope_parameters"]["mscale_all_dim"] == 0.0
