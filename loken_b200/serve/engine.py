@@ -348,7 +348,7 @@ class LLMEngine:
                 self._logprobs(done, [first[s.seq_id] for s in done], lps)
             spec = self.spec
             commits = None
-            if plan.decodes and spec is not None and not any(s.grammar is not None for s in plan.decodes):
+            if plan.decodes and spec is not None:
                 with nvtx.span("verify"):
                     commits = spec.step(self, list(plan.decodes))
                 toks = []

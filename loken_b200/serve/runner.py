@@ -72,10 +72,11 @@ class ModelRunner:
         self.d_rule_vals = torch.zeros(samp_cap, RULES, **f32)
         self.d_rule_meta = torch.zeros(2, samp_cap, **i32)   # counts, modes
         self.mask_words = (weights.vocab_local * max(weights.tp_size, 1) + 31) // 32
-        self.d_mask = torch.zeros(max_seqs, self.mask_words, **i32)
-        self.d_mask_has = torch.zeros(max_seqs, **i32)
-        self.h_mask = torch.zeros(max_seqs, self.mask_words, dtype=torch.int32, pin_memory=torch.cuda.is_available())
-        self.h_mask_has = torch.zeros(max_seqs, dtype=torch.int32, pin_memory=torch.cuda.is_available())
+        # one mask row per sampler row: a constrained sequence's verify rows each carry the mask of their own history
+        self.d_mask = torch.zeros(samp_cap, self.mask_words, **i32)
+        self.d_mask_has = torch.zeros(samp_cap, **i32)
+        self.h_mask = torch.zeros(samp_cap, self.mask_words, dtype=torch.int32, pin_memory=torch.cuda.is_available())
+        self.h_mask_has = torch.zeros(samp_cap, dtype=torch.int32, pin_memory=torch.cuda.is_available())
         self.n_mask, self.n_mask_has = self.h_mask.numpy(), self.h_mask_has.numpy()
         self.d_sampled = torch.zeros(cap, **i32)
         self.d_row_seq = torch.zeros(cap, **i32)
@@ -166,7 +167,7 @@ class ModelRunner:
                 self.n_rule_meta[1, i] = mode
         n = len(seqs)
         any_mask = False
-        if n <= self.max_seqs:
+        if n <= self.samp_cap:
             for i, s in enumerate(seqs):
                 g = getattr(s, "grammar", None)
                 if g is None:
@@ -203,7 +204,7 @@ class ModelRunner:
             sampling.token_rules_(logits, self.d_rule_ids, self.d_rule_vals, self.d_rule_meta[0], self.d_rule_meta[1],
                                   rows=n)
         if flags & FLAG_MASK:
-            sampling.token_bitmask_(logits, self.d_mask, self.d_mask_has, rows=min(n, self.max_seqs))
+            sampling.token_bitmask_(logits, self.d_mask, self.d_mask_has, rows=min(n, self.samp_cap))
         sampling.sample(logits, self.d_samp_f[0], self.d_samp_f[3], top_k=self.d_topk, top_p=self.d_samp_f[1],
                         min_p=self.d_samp_f[2], out=self.d_sampled, rows=n)
 
@@ -439,7 +440,20 @@ class ModelRunner:
             self.d_rule_ids[:n].copy_(self.h_rule_ids[:n], non_blocking=True)
             self.d_rule_vals[:n].copy_(self.h_rule_vals[:n], non_blocking=True)
             self.d_rule_meta[:, :n].copy_(self.h_rule_meta[:, :n], non_blocking=True)
-        flags = (FLAG_PENALTY if any_pen else 0) | (FLAG_RULES if any_rules else 0)
+        any_mask = False
+        for i, v in enumerate(views):
+            m = getattr(v, "mask", None)          # the grammar's mask after this row's history (serve/speculative.py)
+            if m is None:
+                self.n_mask_has[i] = 0
+            else:
+                any_mask = True
+                self.n_mask_has[i] = 1
+                self.n_mask[i, :len(m)] = m
+                self.n_mask[i, len(m):] = 0
+        if any_mask:
+            self.d_mask[:n].copy_(self.h_mask[:n], non_blocking=True)
+            self.d_mask_has[:n].copy_(self.h_mask_has[:n], non_blocking=True)
+        flags = (FLAG_PENALTY if any_pen else 0) | (FLAG_RULES if any_rules else 0) | (FLAG_MASK if any_mask else 0)
         self._sample(logits, n, flags)
         self.h_sampled[:n].copy_(self.d_sampled[:n], non_blocking=True)
         torch.cuda.current_stream().synchronize()

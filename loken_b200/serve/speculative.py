@@ -38,6 +38,7 @@ class _RowView:
         self.params = seq.params
         self._base = seq
         self._extra = extra
+        self.mask = None             # int32 words: the grammar's mask after this row's history, for constrained requests
 
     @property
     def tokens(self) -> List[int]:
@@ -305,11 +306,18 @@ class Speculator:
             room = engine.max_ctx - s.total_len - 1
             d = list(d[:max(0, min(k, room))])
             toks = s.tokens
+            masks = None
+            if getattr(s, "grammar", None) is not None:
+                # a constrained request: every row is masked for its own history, drafts the language refuses are cut
+                masks, d = s.grammar.rows_for_drafts(d)
             items.append((s, [toks[-1]] + d, len(toks) - 1))
             rng = engine.rngs[s.seq_id]
             st = rng.getstate()
             for i in range(len(d) + 1):
-                views.append(_RowView(s, d[:i]))
+                v = _RowView(s, d[:i])
+                if masks is not None:
+                    v.mask = masks[i]
+                views.append(v)
                 uniforms.append(rng.random() if not s.params.greedy else 0.0)
             states.append((rng, st, d))
         logits = engine.runner.forward_rows(items, engine.alloc)

@@ -125,3 +125,33 @@ class GrammarSession:
 
     def done(self) -> bool:
         return bool(self.m.is_stopped())
+
+    def rollback(self, n: int):
+        """Forgets the last `n` accepted tokens (rows of a speculative step that were only looked at)."""
+        if n > 0 and not self.m.rollback(int(n)):
+            raise GrammarError(f"the matcher cannot go back {n} tokens: {self.m.get_error()}")
+
+    def rows_for_drafts(self, drafts) -> tuple:
+        """Masks for the verify rows of a speculative step: row i is sampled after drafts[:i], so it carries the
+        mask of the matcher's state there.  Drafts stop being usable at the first token the language refuses,
+        and at a token that completes it (the row sampling that token ends the request, nothing follows it).
+        Returns (masks, the usable drafts); the matcher is left where it was."""
+        masks, used = [self.mask()], 0
+        try:
+            for t in drafts:
+                t = int(t)
+                cur = masks[-1]
+                if t < 0 or (t >> 5) >= len(cur) or not (int(cur[t >> 5]) >> (t & 31)) & 1:
+                    break
+                if not self.m.consume_token(t):
+                    break
+                used += 1
+                if self.m.is_stopped():
+                    used -= 1
+                    self.rollback(1)
+                    break
+                masks.append(self.mask())
+        finally:
+            keep = len(masks) - 1
+            self.rollback(used)
+        return masks[:keep + 1], list(drafts[:keep])

@@ -52,3 +52,30 @@ def test_json_schema_and_unconstrained_neighbours(llm):
         llm.generate("x", GenerationParams(grammar=("regex", "(unclosed")))
     assert llm.worker.healthy
     assert llm.engine.runner.wsp.read_status() == 0
+
+
+def test_constrained_requests_under_speculation(llm):
+    """Verify rows of a constrained request are masked for their own history: the text stays in the language,
+    drafts that fit it are accepted, and the output equals plain constrained decoding."""
+    from loken_b200.engine.llm import GenerationParams
+    from loken_b200.serve.speculative import PromptLookupDrafter, Speculator
+
+    forced = GenerationParams(temperature=0.0, max_tokens=40, grammar=("regex", "(ab ){6}ab"))
+    schema = {"type": "object", "properties": {"n": {"enum": [1, 22, 333]}, "ok": {"type": "boolean"}},
+              "required": ["n", "ok"], "additionalProperties": False, "x-guidance": {"whitespace_flexible": False}}
+    sampled = GenerationParams(temperature=0.8, top_k=0, top_p=1.0, max_tokens=96, seed=3, grammar=("json_schema", schema))
+    free = GenerationParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    plain = [llm.generate("ab ab ab ab ", forced).text, llm.generate("json:", sampled).text,
+             llm.generate("ab ab ab ab ", free).token_ids]
+    llm.on_engine_thread(lambda eng: eng.attach_speculator(Speculator(PromptLookupDrafter(), 4)))
+    try:
+        a = llm.generate("ab ab ab ab ", forced)
+        assert a.text == "ab ab ab ab ab ab ab" == plain[0] and a.finish_reason == "stop"
+        spec = llm.engine.spec
+        assert spec.accepted > 0                    # the language leaves one choice per position, so the looked-up drafts fit
+        b = llm.generate("json:", sampled)
+        assert b.text == plain[1] and set(json.loads(b.text)) == {"n", "ok"}
+        assert llm.generate("ab ab ab ab ", free).token_ids == plain[2]
+    finally:
+        llm.on_engine_thread(lambda eng: eng.detach_speculator())
+    assert llm.worker.healthy and llm.engine.runner.wsp.read_status() == 0
