@@ -641,6 +641,49 @@ def ops_router(ctx: ServerContext):
             raise ApiError(409, "no arrangement of these layers fits these nodes over these links")
         return plan.to_json()
 
+    @r.post("/api/layers/swap")
+    async def layers_swap(req: Request):
+        """Attach or detach adapters on a loaded model without reloading it.  `adapters` is the set the model
+        should end up with: PEFT directories, each optionally with a `weight` (`[]` detaches everything).  The
+        weights are rewritten in place (`models/lora.py: AdapterSet`), cached prompt rows computed under the
+        old weights are dropped, and the call waits for nothing: it answers 409 while requests are in flight."""
+        from starlette.concurrency import run_in_threadpool
+
+        body = await req.json()
+        llm = ctx.registry.get(body.get("model"))
+        wanted = {}
+        for a in body.get("adapters") or []:
+            path, wt = (a, 1.0) if isinstance(a, str) else (a.get("path"), a.get("weight", 1.0))
+            if not path:
+                raise ApiError(400, "every adapter names its path")
+            wanted[str(path)] = float(wt)
+
+        def work(eng):
+            from ..models.lora import AdapterSet
+
+            e = getattr(eng, "_e", eng)
+            if eng.has_work():
+                raise RuntimeError("busy")
+            mw = getattr(e, "weights", None)
+            if mw is None:
+                raise ValueError("this engine exposes no weights to adapt")
+            if getattr(e, "adapters", None) is None:
+                e.adapters = AdapterSet(mw)
+            rep = e.adapters.apply(wanted)
+            rep["prefix_blocks_dropped"] = int(e.alloc.reset_prefix_cache() or 0)
+            if getattr(e, "disk", None) is not None:
+                e.disk.rescope("|".join(f"{p}={w}" for p, w in sorted(wanted.items())))
+            return rep
+
+        try:
+            return await run_in_threadpool(llm.on_engine_thread, work)
+        except RuntimeError as e:
+            if str(e) == "busy":
+                raise ApiError(409, "requests are in flight on this model; swap adapters when it is idle")
+            raise ApiError(500, str(e))
+        except (ValueError, OSError, KeyError) as e:
+            raise ApiError(400, f"cannot swap adapters: {e}")
+
     @r.post("/api/swap")
     async def swap(req: Request):
         """Replace the resident model: the named one (or every resident language model when none is

@@ -112,3 +112,86 @@ def merge_lora(mw: ModelWeights, adapter: LoraAdapter, weight: float = 1.0) -> i
             full[r0:r1] += (weight * adapter.scale) * (B.to(dev) @ A.to(dev))
         setattr(mw.layers[il], name, make_linear(full, lin.kind, lin.bias))
     return len(adapter.pairs)
+
+
+class AdapterSet:
+    """The adapters of a loaded model, changed in place without a reload (`POST /api/layers/swap`).
+
+    `apply(wanted)` takes the set the model should end up with (path -> weight).  Every projection an old or a
+    new adapter touches is rebuilt as base + the sum of the wanted adapters and copied INTO the tensors the
+    model already uses, so captured graphs, fused layers and workspaces keep pointing at valid weights.  The
+    base of a projection is kept on the host from the first time an adapter touches it (what was merged at
+    load counts as base), which makes a detach exact: the bytes return, not an approximation of them."""
+
+    def __init__(self, mw: ModelWeights):
+        if mw.tp_size != 1:
+            raise ValueError("adapters are swapped on an unsharded model")
+        self.mw = mw
+        self.base: Dict[Tuple[int, str], Linear] = {}       # host copies, as stored
+        self.active: Dict[str, Tuple[LoraAdapter, float]] = {}
+
+    @staticmethod
+    def _host_copy(lin: Linear) -> Linear:
+        if lin.kind == "bf16":
+            return Linear("bf16", lin.weight.detach().to("cpu", copy=True), lin.bias, lin.n_out, lin.n_in)
+        w = lin.weight
+        return Linear(lin.kind, type(w)(w.data.detach().to("cpu", copy=True), w.scale.detach().to("cpu", copy=True)),
+                      lin.bias, lin.n_out, lin.n_in)
+
+    @staticmethod
+    def _write(dst: Linear, src: Linear):
+        if dst.kind == "bf16":
+            dst.weight.copy_(src.weight.to(dst.weight.device))
+        else:
+            dst.weight.data.copy_(src.weight.data.to(dst.weight.data.device))
+            dst.weight.scale.copy_(src.weight.scale.to(dst.weight.scale.device))
+
+    def _targets(self, adapter: LoraAdapter, ranges) -> Dict[Tuple[int, str], list]:
+        out: Dict[Tuple[int, str], list] = {}
+        for (il, proj), (A, B) in adapter.pairs.items():
+            if il >= len(self.mw.layers) or self.mw.layers[il] is None:
+                raise ValueError(f"adapter names layer {il}; the model holds {len(self.mw.layers)}")
+            name, r0, r1 = ranges[proj]
+            lin = getattr(self.mw.layers[il], name)
+            if lin is None:
+                raise ValueError(f"layer {il} has no dense {proj} (mixture-of-experts layers take no adapter here)")
+            if lin.kind == "gguf":
+                raise ValueError("GGUF block weights take no merged adapter; load the bf16 or fp8 checkpoint")
+            if B.shape[0] != r1 - r0 or A.shape[1] != lin.n_in:
+                raise ValueError(f"layer {il} {proj}: adapter is {B.shape[0]} x {A.shape[1]}, the model {r1 - r0} x {lin.n_in}")
+            out.setdefault((il, name), []).append((r0, r1, A, B))
+        return out
+
+    def apply(self, wanted: Dict[str, float], loader=load_lora) -> dict:
+        ranges = _row_ranges(self.mw)
+        new_active: Dict[str, Tuple[LoraAdapter, float]] = {}
+        for path, wt in wanted.items():
+            old = self.active.get(path)
+            new_active[path] = (old[0] if old is not None else loader(path), float(wt))
+        # everything is checked before anything is written
+        plans = {path: self._targets(ad, ranges) for path, (ad, _w) in new_active.items()}
+        touched = set()
+        for path, (ad, _w) in self.active.items():
+            touched |= set(self._targets(ad, ranges))
+        for t in plans.values():
+            touched |= set(t)
+        for key in touched:
+            il, name = key
+            lin = getattr(self.mw.layers[il], name)
+            if key not in self.base:
+                self.base[key] = self._host_copy(lin)
+            base = self.base[key]
+            parts = [(r0, r1, A, B, w * ad.scale) for path, (ad, w) in new_active.items()
+                     for (r0, r1, A, B) in plans[path].get(key, [])]
+            if not parts:
+                self._write(lin, base)                  # no adapter left on it: the stored bytes come back
+                continue
+            dev = lin.weight.device if lin.kind == "bf16" else lin.weight.data.device
+            full = dequant_linear(base).to(dev)
+            for r0, r1, A, B, sc in parts:
+                full[r0:r1] += sc * (B.to(dev) @ A.to(dev))
+            self._write(lin, make_linear(full, lin.kind, lin.bias))
+        report = {"attached": sorted(set(new_active) - set(self.active)), "detached": sorted(set(self.active) - set(new_active)),
+                  "kept": sorted(set(new_active) & set(self.active)), "projections": len(touched)}
+        self.active = new_active
+        return report

@@ -35,10 +35,16 @@ class DiskPersistence:
         from ..cluster.handover import model_identity
 
         self.runner, self.alloc, self.tier = runner, alloc, tier
-        self.ident = _fnv64(model_identity(runner))
+        self._identity = model_identity(runner)
+        self.ident = _fnv64(self._identity)
         self.saved_blocks = 0
         self.restored_tokens = 0
         self.failures = 0
+
+    def rescope(self, what: str):
+        """The weights changed in place (adapters were swapped): rows written under the old weights are no longer
+        this model's, so the keys move to a scope of their own."""
+        self.ident = _fnv64(self._identity + ("|" + what if what else ""))
 
     def _salt(self, salt: int) -> int:
         return (int(salt) * 0x9E3779B97F4A7C15 ^ self.ident) & 0x7FFFFFFFFFFFFFFF

@@ -253,3 +253,40 @@ def test_kv_handover_between_two_engines():
     assert b.generate([prompt], sp)[0].output == want
     with pytest.raises(ValueError):
         b.import_prefix(b"not a container")
+
+
+def test_adapters_swapped_in_place_under_captured_graphs():
+    """An adapter attached to a running engine changes its tokens to those of a model merged at load, and a
+    detach brings the original tokens back: the decode graphs captured before the swap read the rewritten
+    weights through the same pointers."""
+    from loken_b200.models.lora import AdapterSet, adapter_from_tensors, merge_lora
+    from loken_b200.models.weights import random_weights
+    from loken_b200.serve.engine import LLMEngine
+    from loken_b200.serve.params import SamplingParams
+
+    cfg, w = _mk("llama", "bf16")
+    g = torch.Generator().manual_seed(11)
+    t = {}
+    for il in range(cfg.n_layers):
+        for blk, proj, out, inn in (("self_attn", "q_proj", cfg.n_q * cfg.head_dim, cfg.hidden),
+                                    ("mlp", "down_proj", cfg.hidden, cfg.intermediate)):
+            base = f"base_model.model.model.layers.{il}.{blk}.{proj}"
+            t[base + ".lora_A.weight"] = torch.randn(4, inn, generator=g) * 0.3
+            t[base + ".lora_B.weight"] = torch.randn(out, 4, generator=g) * 0.3
+    ad = adapter_from_tensors(t, 4, 8.0)
+    merged = random_weights(cfg, torch.device(DEV), seed=1, std=0.05)
+    merge_lora(merged, ad, 1.0)
+    mk = lambda ww: LLMEngine(cfg, weights=ww, num_blocks=64, max_seqs=4, max_prefill_tokens=256, max_ctx=256)
+    sp = SamplingParams(temperature=0.0, top_k=0, top_p=1.0, max_tokens=12, ignore_eos=True)
+    prompt = torch.randint(0, cfg.vocab, (20,), generator=g).tolist()
+    eng = mk(w)
+    plain = eng.generate([prompt], sp)[0].output                    # captures the decode graph over the base weights
+    want = mk(merged).generate([prompt], sp)[0].output
+    assert want != plain                                            # the adapter is strong enough to be seen
+    s = AdapterSet(eng.weights)
+    s.apply({"a": 1.0}, loader=lambda _p: ad)
+    eng.reset_prefix_cache()
+    assert eng.generate([prompt], sp)[0].output == want
+    s.apply({}, loader=lambda _p: ad)
+    eng.reset_prefix_cache()
+    assert eng.generate([prompt], sp)[0].output == plain

@@ -78,3 +78,46 @@ def test_adapter_files_and_refusals(tmp_path):
     q8 = random_weights(tiny("llama", weight_format="q8_0"), torch.device("cpu"), seed=2, std=0.05)
     with pytest.raises(ValueError):
         merge_lora(q8, ad)
+
+
+@pytest.mark.parametrize("fmt", ["bf16", "fp8_block"])
+def test_adapters_are_swapped_in_place_and_a_detach_is_exact(fmt):
+    from loken_b200.models.lora import AdapterSet
+
+    kw = dict(head_dim=128, n_q=4, n_kv=2, hidden=512, intermediate=1024) if fmt == "fp8_block" else {}
+    cfg = tiny("llama", weight_format=fmt, **kw)
+    mw = random_weights(cfg, torch.device("cpu"), seed=2, std=0.05)
+    ref = random_weights(cfg, torch.device("cpu"), seed=2, std=0.05)          # the same model, merged the load-time way
+    raw = lambda lin: lin.weight if lin.kind == "bf16" else lin.weight.data.view(torch.uint8)
+    ptrs = [raw(getattr(l, n)).data_ptr() for l in mw.layers for n in ("wqkv", "wo", "w_gate_up", "w_down")]
+    before = [raw(getattr(l, n)).clone() for l in mw.layers for n in ("wqkv", "wo", "w_gate_up", "w_down")]
+    ads = {"a": adapter_from_tensors(_adapter_tensors(cfg, 4, [1], ["q_proj", "v_proj", "down_proj"]), 4, 8.0),
+           "b": adapter_from_tensors(_adapter_tensors(cfg, 2, [0, 1], ["o_proj", "down_proj"]), 2, 2.0)}
+    s = AdapterSet(mw)
+    rep = s.apply({"a": 0.5}, loader=ads.__getitem__)
+    assert rep["attached"] == ["a"] and rep["projections"] == 2
+    merge_lora(ref, ads["a"], 0.5)
+    for l, r in zip(mw.layers, ref.layers):
+        for n in ("wqkv", "wo", "w_gate_up", "w_down"):
+            assert torch.equal(raw(getattr(l, n)), raw(getattr(r, n))), n                 # the same bits as a merge at load
+    # the set the model should end up with: a stays at another weight, b joins; both touch layer 1's down projection
+    rep = s.apply({"a": 1.0, "b": 0.25}, loader=ads.__getitem__)
+    assert rep == {"attached": ["b"], "detached": [], "kept": ["a"], "projections": 5}
+    want = dequant_linear(AdapterSet._host_copy(random_weights(cfg, torch.device("cpu"), seed=2, std=0.05).layers[1].w_down))
+    for name, w in (("a", 1.0), ("b", 0.25)):
+        A, B = ads[name].pairs[(1, "down_proj")]
+        want = want + w * ads[name].scale * (B @ A)
+    got = dequant_linear(mw.layers[1].w_down)
+    assert (got - want).abs().max() <= (2e-2 if fmt == "bf16" else 8e-2) * want.abs().max()
+    # everything detached: the stored bytes are back, and no tensor was replaced on the way
+    rep = s.apply({}, loader=ads.__getitem__)
+    assert rep["detached"] == ["a", "b"] and rep["attached"] == []
+    after = [raw(getattr(l, n)) for l in mw.layers for n in ("wqkv", "wo", "w_gate_up", "w_down")]
+    assert all(torch.equal(x, y) for x, y in zip(before, after))
+    assert ptrs == [t.data_ptr() for t in after]
+    # a bad adapter changes nothing
+    bad = adapter_from_tensors(_adapter_tensors(cfg, 4, [7], ["q_proj"]), 4, 8.0)
+    with pytest.raises(ValueError):
+        s.apply({"a": 1.0, "bad": 1.0}, loader={"a": ads["a"], "bad": bad}.__getitem__)
+    assert all(torch.equal(x, raw(getattr(l, n))) for x, (l, n) in
+               zip(before, [(l, n) for l in mw.layers for n in ("wqkv", "wo", "w_gate_up", "w_down")]))

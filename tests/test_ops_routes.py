@@ -112,3 +112,36 @@ def test_validate_and_repair(tmp_path):
     bad = c.post("/api/models/repair", json={"path": path, "model": "m"}).json()
     assert not bad["ok"] and not bad["repaired"] and "api/pull" in bad["action"]
     assert c.post("/api/models/validate", json={"model": "nowhere"}).status_code == 404
+
+
+def test_layers_swap_route(monkeypatch):
+    import types
+
+    from loken_b200.models import lora
+
+    c, ctx, llm = client()
+    assert c.post("/api/layers/swap", json={"model": "fake-model", "adapters": ["/x"]}).status_code == 400   # no weights here
+    calls = []
+
+    class FakeSet:
+        def __init__(self, mw):
+            self.mw = mw
+
+        def apply(self, wanted):
+            calls.append(dict(wanted))
+            if "bad" in wanted:
+                raise ValueError("adapter names layer 7")
+            return {"attached": sorted(wanted), "detached": [], "kept": [], "projections": len(wanted)}
+
+    monkeypatch.setattr(lora, "AdapterSet", FakeSet)
+    llm.engine.weights = types.SimpleNamespace()
+    toks = list(range(50))
+    llm.engine.alloc.allocate_with_prefix(7, toks)
+    llm.engine.alloc.commit_prefix(7, toks)
+    llm.engine.alloc.free(7)
+    r = c.post("/api/layers/swap", json={"model": "fake-model", "adapters": ["/a", {"path": "/b", "weight": 0.5}]})
+    assert r.status_code == 200 and r.json()["attached"] == ["/a", "/b"] and r.json()["prefix_blocks_dropped"] == 3
+    assert calls[-1] == {"/a": 1.0, "/b": 0.5}
+    assert c.post("/api/layers/swap", json={"adapters": []}).json()["attached"] == []
+    assert c.post("/api/layers/swap", json={"adapters": ["bad"]}).status_code == 400
+    assert c.post("/api/layers/swap", json={"adapters": [{"weight": 2}]}).status_code == 400
