@@ -54,7 +54,8 @@ def router(ctx: ServerContext) -> APIRouter:
     @r.get("/api/tags")
     async def tags():
         """Loaded models, then what the model stores hold (Ollama manifests, the Hugging Face cache,
-        bare GGUF files), each listed once."""
+        bare GGUF files), each listed once; then the models resident on the peers this node sees, each
+        under its `node` (`docs/CLUSTER.md:57` of the reference)."""
         out, seen = [], set()
         for m in ctx.registry.list():
             seen.add(m.model_id)
@@ -69,6 +70,11 @@ def router(ctx: ServerContext) -> APIRouter:
                         "modified_at": datetime.datetime.fromtimestamp(e.modified or 0, datetime.timezone.utc).isoformat(),
                         "details": {"format": "gguf" if e.source != "huggingface" else "safetensors",
                                     "family": "", "parameter_size": "", "quantization_level": ""}})
+        m = getattr(ctx, "membership", None)
+        for p in (m.alive() if m is not None else []):
+            for name in p.models:
+                out.append({"name": name, "model": name, "node": p.node_id, "endpoint": p.addr, "size": 0, "digest": "",
+                            "details": {"format": "", "family": "", "parameter_size": "", "quantization_level": ""}})
         return {"models": out}
 
     @r.post("/api/show")

@@ -429,7 +429,8 @@ def ops_router(ctx: ServerContext):
         """Records what the matrices of a checkpoint see on the given `texts` as the calibration `name`:
         per tensor, the mean square of the activations it multiplies and of its own values (the fp32
         forward of `models/reference.py`).  `model` is a path or a store name; `tokens` bounds the pass
-        (default 4096), `excerpt` the characters taken from each text."""
+        (default 4096), `excerpt` the characters taken from each text, `rows` how many activation rows per
+        tensor are kept beside the record for error-compensated conversion (default 64, 0 for none)."""
         from starlette.concurrency import run_in_threadpool
 
         body = await req.json()
@@ -457,10 +458,13 @@ def ops_router(ctx: ServerContext):
             tk = from_gguf_meta(meta)
             lists = [tk.encode(t[:excerpt], True) for t in texts]
             emit({"status": "recording", "texts": len(lists), "tokens": min(budget, sum(len(x) for x in lists))})
-            stats = _cal(w, lists, max_tokens=budget)
+            keep = int(body.get("rows", 64) or 0)
+            kept = {} if keep > 0 else None
+            stats = _cal(w, lists, max_tokens=budget, keep_rows=keep, rows_out=kept)
             out = _os.path.join(_calibration_dir(), name + ".json")
-            rec = write_calibration(out, name, model, stats, len(lists), min(budget, sum(len(x) for x in lists)))
-            emit({"status": "success", "calibration": name, "path": out, "tensors": len(rec["stats"])})
+            rec = write_calibration(out, name, model, stats, len(lists), min(budget, sum(len(x) for x in lists)), rows=kept)
+            emit({"status": "success", "calibration": name, "path": out, "tensors": len(rec["stats"]),
+                  "rows": keep if kept else 0})
 
         return await run_in_threadpool(_ndjson_job, job, body.get("stream", True) is not False)
 

@@ -11,7 +11,10 @@ fits, then to bf16.
 
 A calibration record (`calibrate()`: per-tensor sensitivity measured on text) lifts the most
 sensitive tensors one step (Q4_K -> Q6_K -> Q8_0): the reference's convert takes a calibration the
-same way (`docs/API.md:528-529`, `src/convert/`).  The decode -> encode path runs in the C++ codecs
+same way (`docs/API.md:528-529`, `src/convert/`).  When the record also carries activation rows
+(`<record>.rows.npz`, kept by `calibrate(keep_rows=...)`), the matrices those rows feed are encoded with
+error compensation (`formats/compensate.py`): the format's own bytes, chosen so that the outputs over such
+rows stay close.  The decode -> encode path runs in the C++ codecs
 (`csrc/host/formats.cpp`), one tensor in memory at a time.
 """
 from __future__ import annotations
@@ -109,9 +112,13 @@ def requantize_gguf(src: str, dst: str, fmt: str, *, calibration: Optional[str] 
     if fmt not in FORMATS:
         raise ValueError(f"unknown target format {fmt} (known: {', '.join(FORMATS)})")
     sens = None
+    rows = None
     if calibration:
         with open(calibration) as f:
             sens = json.load(f).get("sensitivity", {})
+        if os.path.exists(calibration + ".rows.npz"):
+            rows = np.load(calibration + ".rows.npz")
+    compensated = 0
     r = G.GGUFReader(src)
     tmp = dst + ".partial"
     try:
@@ -140,7 +147,14 @@ def requantize_gguf(src: str, dst: str, fmt: str, *, calibration: Optional[str] 
                 bytes_out += ti.nbytes
             else:
                 x = G.dequantize(ti.data, ti.ggml_type, ti.shape, threads=threads)
-                raw = G.quantize(x, t, threads=threads)
+                if (rows is not None and name in rows.files and len(ti.shape) == 2 and t not in (G.F32, G.F16, G.BF16)
+                        and rows[name].shape[1] == ti.shape[-1]):
+                    from .compensate import quantize_compensated
+
+                    raw, _ = quantize_compensated(x, rows[name].astype(np.float32), t, threads=threads)
+                    compensated += 1
+                else:
+                    raw = G.quantize(x, t, threads=threads)
                 w.add_tensor(name, shape_only, t, raw=raw)
                 out_t = t
                 bytes_out += raw.nbytes
@@ -156,7 +170,7 @@ def requantize_gguf(src: str, dst: str, fmt: str, *, calibration: Optional[str] 
         if os.path.exists(tmp):
             os.remove(tmp)
     return {"source": src, "output": dst, "format": fmt, "tensors": len(names), "types": counts,
-            "bytes_in": bytes_in, "bytes_out": bytes_out, "calibrated": bool(sens)}
+            "bytes_in": bytes_in, "bytes_out": bytes_out, "calibrated": bool(sens), "compensated": compensated}
 
 
 def sensitivity_from_activations(stats: Dict[str, Dict[str, float]]) -> Dict[str, float]:
@@ -170,10 +184,17 @@ def sensitivity_from_activations(stats: Dict[str, Dict[str, float]]) -> Dict[str
     return {k: v / tot for k, v in out.items()}
 
 
-def write_calibration(path: str, name: str, model: str, stats: Dict[str, Dict[str, float]], texts: int, tokens: int):
+def write_calibration(path: str, name: str, model: str, stats: Dict[str, Dict[str, float]], texts: int, tokens: int,
+                      rows: Optional[Dict[str, np.ndarray]] = None):
+    """`rows`: tensor name -> activation rows [n, K] (float16) kept for error compensation; stored beside the
+    record as `<path>.rows.npz`."""
     rec = {"name": name, "model": model, "texts": texts, "tokens": tokens, "stats": stats,
-           "sensitivity": sensitivity_from_activations(stats)}
+           "sensitivity": sensitivity_from_activations(stats), "rows": bool(rows)}
     os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+    if rows:
+        tmpz = path + ".rows.partial.npz"
+        np.savez_compressed(tmpz, **{k: np.asarray(v, dtype=np.float16) for k, v in rows.items()})
+        os.replace(tmpz, path + ".rows.npz")
     tmp = path + ".partial"
     with open(tmp, "w") as f:
         json.dump(rec, f)
@@ -186,21 +207,32 @@ _ROLE_TENSORS = {"qkv": ("attn_q", "attn_k", "attn_v", "attn_qkv"), "o": ("attn_
                  "gate_up": ("ffn_gate", "ffn_up", "ffn_gate_exps", "ffn_up_exps"), "down": ("ffn_down",)}
 
 
-def calibrate(weights, token_lists, *, max_tokens: int = 4096) -> Dict[str, Dict[str, float]]:
+def calibrate(weights, token_lists, *, max_tokens: int = 4096, keep_rows: int = 0, rows_out: Optional[dict] = None
+              ) -> Dict[str, Dict[str, float]]:
     """Runs the fp32 forward of `weights` (a loaded model, one rank) over the given token lists and records,
     per stored tensor, the mean square of the activations it multiplies, the mean square of its own
     values and its row length: what `sensitivity_from_activations` turns into a ranking.  Returns the
-    stats keyed by GGUF tensor name."""
+    stats keyed by GGUF tensor name.  With `keep_rows` > 0, up to that many activation rows per tensor
+    (evenly spaced over the text) are put into `rows_out` under the same names, for error compensation."""
     import torch
 
     from ..models.reference import dequant_linear, forward_ref
 
     acc: Dict[tuple, list] = {}
 
+    kept: Dict[tuple, list] = {}
+
     def probe(il, role, x):
         s = acc.setdefault((il, role), [0.0, 0])
         s[0] += float(x.float().pow(2).sum())
         s[1] += x.numel()
+        if keep_rows > 0:
+            have = kept.setdefault((il, role), [])
+            room = keep_rows - sum(r.shape[0] for r in have)
+            if room > 0:
+                xr = x.float().reshape(-1, x.shape[-1])
+                step = max(1, xr.shape[0] // room)
+                have.append(xr[::step][:room].to(torch.float16).cpu().numpy())
 
     seen = 0
     with torch.no_grad():
@@ -222,4 +254,6 @@ def calibrate(weights, token_lists, *, max_tokens: int = 4096) -> Dict[str, Dict
             w_ms, k = float(wf.pow(2).mean()), float(wf.shape[1])
         for leaf in _ROLE_TENSORS[role]:
             stats[f"blk.{il}.{leaf}.weight"] = {"act_ms": ss / max(n, 1), "w_ms": w_ms, "k": k}
+            if rows_out is not None and kept.get((il, role)):
+                rows_out[f"blk.{il}.{leaf}.weight"] = np.concatenate(kept[(il, role)], 0)
     return stats

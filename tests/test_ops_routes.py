@@ -30,6 +30,8 @@ def test_peers_prefix_measure_and_status():
                            layer_cost={"fake-model": {"card_ms": 0.2, "host_ms": 0.0, "card_bytes": 10}}, card_bytes_free=1 << 30)
     ctx.membership.timed("n2", 4.0)
     ctx.membership.timed("n2", 2.0)
+    tags = c.get("/api/tags").json()["models"]
+    assert [t.get("node") for t in tags] == [None, "n2"] and tags[1]["endpoint"] == "http://n2:1"
     r = c.get("/api/cluster/peers").json()
     p2 = [p for p in r["peers"] if p["node_id"] == "n2"][0]
     assert r["clustered"] and p2["alive"] and 2.0 < p2["rtt_ms"] < 4.0 and p2["state"]["layer_cost"]["fake-model"]["card_ms"] == 0.2

@@ -101,3 +101,31 @@ def test_convert_and_calibrate_routes(src, tmp_path):
     assert entry is not None and G.GGUFReader(entry.path).meta["general.file_type"] == 15
     assert c.post("/api/convert", json={"name": "y:q8", "model": str(tmp_path / "none.gguf"), "stream": False}).status_code == 400
     assert c.post("/api/convert", json={"name": "y", "model": src, "calibration": "nope"}).status_code == 404
+
+
+def test_conversion_with_activation_rows_keeps_the_model_closer(src, tmp_path):
+    """A record that carries activation rows makes the conversion error-compensated: the converted model's
+    logits on text like the calibration text are closer to the source's than a plain conversion's."""
+    from loken_b200.models.loader import load_gguf
+    from loken_b200.models.reference import forward_ref
+
+    w, _ = load_gguf(src, torch.device("cpu"))
+    g = torch.Generator().manual_seed(0)
+    texts = [torch.randint(0, 64, (48,), generator=g).tolist() for _ in range(4)]       # a narrow "language": 64 of 512 ids
+    kept = {}
+    stats = R.calibrate(w, texts, max_tokens=192, keep_rows=96, rows_out=kept)
+    assert kept["blk.0.attn_q.weight"].shape == (96, 256) and kept["blk.1.ffn_down.weight"].shape[1] == 512
+    assert kept["blk.0.attn_q.weight"] is not None and kept["blk.0.attn_k.weight"].shape == kept["blk.0.attn_q.weight"].shape
+    R.write_calibration(str(tmp_path / "c.json"), "c", "src", stats, 4, 192, rows=kept)
+    assert os.path.exists(str(tmp_path / "c.json.rows.npz"))
+    plain = R.requantize_gguf(src, str(tmp_path / "plain.gguf"), "q4_k")
+    comp = R.requantize_gguf(src, str(tmp_path / "comp.gguf"), "q4_k", calibration=str(tmp_path / "c.json"))
+    assert plain["compensated"] == 0 and comp["compensated"] >= 8
+    held = torch.randint(0, 64, (40,), generator=g).tolist()
+    want = forward_ref(w, held).float()
+    err = {}
+    for name in ("plain", "comp"):
+        wq, _ = load_gguf(str(tmp_path / f"{name}.gguf"), torch.device("cpu"))
+        err[name] = float((forward_ref(wq, held).float() - want).pow(2).mean())
+    # the lifted tensors of the calibrated plan help too; what is asserted is the whole effect a user gets
+    assert err["comp"] < err["plain"], err
