@@ -155,7 +155,8 @@ def build_parser() -> argparse.ArgumentParser:
     pc = sub.add_parser("plan-cut", help="where to cut a layer stack over nodes; computed here, no server needed")
     pc.add_argument("spec", help="a JSON file: layers, layer_bytes, nodes, links, objective (see cluster/cut_plan.py)")
     dh = sub.add_parser("draft-head")
-    dh.add_argument("source", help="a checkpoint directory (safetensors) or a GGUF file that carries mtp.* tensors")
+    dh.add_argument("source", help="a checkpoint directory (safetensors), a GGUF file that carries mtp.* tensors, or a hub "
+                                   "repository (owner/name): then only the head's bytes are fetched, by ranged reads")
     dh.add_argument("output", help="OUT.gguf, or a directory for a safetensors companion")
     return ap
 
@@ -325,7 +326,14 @@ def main(argv=None, out=sys.stdout) -> int:
         p(f"crossings {plan.crossing_ms:.3f} ms per token, objective {plan.total_ms:.3f}" + ("" if plan.exact else "  (fixed node order: not exact)"))
     elif args.cmd == "draft-head":
         try:
-            p(json.dumps(extract_draft_head(args.source, args.output), indent=1))
+            import os
+
+            if not os.path.exists(args.source) and args.source.count("/") == 1 and args.output.endswith(".gguf"):
+                from ..store.download import fetch_draft_head
+
+                p(json.dumps(fetch_draft_head(args.source, args.output, token=os.environ.get("HF_TOKEN")), indent=1))
+            else:
+                p(json.dumps(extract_draft_head(args.source, args.output), indent=1))
         except (ValueError, OSError) as e:
             p(f"loken draft-head: {e}")
             return 1

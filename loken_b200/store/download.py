@@ -126,3 +126,78 @@ def pull_huggingface(hf_dir: str, repo: str, files: Iterable[str], *, revision: 
     with open(os.path.join(repo_dir, "refs", "main"), "w") as fh:
         fh.write(revision)
     yield {"status": "success"}
+
+
+# ---- a model's draft head without the model ------------------------------------------------------------------
+def _read_range(url: str, lo: int, hi: int, opener: Opener, headers: Dict[str, str]) -> bytes:
+    """Bytes [lo, hi) of `url`.  A server that ignores the Range header is refused: the point is not to fetch
+    a whole shard for a few tensors."""
+    status, _rh, chunks = opener(url, dict(headers, Range=f"bytes={lo}-{hi - 1}"))
+    if status != 206:
+        raise IOError(f"GET {url} with a byte range answered {status}; a ranged read was needed")
+    data = b"".join(chunks)
+    if len(data) != hi - lo:
+        raise IOError(f"GET {url} returned {len(data)} bytes for a range of {hi - lo}")
+    return data
+
+
+def fetch_draft_head(repo: str, output: str, *, revision: str = "main", opener: Opener = requests_opener,
+                     base_url: str = "https://huggingface.co", token: Optional[str] = None,
+                     prefixes: Tuple[str, ...] = ("mtp.", "model.mtp.")) -> dict:
+    """Writes `<output>` (a GGUF companion, `general.type = draft-head`) from the `mtp.*` tensors of a hub
+    repository, reading only their bytes: the index names the shards, a ranged read of each shard's
+    safetensors header names the offsets, and one ranged read per tensor brings its data
+    (reference: `src/inference/load/mtp_head.rs`, `loken draft-head`).  Returns a summary with the bytes read."""
+    import struct
+
+    import numpy as np
+
+    from ..formats import gguf as G
+
+    headers = {"Authorization": f"Bearer {token}"} if token else {}
+    url = lambda f: f"{base_url}/{repo}/resolve/{revision}/{f}"
+    status, _rh, chunks = opener(url("model.safetensors.index.json"), dict(headers))
+    if status == 200:
+        wm = json.loads(b"".join(chunks))["weight_map"]
+        shards = sorted({f for k, f in wm.items() if k.startswith(prefixes)})
+        if not shards:
+            raise ValueError(f"{repo} names no mtp.* tensors in its index")
+    elif status == 404:
+        shards = ["model.safetensors"]
+    else:
+        raise IOError(f"GET {url('model.safetensors.index.json')} answered {status}")
+    wire = 0
+    tensors = {}
+    dt = {"F32": ("<f4", 4), "F16": ("<f2", 2), "BF16": ("<u2", 2)}
+    for shard in shards:
+        (hl,) = struct.unpack("<Q", _read_range(url(shard), 0, 8, opener, headers))
+        if hl <= 0 or hl > (256 << 20):
+            raise IOError(f"{shard}: implausible safetensors header length {hl}")
+        head = json.loads(_read_range(url(shard), 8, 8 + hl, opener, headers))
+        wire += 8 + hl
+        for name, meta in head.items():
+            if name == "__metadata__" or not name.startswith(prefixes):
+                continue
+            if meta["dtype"] not in dt:
+                raise ValueError(f"{name}: dtype {meta['dtype']} is not read for a draft head")
+            lo, hi = meta["data_offsets"]
+            raw = _read_range(url(shard), 8 + hl + lo, 8 + hl + hi, opener, headers)
+            wire += hi - lo
+            ndt, _esz = dt[meta["dtype"]]
+            a = np.frombuffer(raw, dtype=ndt).reshape(meta["shape"])
+            if meta["dtype"] == "BF16":
+                a = (a.astype(np.uint32) << 16).view(np.float32)
+            short = name[len("model."):] if name.startswith("model.") else name
+            tensors[short[len("mtp."):]] = np.ascontiguousarray(a, dtype=np.float32)
+    if not tensors:
+        raise ValueError(f"{repo} carries no mtp.* tensors")
+    os.makedirs(os.path.dirname(os.path.abspath(output)) or ".", exist_ok=True)
+    tmp = output + ".partial"
+    w = G.GGUFWriter(tmp)
+    w.add_meta("general.type", "draft-head")
+    w.add_meta("general.name", f"{repo} (mtp)")
+    for k, v in tensors.items():
+        w.add_tensor(k, v, G.F32 if v.ndim < 2 else G.BF16)
+    w.close()
+    os.replace(tmp, output)
+    return {"repo": repo, "output": output, "tensors": len(tensors), "shards": len(shards), "bytes_read": wire}

@@ -168,3 +168,58 @@ def test_config_reads_store_directories():
 
     cfg = load_config(text="ollama_models_dir = [\"/a\", \"/b\"]\nhuggingface_models_dir = \"/hf\"\n")
     assert cfg.ollama_models_dir == ["/a", "/b"] and cfg.huggingface_models_dir == ["/hf"] and not cfg.notes
+
+
+def test_draft_head_is_fetched_by_ranged_reads_only(tmp_path):
+    """Two shards on a fake hub; the head's tensors sit in the second.  Only headers and the head's own bytes
+    cross the wire, and the companion file carries the tensors under their short names."""
+    import io
+    import json as _json
+
+    import torch
+    from safetensors.torch import save
+
+    from loken_b200.formats import gguf as G
+    from loken_b200.store.download import fetch_draft_head
+
+    g = torch.Generator().manual_seed(0)
+    big = {"model.layers.0.mlp.up_proj.weight": torch.randn(512, 256, generator=g).bfloat16()}
+    head = {"model.layers.0.self_attn.q_proj.weight": torch.randn(64, 64, generator=g).bfloat16(),
+            "model.mtp.fc.weight": torch.randn(32, 64, generator=g).bfloat16(),
+            "model.mtp.norm.weight": torch.randn(32, generator=g).float(),
+            "model.mtp.layers.0.self_attn.q_proj.weight": torch.randn(32, 32, generator=g).half()}
+    files = {"model-00001-of-00002.safetensors": save(big), "model-00002-of-00002.safetensors": save(head)}
+    index = {"weight_map": {**{k: "model-00001-of-00002.safetensors" for k in big},
+                            **{k: "model-00002-of-00002.safetensors" for k in head}}}
+    files["model.safetensors.index.json"] = _json.dumps(index).encode()
+    wire = {"bytes": 0, "whole": 0}
+
+    def opener(url, headers):
+        name = url.rsplit("/", 1)[-1]
+        if name not in files:
+            return 404, {}, iter(())
+        data = files[name]
+        rng = headers.get("Range")
+        if rng:
+            lo, hi = rng.split("=")[1].split("-")
+            part = data[int(lo):int(hi) + 1]
+            wire["bytes"] += len(part)
+            return 206, {}, iter([part])
+        wire["whole"] += len(data)
+        return 200, {}, iter([data])
+
+    out = str(tmp_path / "m.mtp.gguf")
+    rep = fetch_draft_head("acme/model", out, opener=opener)
+    assert rep["tensors"] == 3 and rep["shards"] == 1
+    assert wire["whole"] == len(files["model.safetensors.index.json"])                    # no shard was fetched whole
+    assert wire["bytes"] == rep["bytes_read"] < len(files["model-00002-of-00002.safetensors"])
+    r = G.GGUFReader(out)
+    assert r.meta["general.type"] == "draft-head" and set(r.tensors) == {"fc.weight", "norm.weight", "layers.0.self_attn.q_proj.weight"}
+    assert torch.equal(torch.from_numpy(r.tensors["fc.weight"].to_float()), head["model.mtp.fc.weight"].float())
+    assert torch.allclose(torch.from_numpy(r.tensors["norm.weight"].to_float()), head["model.mtp.norm.weight"])
+    r.close()
+    with pytest.raises(IOError):                                                           # a server without ranges is refused
+        fetch_draft_head("acme/model", out, opener=lambda u, h: (200, {}, iter([files.get(u.rsplit("/", 1)[-1], b"")])))
+    del files["model.safetensors.index.json"]
+    with pytest.raises((IOError, ValueError)):
+        fetch_draft_head("acme/other", str(tmp_path / "x.gguf"), opener=opener)
