@@ -13,6 +13,15 @@ from .common import ApiError, Auth, ModelRegistry, RateLimiter, RequestGate
 VERSION = "0.1.0"
 
 
+def _ask_prefix(peer: str, model_id: str, ids: List[int], cache_salt=None) -> int:
+    import requests
+
+    r = requests.post(peer.rstrip("/") + "/api/cluster/prefix",
+                      json={"model": model_id, "prompt": list(ids), "cache_salt": cache_salt}, timeout=2.0)
+    r.raise_for_status()
+    return int(r.json().get("cached_tokens", 0))
+
+
 def _fetch_prefill(peer: str, model_id: str, ids: List[int], timeout_s: float) -> bytes:
     import requests
 
@@ -41,6 +50,7 @@ class ServerSettings:
     # an answer a peer left unfinished is continued here only when both nodes hold the same bytes, unless
     # `resume_unverified` allows it anyway
     route_requests: bool = False
+    prefix_ask_min_tokens: int = 512        # prompts at least this long ask the peers how much of them they hold
     resume_unverified: bool = False
     node_id: Optional[str] = None
 
@@ -65,6 +75,8 @@ class ServerContext:
         from ..cluster.routing import RateMeter
 
         self.rate = RateMeter()                  # this node's decode rate, published by the gossip
+        self.prefill_rate = RateMeter()          # and the rate at which it reads prompts
+        self.ask_prefix = None                   # callable(addr, model, ids) -> cached tokens on that peer; None = HTTP
         self.layer_cost = {}                     # model -> what a layer costs here (POST /api/cluster/measure), published too
         self.membership = None
         self.router = None                       # cluster.routing.Router once a membership exists and routing is on
@@ -83,9 +95,22 @@ class ServerContext:
             self.router = Router(self.membership)
         expected = int(params.max_tokens or 256)
         load = float(len(llm.worker.tickets))
+        # a long prompt: who already holds how much of it goes into the estimate (each peer answers for itself)
+        prompt_tokens, local_cached, peer_cached = len(ids), 0, {}
+        if prompt_tokens >= self.settings.prefix_ask_min_tokens:
+            alloc = llm.engine.alloc
+            local_cached = len(alloc.match_prefix(list(ids), llm._salt(params))[0]) * alloc.block_size
+            for p in self.membership.alive():
+                if llm.model_id in p.models and p.tok_per_s > 0:
+                    try:
+                        peer_cached[p.node_id] = int((self.ask_prefix or _ask_prefix)(p.addr, llm.model_id, list(ids),
+                                                                                       params.cache_salt))
+                    except Exception:
+                        peer_cached[p.node_id] = 0
         try:
             c = self.router.choose(llm.model_id, expected, load, self.rate.rate, local_serves=True,
-                                   conversation=params.cache_salt)
+                                   conversation=params.cache_salt, prompt_tokens=prompt_tokens, local_cached=local_cached,
+                                   local_prefill_rate=self.prefill_rate.rate, peer_cached=peer_cached)
         except LookupError:
             return None
         return c if c.addr is not None else None
@@ -129,6 +154,7 @@ class ServerContext:
         reason = None
         self.inflight[request_id] = {"model": llm.model_id, "prompt_tokens": len(ids), "started": time.time()}
         peer = None
+        cached = 0
         try:
             peer = self._route(llm, ids, params)
             if peer is not None:
@@ -150,6 +176,7 @@ class ServerContext:
                         self.handover.observe_local(len(ids), first)
                 n_out += len(ev.token_ids)
                 reason = ev.finish_reason or reason
+                cached = max(cached, int(ev.cached_tokens or 0))
                 yield ev
         finally:
             self.gate.release(started)
@@ -157,6 +184,8 @@ class ServerContext:
             total = time.perf_counter() - t0
             if peer is None and first is not None and n_out > 1:
                 self.rate.observe(n_out - 1, total - first)         # decode rate of this node: tokens after the first
+            if peer is None and first is not None and len(ids) - cached >= 64:
+                self.prefill_rate.observe(len(ids) - cached, first)  # and the rate it read this prompt at
             self.metrics.observe_request(llm.model_id, len(ids), n_out, first, total, reason or "disconnect")
 
     def _peer_failed(self, node_id: str):

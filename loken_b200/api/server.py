@@ -88,7 +88,8 @@ def ops_router(ctx: ServerContext):
         models = ctx.registry.list()
         free = sum(m.engine.alloc.free_blocks() for m in models)
         return {"models": [m.model_id for m in models], "load": float(sum(len(m.worker.tickets) for m in models)),
-                "tok_per_s": float(ctx.rate.rate), "free_kv_blocks": int(free), "layer_cost": dict(ctx.layer_cost),
+                "tok_per_s": float(ctx.rate.rate), "prefill_tok_per_s": float(ctx.prefill_rate.rate),
+                "free_kv_blocks": int(free), "layer_cost": dict(ctx.layer_cost),
                 "card_bytes_free": int(_card_bytes_free())}
 
     def _card_bytes_free() -> int:
@@ -127,7 +128,8 @@ def ops_router(ctx: ServerContext):
         fold(m, body)
         d = _describe()
         return m.gossip_payload(f"http://{ctx.settings.host}:{ctx.settings.port}", d["models"], d["load"],
-                                d["tok_per_s"], d["free_kv_blocks"])
+                                d["tok_per_s"], d["free_kv_blocks"], d["layer_cost"], d["card_bytes_free"],
+                                d["prefill_tok_per_s"])
 
     @r.get("/api/cluster/peers")
     async def cluster_peers():

@@ -29,7 +29,7 @@ def fold(m: Membership, payload: dict):
     m.observe(payload["id"], payload.get("addr", ""), models=payload.get("models"), load=payload.get("load"),
               tok_per_s=payload.get("tok_per_s"), free_kv_blocks=payload.get("free_kv_blocks"),
               incarnation=int(payload.get("incarnation", 0)), layer_cost=payload.get("layer_cost"),
-              card_bytes_free=payload.get("card_bytes_free"))
+              card_bytes_free=payload.get("card_bytes_free"), prefill_tok_per_s=payload.get("prefill_tok_per_s"))
     return [k for k in payload.get("known", []) if k.get("id") not in m.peers and k.get("id") != m.self_id]
 
 
@@ -46,7 +46,8 @@ class GossipLoop:
     def payload(self) -> dict:
         d = self.describe()
         return self.m.gossip_payload(self.self_addr, d.get("models", []), d.get("load", 0.0), d.get("tok_per_s", 0.0),
-                                     d.get("free_kv_blocks", 0), d.get("layer_cost"), d.get("card_bytes_free", 0))
+                                     d.get("free_kv_blocks", 0), d.get("layer_cost"), d.get("card_bytes_free", 0),
+                                     d.get("prefill_tok_per_s", 0.0))
 
     def round(self):
         """One gossip round: every known address is told our state and asked for its own."""

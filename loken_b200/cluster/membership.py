@@ -59,6 +59,7 @@ class Peer:
     models: List[str] = field(default_factory=list)
     load: float = 0.0                  # running + queued requests
     tok_per_s: float = 0.0             # measured decode rate
+    prefill_tok_per_s: float = 0.0     # measured prompt-reading rate
     free_kv_blocks: int = 0
     incarnation: int = 0
     detector: PhiAccrual = None
@@ -77,7 +78,7 @@ class Membership:
         self.round = 0
 
     def observe(self, node_id: str, addr: str, *, models=None, load=None, tok_per_s=None, free_kv_blocks=None,
-                incarnation: int = 0, layer_cost=None, card_bytes_free=None):
+                incarnation: int = 0, layer_cost=None, card_bytes_free=None, prefill_tok_per_s=None):
         """A heartbeat / gossip entry about `node_id` arrived."""
         if node_id == self.self_id:
             return
@@ -99,6 +100,8 @@ class Membership:
             p.layer_cost = {str(k): dict(v) for k, v in layer_cost.items() if isinstance(v, dict)}
         if card_bytes_free is not None:
             p.card_bytes_free = int(card_bytes_free)
+        if prefill_tok_per_s is not None:
+            p.prefill_tok_per_s = float(prefill_tok_per_s)
         p.detector.heartbeat()
 
     def timed(self, node_id: str, rtt_ms: float, alpha: float = 0.3):
@@ -122,12 +125,14 @@ class Membership:
     def state(self) -> dict:
         return {"self": self.self_id, "round": self.round, "peers": [
             {"id": p.node_id, "addr": p.addr, "models": p.models, "load": p.load, "tok_per_s": p.tok_per_s,
+             "prefill_tok_per_s": p.prefill_tok_per_s,
              "phi": round(p.detector.phi(), 3), "alive": p.detector.available(), "rtt_ms": p.rtt_ms,
              "layer_cost": p.layer_cost, "card_bytes_free": p.card_bytes_free,
              "excluded": p.excluded_until_round >= self.round} for p in self.peers.values()]}
 
     def gossip_payload(self, self_addr: str, models, load, tok_per_s, free_kv_blocks, layer_cost=None,
-                       card_bytes_free: int = 0) -> dict:
+                       card_bytes_free: int = 0, prefill_tok_per_s: float = 0.0) -> dict:
         return {"id": self.self_id, "addr": self_addr, "models": list(models), "load": load, "tok_per_s": tok_per_s,
+                "prefill_tok_per_s": prefill_tok_per_s,
                 "free_kv_blocks": free_kv_blocks, "layer_cost": layer_cost or {}, "card_bytes_free": int(card_bytes_free),
                 "known": [{"id": p.node_id, "addr": p.addr, "incarnation": p.incarnation} for p in self.alive()]}

@@ -43,16 +43,30 @@ class Router:
         self.sticky: Dict[str, str] = {}        # conversation key -> node id that served it last
 
     def choose(self, model: str, expected_tokens: int, local_load: float, local_rate: float,
-               local_serves: bool = True, conversation: Optional[str] = None) -> Candidate:
+               local_serves: bool = True, conversation: Optional[str] = None, *, prompt_tokens: int = 0,
+               local_cached: int = 0, local_prefill_rate: float = 0.0,
+               peer_cached: Optional[Dict[str, int]] = None) -> Candidate:
+        """`prompt_tokens`, the tokens of it each node already holds (`local_cached`, `peer_cached`: what the peers
+        answered on `/api/cluster/prefix`) and the measured prompt-reading rates put the prefix cache into the same
+        arithmetic as everything else: a node that holds the prompt reads less of it, which is a smaller predicted
+        completion (`src/distributed/routing.rs:13-16` of the reference)."""
+        peer_cached = peer_cached or {}
+
+        def read_s(cached: int, rate: float) -> float:
+            left = max(0, prompt_tokens - cached)
+            return left / rate if rate > 0 and left > 0 else 0.0
+
         cands: List[Candidate] = []
         if local_serves:
             rate = max(local_rate, 1e-6)
-            cands.append(Candidate(self.m.self_id, None, (local_load * expected_tokens + expected_tokens) / rate,
+            eta = (local_load * expected_tokens + expected_tokens) / rate + read_s(local_cached, local_prefill_rate)
+            cands.append(Candidate(self.m.self_id, None, eta,
                                    conversation is not None and self.sticky.get(conversation) == self.m.self_id))
         for p in self.m.alive():
             if model not in p.models or p.tok_per_s <= 0:
                 continue
-            eta = (p.load * expected_tokens + expected_tokens) / p.tok_per_s + self.hop_cost_s
+            eta = ((p.load * expected_tokens + expected_tokens) / p.tok_per_s + self.hop_cost_s
+                   + read_s(peer_cached.get(p.node_id, 0), getattr(p, "prefill_tok_per_s", 0.0) or local_prefill_rate))
             cands.append(Candidate(p.node_id, p.addr, eta,
                                    conversation is not None and self.sticky.get(conversation) == p.node_id))
         if not cands:

@@ -179,3 +179,32 @@ def test_streaming_through_a_peer_that_leaves():
         text = "".join(json.loads(l[6:])["choices"][0]["delta"].get("content", "")
                        for l in r.iter_lines() if l.startswith("data: {") and json.loads(l[6:])["choices"])
     assert text == REPLY
+
+
+def test_the_prefix_cache_enters_the_routing_arithmetic():
+    from loken_b200.cluster.routing import Router
+
+    m = Membership("A")
+    m.observe("B", "http://b", models=["m"], load=0.0, tok_per_s=100.0, prefill_tok_per_s=1000.0)
+    r = Router(m)
+    # equal decode rates: the hop keeps a short request at home
+    assert r.choose("m", 100, 0.0, 100.0).addr is None
+    # a 4000-token prompt that B already holds: reading it here costs 4 s, there nothing
+    c = r.choose("m", 100, 0.0, 100.0, prompt_tokens=4000, local_cached=0, local_prefill_rate=1000.0, peer_cached={"B": 3968})
+    assert c.node_id == "B"
+    # held here instead: it stays
+    c = r.choose("m", 100, 0.0, 100.0, prompt_tokens=4000, local_cached=3968, local_prefill_rate=1000.0, peer_cached={"B": 0})
+    assert c.addr is None
+
+
+def test_long_prompts_ask_the_peers_what_they_hold():
+    cA, ctx, llmA, llmB = two_nodes()
+    ctx.membership.observe("B", "http://b:1", models=["fake-model"], load=0.0, tok_per_s=500.0, prefill_tok_per_s=1000.0)
+    asked = []
+    ctx.ask_prefix = lambda addr, model, ids, salt: asked.append((addr, model, len(ids))) or 128
+    ctx.settings.prefix_ask_min_tokens = 100
+    r = ask(cA, prompt="x" * 150)
+    assert r.status_code == 200 and asked and asked[0][:2] == ("http://b:1", "fake-model") and asked[0][2] >= 150
+    asked.clear()
+    ask(cA, prompt="short")
+    assert asked == []
