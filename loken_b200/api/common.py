@@ -173,6 +173,14 @@ def params_from_openai(body: dict, llm: LLM, chat: bool) -> GenerationParams:
             ids = llm.tokenize(variant, add_special=False)
             if ids:
                 bad_words.append(ids)
+    if body.get("prompt_logprobs") is not None:
+        raise ApiError(400, "prompt_logprobs is not offered: log-probabilities cover the answer's tokens")
+    if body.get("chat_template") is not None:
+        raise ApiError(400, "a request does not bring its own chat_template; the model's template is used")
+    if body.get("continue_final_message") and body.get("add_generation_prompt") is True:
+        raise ApiError(400, "continue_final_message and add_generation_prompt: true contradict each other")
+    if body.get("truncation_side") not in (None, "left", "right"):
+        raise ApiError(400, "truncation_side is left or right")
     p = GenerationParams(
         temperature=float(_get(body, "temperature", default=1.0)),
         top_p=float(_get(body, "top_p", default=1.0)),
@@ -196,6 +204,7 @@ def params_from_openai(body: dict, llm: LLM, chat: bool) -> GenerationParams:
         echo=bool(body.get("echo", False)),
         thinking_token_budget=body.get("thinking_token_budget"),
         truncate_prompt_tokens=body.get("truncate_prompt_tokens"),
+        truncation_side=str(body.get("truncation_side") or "left"),
         cache_salt=body.get("cache_salt"),
         context_shift=bool(body.get("context_shift", False)),
         num_keep=max(0, int(body.get("num_keep", 1))),

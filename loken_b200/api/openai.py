@@ -30,21 +30,24 @@ def _sse(obj) -> bytes:
     return b"data: " + json.dumps(obj, ensure_ascii=False).encode() + b"\n\n"
 
 
-def _lp_chat(llm, toks: List[int], lps) -> dict:
+def _lp_chat(llm, toks: List[int], lps, as_ids: bool = False) -> dict:
+    """`as_ids` (`return_tokens_as_token_ids`): each token is written `token_id:<id>`, which survives tokens
+    that are not valid text on their own."""
+    name = (lambda i: f"token_id:{i}") if as_ids else (lambda i: llm.detokenize([i], skip_special=False))
     content = []
     for t, (lp, top) in zip(toks, lps or []):
         piece = llm.detokenize([t], skip_special=False)
-        content.append({"token": piece, "logprob": lp, "bytes": list(piece.encode()),
-                        "top_logprobs": [{"token": llm.detokenize([i], skip_special=False), "logprob": l,
+        content.append({"token": name(t), "logprob": lp, "bytes": list(piece.encode()),
+                        "top_logprobs": [{"token": name(i), "logprob": l,
                                           "bytes": list(llm.detokenize([i], skip_special=False).encode())}
                                          for i, l in top]})
     return {"content": content}
 
 
-def _lp_text(llm, toks: List[int], lps) -> dict:
-    pieces = [llm.detokenize([t], skip_special=False) for t in toks]
-    return {"tokens": pieces, "token_logprobs": [lp for lp, _ in (lps or [])],
-            "top_logprobs": [{llm.detokenize([i], skip_special=False): l for i, l in top} for _, top in (lps or [])],
+def _lp_text(llm, toks: List[int], lps, as_ids: bool = False) -> dict:
+    name = (lambda i: f"token_id:{i}") if as_ids else (lambda i: llm.detokenize([i], skip_special=False))
+    return {"tokens": [name(t) for t in toks], "token_logprobs": [lp for lp, _ in (lps or [])],
+            "top_logprobs": [{name(i): l for i, l in top} for _, top in (lps or [])],
             "text_offset": []}
 
 
@@ -165,6 +168,8 @@ def router(ctx: ServerContext) -> APIRouter:
         params = params_from_openai(body, llm, chat=True)
         tools = body.get("tools") if body.get("tool_choice") != "none" else None
         kw = dict(body.get("chat_template_kwargs") or {})
+        if body.get("documents") is not None:
+            kw["documents"] = body["documents"]           # a variable of the model's template (retrieval-style templates read it)
         ids = await run_in_threadpool(
             llm.prompt_ids, None, body["messages"], tools, params,
             add_generation_prompt=body.get("add_generation_prompt", True),
@@ -235,7 +240,7 @@ def router(ctx: ServerContext) -> APIRouter:
                                 delta = {"content": text}
                                 ch = {"index": 0, "delta": delta, "finish_reason": None}
                                 if ev.logprobs and params.logprobs:
-                                    ch["logprobs"] = _lp_chat(llm, ev.token_ids, ev.logprobs)
+                                    ch["logprobs"] = _lp_chat(llm, ev.token_ids, ev.logprobs, bool(body.get("return_tokens_as_token_ids")))
                                 yield _sse({**base, "choices": [ch]})
                         if ev.finished:
                             reason = ev.finish_reason
@@ -295,7 +300,7 @@ def router(ctx: ServerContext) -> APIRouter:
                 ch = {"index": idx, "message": msg,
                       "finish_reason": "tool_calls" if calls else ("length" if reason == "length" else "stop")}
                 if params.logprobs:
-                    ch["logprobs"] = _lp_chat(llm, toks, lps)
+                    ch["logprobs"] = _lp_chat(llm, toks, lps, bool(body.get("return_tokens_as_token_ids")))
                 choices.append(ch)
                 total_out += len(toks)
             return {"id": rid, "object": "chat.completion", "created": created, "model": llm.model_id,
@@ -365,7 +370,7 @@ def router(ctx: ServerContext) -> APIRouter:
                         ch = {"index": 0, "text": ev.text,
                               "finish_reason": None if not ev.finished else ("length" if reason == "length" else "stop")}
                         if params.logprobs and ev.logprobs:
-                            ch["logprobs"] = _lp_text(llm, ev.token_ids, ev.logprobs)
+                            ch["logprobs"] = _lp_text(llm, ev.token_ids, ev.logprobs, bool(body.get("return_tokens_as_token_ids")))
                         yield _sse({**base, "choices": [ch]})
                 if (body.get("stream_options") or {}).get("include_usage"):
                     yield _sse({**base, "choices": [], "usage": Usage(len(ids), n_out).openai()})
@@ -391,7 +396,7 @@ def router(ctx: ServerContext) -> APIRouter:
                     ch = {"index": len(choices), "text": text,
                           "finish_reason": "length" if reason == "length" else "stop"}
                     if params.logprobs:
-                        ch["logprobs"] = _lp_text(llm, toks, lps)
+                        ch["logprobs"] = _lp_text(llm, toks, lps, bool(body.get("return_tokens_as_token_ids")))
                     choices.append(ch)
                     n_out += len(toks)
                 n_in += len(ids)

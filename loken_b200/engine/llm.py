@@ -35,7 +35,8 @@ class GenerationParams(SamplingParams):
     skip_special_tokens: bool = True
     echo: bool = False
     thinking_token_budget: Optional[int] = None
-    truncate_prompt_tokens: Optional[int] = None
+    truncate_prompt_tokens: Optional[int] = None   # -1: the model's window
+    truncation_side: str = "left"                  # left keeps the last tokens, right the first
     cache_salt: Optional[str] = None
 
 
@@ -402,7 +403,10 @@ class LLM:
         else:
             ids = [int(t) for t in (prompt or [])]
         if params is not None and params.truncate_prompt_tokens:
-            ids = ids[-params.truncate_prompt_tokens:]
+            keep = params.truncate_prompt_tokens
+            if keep < 0:
+                keep = max(1, self.engine.max_ctx - 1 - int(params.max_tokens or 1))
+            ids = ids[:keep] if params.truncation_side == "right" else ids[-keep:]
         bad = [t for t in ids if not (0 <= t < self.cfg.vocab)]
         if bad:
             raise ValueError(f"token id {bad[0]} is outside the model's vocabulary of {self.cfg.vocab}")

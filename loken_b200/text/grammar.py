@@ -36,8 +36,44 @@ def spec_from_request(body: dict) -> Optional[Tuple[str, object]]:
         if src is not None:
             if kind == "json_schema" and isinstance(src, str):
                 src = json.loads(src)
+            if kind == "json_schema":
+                src = _json_options(src, so, body)
             return kind, src
+    if so.get("json_object"):
+        return "json_schema", _json_options({"type": "object"}, so, body)
     return None
+
+
+def _json_options(schema, so: dict, body: dict):
+    """vLLM's options of a JSON constraint, as the matcher's own schema annotations: `disable_any_whitespace`
+    (no whitespace between tokens of the JSON), `whitespace_pattern` / `guided_whitespace_pattern` (a regular
+    expression for what may stand there) and `disable_additional_properties` (every object of the schema that
+    does not say otherwise is closed)."""
+    if not isinstance(schema, dict):
+        return schema
+    ws = so.get("whitespace_pattern") or body.get("guided_whitespace_pattern")
+    if not (so.get("disable_any_whitespace") or so.get("disable_additional_properties") or ws):
+        return schema
+    schema = json.loads(json.dumps(schema))              # the request's own object is left as sent
+    xg = dict(schema.get("x-guidance") or {})
+    if so.get("disable_any_whitespace"):
+        xg["whitespace_flexible"] = False
+    if ws:
+        xg["whitespace_pattern"] = str(ws)
+    if xg:
+        schema["x-guidance"] = xg
+    if so.get("disable_additional_properties"):
+        def close(node):
+            if isinstance(node, dict):
+                if (node.get("type") == "object" or "properties" in node) and "additionalProperties" not in node:
+                    node["additionalProperties"] = False
+                for v in node.values():
+                    close(v)
+            elif isinstance(node, list):
+                for v in node:
+                    close(v)
+        close(schema)
+    return schema
 
 
 class _VocabAdapter:

@@ -508,3 +508,41 @@ def test_prefill_peer_is_asked_for_long_prompts_and_failures_fall_back():
     ctx.handover.peer_rate, ctx.handover.local_rate = 2.0, 1.0      # the peer looks faster: it is asked again
     r = c.post("/v1/completions", json={"prompt": "another prompt that is long enough", "max_tokens": 2})
     assert r.status_code == 200 and "loken_prefill_peer_failures_total 1" in c.get("/metrics").text
+
+
+def test_vllm_extension_fields_small_print():
+    c, reg = client()
+    base = {"model": "fake-model", "messages": [{"role": "user", "content": "hi"}]}
+    assert c.post("/v1/chat/completions", json=dict(base, prompt_logprobs=1)).status_code == 400
+    assert c.post("/v1/chat/completions", json=dict(base, chat_template="{{ x }}")).status_code == 400
+    assert c.post("/v1/chat/completions", json=dict(base, continue_final_message=True, add_generation_prompt=True)).status_code == 400
+    assert c.post("/v1/completions", json={"prompt": "x", "truncation_side": "middle"}).status_code == 400
+    # log-probabilities by token id
+    r = c.post("/v1/chat/completions", json=dict(base, logprobs=True, top_logprobs=2, return_tokens_as_token_ids=True, max_tokens=3))
+    lp = r.json()["choices"][0]["logprobs"]["content"]
+    assert lp[0]["token"] == f"token_id:{ord('H')}" and lp[0]["top_logprobs"][1]["token"] == "token_id:32"
+    r = c.post("/v1/completions", json={"prompt": "x", "logprobs": 1, "return_tokens_as_token_ids": True, "max_tokens": 2})
+    assert r.json()["choices"][0]["logprobs"]["tokens"][0] == f"token_id:{ord('H')}"
+    # truncation: the last tokens by default, the first with side right, the window with -1
+    eng = reg.get(None).engine
+    c.post("/v1/completions", json={"prompt": "abcdefghij", "truncate_prompt_tokens": 4, "max_tokens": 1})
+    c.post("/v1/completions", json={"prompt": "abcdefghij", "truncate_prompt_tokens": 4, "truncation_side": "right", "max_tokens": 1})
+    c.post("/v1/completions", json={"prompt": "a" * 600, "truncate_prompt_tokens": -1, "max_tokens": 10})
+    left, right, window = eng.prompts[-3:]
+    assert len(left) == 4 and len(right) == 4 and left != right and len(window) == eng.max_ctx - 1 - 10
+
+
+def test_json_constraint_options():
+    from loken_b200.text.grammar import spec_from_request
+
+    schema = {"type": "object", "properties": {"a": {"type": "object", "properties": {"b": {"type": "integer"}}},
+                                               "open": {"type": "object", "additionalProperties": True}}}
+    kind, got = spec_from_request({"structured_outputs": {"json": schema, "disable_any_whitespace": True,
+                                                          "disable_additional_properties": True}})
+    assert kind == "json_schema" and got["x-guidance"]["whitespace_flexible"] is False
+    assert got["additionalProperties"] is False and got["properties"]["a"]["additionalProperties"] is False
+    assert got["properties"]["open"]["additionalProperties"] is True and "x-guidance" not in schema
+    kind, got = spec_from_request({"guided_json": '{"type": "object"}', "guided_whitespace_pattern": "[ ]?"})
+    assert got["x-guidance"]["whitespace_pattern"] == "[ ]?"
+    assert spec_from_request({"structured_outputs": {"json_object": True}}) == ("json_schema", {"type": "object"})
+    assert spec_from_request({"structured_outputs": {"json": schema}})[1] is schema
