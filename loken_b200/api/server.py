@@ -159,11 +159,13 @@ def ops_router(ctx: ServerContext):
         ids = [int(t) for t in prompt] if isinstance(prompt, list) else llm.tokenize(str(prompt))
         if not ids:
             return {"cached_tokens": 0}
+        # a cached prompt belongs to the key that wrote it: the answer covers the caller's own scope only
+        scope = body.get("cache_salt") or (("key:" + req.state.api_key) if getattr(req.state, "api_key", None) else None)
         salt = 0
-        if body.get("cache_salt"):
+        if scope:
             from ..engine.llm import GenerationParams
 
-            salt = llm._salt(GenerationParams(cache_salt=str(body["cache_salt"])))
+            salt = llm._salt(GenerationParams(cache_salt=str(scope)))
         alloc = llm.engine.alloc
         return {"cached_tokens": len(alloc.match_prefix(ids, salt)[0]) * alloc.block_size, "prompt_tokens": len(ids)}
 
