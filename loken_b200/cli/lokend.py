@@ -100,7 +100,8 @@ def serve(cfg, requant=None) -> int:
     llm = LLM.load(i.model, model_id=i.model_id, requant=requant, kv_format=cfg.kv_format, tp_rank=rank,
                    tp_size=world, comm=comm, max_seqs=i.max_seqs, max_ctx=i.max_ctx,
                    max_prefill_tokens=i.max_prefill_tokens, lora=i.lora, expert_slots=i.expert_slots,
-                   kv_disk_dir=i.kv_disk_dir if world == 1 else None,
+                   kv_disk_dir=i.kv_disk_dir if world == 1 else None, kv_disk_host_mb=i.kv_disk_host_mb,
+                   kv_disk_max_gb=i.kv_disk_max_gb,
                    **({"draft": (i.draft_model, i.draft_k)} if (i.draft_model and world > 1) else {}))
     if i.draft_model and world == 1:
         from ..serve.speculative import attach_draft

@@ -7,7 +7,7 @@ the reference derives from measurement and a B200 node wants stated):
                  max_body_mb, request_timeout_s
     [inference]  model_id, model (GGUF path or built-in shape), replicas, tp, tp_sum, ep, pp, dp, fidelity
                  (reference | balanced | fast), kv_format, max_seqs, max_ctx, max_prefill_tokens,
-                 kv_disk_dir, prefill_peer, draft_model, draft_k, lora, models_dir, expert_slots
+                 kv_disk_dir, kv_disk_host_mb, kv_disk_max_gb, prefill_peer, draft_model, draft_k, lora, models_dir, expert_slots
     [energy]     enabled, grid_g_co2_per_kwh
     [cluster]    node_id, listen, peers, heartbeat_ms, suspect_phi, name, discovery, route_requests, resume_unverified
 
@@ -66,7 +66,9 @@ class InferenceSection:
     max_seqs: int = 256
     max_ctx: int = 8192
     max_prefill_tokens: int = 8192
-    kv_disk_dir: Optional[str] = None
+    kv_disk_dir: Optional[str] = None     # finished conversations' cache blocks are kept here and found again after a restart
+    kv_disk_host_mb: int = 256            # of which the most recently used stay in host memory as well
+    kv_disk_max_gb: float = 0.0           # the directory is trimmed to this size, oldest blocks first (0: no bound)
     prefill_peer: Optional[str] = None
     draft_model: Optional[str] = None
     lora: Optional[str] = None         # PEFT adapter directory merged into the checkpoint at load
