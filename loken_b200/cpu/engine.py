@@ -121,7 +121,10 @@ class CpuModel:
                  seed: Optional[int] = None, eos: Sequence[int] = ()) -> dict:
         """Greedy or temperature / top-k sampling on the host; returns tokens and timings."""
         self.reset()
-        rng = random.Random(seed)
+        # the draw for token N depends on (seed, N) alone, as on the device path (serve/replay.py)
+        from ..serve.replay import PositionRng
+
+        rng = PositionRng(seed if seed is not None else random.SystemRandom().getrandbits(63))
         t0 = time.perf_counter()
         logits = self.prefill(list(prompt))
         t1 = time.perf_counter()
