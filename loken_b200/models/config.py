@@ -27,6 +27,7 @@ ARCH_FACTS: Dict[str, dict] = {
     "olmoe": dict(rope_pairing=1, router="softmax", renorm=False, qk_norm=True, qk_norm_wide=True),
     "phi3": dict(rope_pairing=1),
     "granite": dict(rope_pairing=0),
+    "granitemoe": dict(rope_pairing=0, router="softmax_topk", renorm=True),
 }
 
 
@@ -201,7 +202,7 @@ class ModelConfig:
                   embedding_scale=float(g("embedding_scale", 1.0) or 1.0),
                   logit_scale=float(g("logit_scale", 1.0) or 1.0), attn_scale=g("attention.scale"),
                   qk_norm_wide=facts.get("qk_norm_wide", False))
-        if arch == "granite" and cfg.logit_scale not in (0.0, 1.0):
+        if arch in ("granite", "granitemoe") and cfg.logit_scale not in (0.0, 1.0):
             cfg.logit_scale = 1.0 / cfg.logit_scale           # these files store the divisor of the logits
         pat = g("attention.sliding_window_pattern")
         if isinstance(pat, list):

@@ -192,7 +192,7 @@ def load_gguf(path: str, device, *, tp_rank: int = 0, tp_size: int = 1, ep_rank:
                       tp_rank * vl if tp_size > 1 else 0)
     mw.layer_range = tuple(layer_range) if layer_range is not None else None
     # Granite: every block's output is multiplied before it joins the residual stream; folded into the weights
-    res_mul = float(meta.get(f"{cfg.arch}.residual_scale", 1.0) or 1.0) if cfg.arch == "granite" else 1.0
+    res_mul = float(meta.get(f"{cfg.arch}.residual_scale", 1.0) or 1.0) if cfg.arch in ("granite", "granitemoe") else 1.0
     for il in range(cfg.n_layers):
         if layer_range is not None and not (layer_range[0] <= il < layer_range[1]):
             mw.layers.append(None)
@@ -226,7 +226,7 @@ def load_gguf(path: str, device, *, tp_rank: int = 0, tp_size: int = 1, ep_rank:
         if sk is not None:
             lw.sinks = sk[tp_rank * nql:(tp_rank + 1) * nql].contiguous()
         if cfg.is_moe and has(p + "ffn_gate_exps.weight"):
-            lw.moe = _load_moe(r, cfg, p, device, ep_rank, ep_size, requant)
+            lw.moe = _load_moe(r, cfg, p, device, ep_rank, ep_size, requant, res_mul)
         else:
             I = cfg.intermediate
             il_ = I // tp_size
@@ -245,7 +245,7 @@ def load_gguf(path: str, device, *, tp_rank: int = 0, tp_size: int = 1, ep_rank:
 
 
 def _load_moe(r: G.GGUFReader, cfg: ModelConfig, p: str, device, ep_rank: int, ep_size: int,
-              requant: Optional[str]) -> MoeWeights:
+              requant: Optional[str], out_mul: float = 1.0) -> MoeWeights:
     E, H, I = cfg.n_experts, cfg.hidden, cfg.expert_intermediate
     ecnt = E // ep_size
     elo = ep_rank * ecnt
@@ -257,14 +257,14 @@ def _load_moe(r: G.GGUFReader, cfg: ModelConfig, p: str, device, ep_rank: int, e
     for e in range(elo, elo + ecnt):
         parts_gu += [(g, slice(e * I, (e + 1) * I)), (u, slice(e * I, (e + 1) * I))]
     gu = _linear_from(parts_gu, device, requant)
-    dn = _linear_from([(d, slice(elo * H, (elo + ecnt) * H))], device, requant)
+    dn = _scale_linear(_linear_from([(d, slice(elo * H, (elo + ecnt) * H))], device, requant), out_mul)   # Granite's residual multiplier
     gub = dnb = None
     if (p + "ffn_gate_exps.bias") in r.tensors:
         bg = r.tensors[p + "ffn_gate_exps.bias"].to_float().reshape(E, I)[elo:elo + ecnt]
         bu = r.tensors[p + "ffn_up_exps.bias"].to_float().reshape(E, I)[elo:elo + ecnt]
         gub = torch.from_numpy(np.concatenate([bg, bu], 1)).to(device).contiguous()
         dnb = torch.from_numpy(r.tensors[p + "ffn_down_exps.bias"].to_float().reshape(E, H)[elo:elo + ecnt].copy()
-                               ).to(device)
+                               ).to(device) * out_mul
     fmt = "bf16" if gu.kind == "bf16" else QUANT_TYPES.get(gu.weight.ggml_type, "gguf")
     return MoeWeights(router_w, router_b, gu.weight, dn.weight, gub, dnb, elo, ecnt, fmt)
 

@@ -23,7 +23,7 @@ from .weights import LayerWeights, Linear, ModelWeights, make_linear
 HF_ARCH = {"LlamaForCausalLM": "llama", "MistralForCausalLM": "mistral", "Qwen2ForCausalLM": "qwen2",
            "Qwen3ForCausalLM": "qwen3", "GptOssForCausalLM": "gpt-oss", "MixtralForCausalLM": "mixtral",
            "Qwen3MoeForCausalLM": "qwen3moe", "Phi3ForCausalLM": "phi3", "GraniteForCausalLM": "granite",
-           "OlmoeForCausalLM": "olmoe"}
+           "OlmoeForCausalLM": "olmoe", "GraniteMoeForCausalLM": "granitemoe"}
 # mixture families that store one tensor per expert and matrix: (router, expert stem, gate, up, down)
 HF_EXPERT_NAMES = {
     "mixtral": ("block_sparse_moe.gate", "block_sparse_moe.experts.{e}.", "w1", "w3", "w2"),
@@ -98,7 +98,7 @@ def config_from_hf(cfg: dict, name: str = "hf") -> ModelConfig:
         if f is None:
             f = math.sqrt(1.0 + math.log(ctx / orig) / math.log(orig)) if ctx > orig else 1.0
         sc = RopeScaling(kind="none", attn_factor=float(f))
-    if arch == "granite":
+    if arch in ("granite", "granitemoe"):
         # four multipliers: on the embeddings, on the attention scores (instead of 1 / sqrt(head_dim)), on every
         # block's output before it joins the residual stream (folded into the o and down projections at load),
         # and a divisor of the logits
@@ -108,6 +108,10 @@ def config_from_hf(cfg: dict, name: str = "hf") -> ModelConfig:
     if cfg.get("partial_rotary_factor") not in (None, 1.0):
         extra["rope_dim"] = int(float(cfg["partial_rotary_factor"]) * int(cfg.get("head_dim") or hidden // n_q))
     moe = extra
+    if arch == "granitemoe":
+        # the k best router logits are chosen first and the softmax runs over those alone
+        moe = dict(extra, n_experts=int(cfg["num_local_experts"]), top_k=int(cfg.get("num_experts_per_tok", 2)),
+                   expert_intermediate=int(cfg["intermediate_size"]), router="softmax_topk", renorm=True)
     if arch in HF_EXPERT_NAMES:
         # softmax over all experts, the best k kept (and, unless the file says otherwise, renormalised)
         n_exp = int(cfg.get("num_local_experts") or cfg.get("num_experts"))
@@ -420,7 +424,7 @@ def load_hf(directory: str, device, *, tp_rank: int = 0, tp_size: int = 1, requa
                       tp_rank * vl if tp_size > 1 else 0)
 
     # Granite: every block's output is multiplied before it joins the residual stream; folded into the weights
-    res_mul = float(hf.get("residual_multiplier", 1.0) or 1.0) if cfg.arch == "granite" else 1.0
+    res_mul = float(hf.get("residual_multiplier", 1.0) or 1.0) if cfg.arch in ("granite", "granitemoe") else 1.0
 
     def linear(stems, rows, col=None, bias=None, mul: float = 1.0):
         if requant is None and tp_size == 1 and col is None and mul == 1.0 and sh.has(stems[0] + ".qweight"):
@@ -477,6 +481,22 @@ def load_hf(directory: str, device, *, tp_rank: int = 0, tp_size: int = 1, requa
             lw.moe = MoeWeights(sh.get(m + "router.weight").to(device).bfloat16(),
                                 vec(m + "router.bias") if sh.has(m + "router.bias") else None,
                                 gu, dn, gub, dnb, elo, ecnt, fmt)
+        elif cfg.is_moe and sh.has(p + "block_sparse_moe.input_linear.weight"):
+            # Granite's mixture: experts stacked in two tensors, [E, 2I, H] (gate rows, then up rows) and [E, H, I];
+            # the residual multiplier is folded into the down projections like into the dense ones
+            from ..ops import quant as Q
+            from .moe import MoeWeights
+
+            ecnt = cfg.n_experts // tp_size
+            elo = tp_rank * ecnt
+            b = p + "block_sparse_moe."
+            gu = sh.get(b + "input_linear.weight")[elo:elo + ecnt].float()
+            dn = sh.get(b + "output_linear.weight")[elo:elo + ecnt].float() * res_mul
+            gu, dn = gu.reshape(-1, gu.shape[-1]), dn.reshape(-1, dn.shape[-1])
+            fmt = requant if requant in ("mxfp4", "q8_0", "q4_k", "q6_k") else "bf16"
+            conv = (lambda w: w.to(device).bfloat16()) if fmt == "bf16" else (lambda w: Q.quantize_weight(w.to(device), fmt))
+            lw.moe = MoeWeights(sh.get(b + "router.layer.weight").to(device).bfloat16(), None, conv(gu), conv(dn), None, None,
+                                elo, ecnt, fmt)
         elif cfg.is_moe and cfg.arch in HF_EXPERT_NAMES:
             ecnt = cfg.n_experts // tp_size
             lw.moe = _stacked_experts(sh, p, cfg, tp_rank * ecnt, ecnt, device, requant)

@@ -40,6 +40,11 @@ def _tiny(cls_name):
     if cls_name == "Granite":
         return (transformers.GraniteConfig(**c, embedding_multiplier=6.0, attention_multiplier=0.1, residual_multiplier=0.4,
                                            logits_scaling=3.0), transformers.GraniteForCausalLM)
+    if cls_name == "GraniteMoe":
+        # the four multipliers of Granite over a mixture whose softmax runs over the chosen logits only
+        return (transformers.GraniteMoeConfig(**c, num_local_experts=4, num_experts_per_tok=2, embedding_multiplier=6.0,
+                                              attention_multiplier=0.1, residual_multiplier=0.4, logits_scaling=3.0),
+                transformers.GraniteMoeForCausalLM)
     if cls_name == "Olmoe":
         # the q / k norm runs over all heads of a token; routing weights are not renormalised
         return (transformers.OlmoeConfig(**c, num_experts=8, num_experts_per_tok=2, norm_topk_prob=False),
@@ -66,7 +71,7 @@ def _tiny(cls_name):
 
 
 @pytest.mark.parametrize("family", ["Llama", "Mistral", "Qwen2", "Qwen3", "Mixtral", "Qwen3Moe", "GptOss", "Llama3Rope",
-                                    "Qwen3Yarn", "Phi3", "Phi3Long", "Granite", "Olmoe"])
+                                    "Qwen3Yarn", "Phi3", "Phi3Long", "Granite", "Olmoe", "GraniteMoe"])
 def test_logits_match_transformers(tmp_path, family):
     from loken_b200.models import loader_hf
     from loken_b200.models.reference import forward_ref
@@ -82,7 +87,7 @@ def test_logits_match_transformers(tmp_path, family):
                 p.add_(torch.randn_like(p) * 0.05)
     model.save_pretrained(str(tmp_path), safe_serialization=True)
     w, hf = loader_hf.load_hf(str(tmp_path), torch.device("cpu"))
-    assert w.cfg.is_moe == (family in ("Mixtral", "Qwen3Moe", "GptOss", "Olmoe"))
+    assert w.cfg.is_moe == (family in ("Mixtral", "Qwen3Moe", "GptOss", "Olmoe", "GraniteMoe"))
     # (Phi-3's long-context files switch to their long divisors once a sequence is longer than the trained length;
     # the loader picks the list for the configured context, so that case runs a sequence beyond that length)
     n_tok = 80 if family == "Phi3Long" else 40
