@@ -23,7 +23,13 @@ from .weights import LayerWeights, Linear, ModelWeights, make_linear
 HF_ARCH = {"LlamaForCausalLM": "llama", "MistralForCausalLM": "mistral", "Qwen2ForCausalLM": "qwen2",
            "Qwen3ForCausalLM": "qwen3", "GptOssForCausalLM": "gpt-oss", "MixtralForCausalLM": "mixtral",
            "Qwen3MoeForCausalLM": "qwen3moe", "Phi3ForCausalLM": "phi3", "GraniteForCausalLM": "granite",
-           "OlmoeForCausalLM": "olmoe", "GraniteMoeForCausalLM": "granitemoe"}
+           "OlmoeForCausalLM": "olmoe", "GraniteMoeForCausalLM": "granitemoe",
+           # families that are one of the above in every respect the engine sees (checked against transformers):
+           # GLM = fused gate / up, partial rotary, q / k / v biases; ERNIE 4.5 and Helium = Llama; Seed-OSS = Qwen2
+           "GlmForCausalLM": "phi3", "Ernie4_5ForCausalLM": "llama", "HeliumForCausalLM": "llama",
+           "SeedOssForCausalLM": "qwen2"}
+# of which these rotate adjacent lanes (2i, 2i+1) instead of the half-split pairs the library layout usually means
+HF_ADJACENT_ROPE = {"GlmForCausalLM", "Ernie4_5ForCausalLM", "HeliumForCausalLM"}
 # mixture families that store one tensor per expert and matrix: (router, expert stem, gate, up, down)
 HF_EXPERT_NAMES = {
     "mixtral": ("block_sparse_moe.gate", "block_sparse_moe.experts.{e}.", "w1", "w3", "w2"),
@@ -397,8 +403,8 @@ def load_hf(directory: str, device, *, tp_rank: int = 0, tp_size: int = 1, requa
         with open(os.path.join(directory, "config.json")) as f:
             hf = json.load(f)
     cfg = config_from_hf(hf, os.path.basename(os.path.normpath(directory)))
-    if native:
-        cfg.rope_pairing = 0        # the vendor's own files keep q / k rows in adjacent-pair order
+    if native or (hf.get("architectures") or [""])[0] in HF_ADJACENT_ROPE:
+        cfg.rope_pairing = 0        # the vendor's own files, and these families, keep q / k rows in adjacent-pair order
     if kv_format:
         cfg.kv_format = kv_format
     if requant and not cfg.is_moe:

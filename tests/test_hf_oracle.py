@@ -40,6 +40,14 @@ def _tiny(cls_name):
     if cls_name == "Granite":
         return (transformers.GraniteConfig(**c, embedding_multiplier=6.0, attention_multiplier=0.1, residual_multiplier=0.4,
                                            logits_scaling=3.0), transformers.GraniteForCausalLM)
+    if cls_name == "Glm":            # fused gate / up, half of each head rotated, adjacent pairs, biases on q / k / v
+        return transformers.GlmConfig(**c, head_dim=16, pad_token_id=0), transformers.GlmForCausalLM
+    if cls_name == "Ernie45":
+        return transformers.Ernie4_5Config(**c, pad_token_id=0), transformers.Ernie4_5ForCausalLM
+    if cls_name == "Helium":
+        return transformers.HeliumConfig(**c, head_dim=16, pad_token_id=0), transformers.HeliumForCausalLM
+    if cls_name == "SeedOss":
+        return transformers.SeedOssConfig(**c, head_dim=16, pad_token_id=0), transformers.SeedOssForCausalLM
     if cls_name == "GraniteMoe":
         # the four multipliers of Granite over a mixture whose softmax runs over the chosen logits only
         return (transformers.GraniteMoeConfig(**c, num_local_experts=4, num_experts_per_tok=2, embedding_multiplier=6.0,
@@ -71,7 +79,7 @@ def _tiny(cls_name):
 
 
 @pytest.mark.parametrize("family", ["Llama", "Mistral", "Qwen2", "Qwen3", "Mixtral", "Qwen3Moe", "GptOss", "Llama3Rope",
-                                    "Qwen3Yarn", "Phi3", "Phi3Long", "Granite", "Olmoe", "GraniteMoe"])
+                                    "Qwen3Yarn", "Phi3", "Phi3Long", "Granite", "Olmoe", "GraniteMoe", "Glm", "Ernie45", "Helium", "SeedOss"])
 def test_logits_match_transformers(tmp_path, family):
     from loken_b200.models import loader_hf
     from loken_b200.models.reference import forward_ref
