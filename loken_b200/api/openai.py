@@ -357,7 +357,7 @@ def router(ctx: ServerContext) -> APIRouter:
 
             def gen():
                 base = {"id": rid, "object": "text_completion", "created": created, "model": llm.model_id}
-                n_out, reason = 0, None
+                n_out, reason, figs, cached = 0, None, None, 0
                 if params.echo and isinstance(prompts[0], str):
                     yield _sse({**base, "choices": [{"index": 0, "text": prompts[0], "finish_reason": None}]})
                 for ev in ctx.run(llm, ids, params, request_id=rid, scope=scope):
@@ -366,6 +366,7 @@ def router(ctx: ServerContext) -> APIRouter:
                         break
                     n_out += len(ev.token_ids)
                     reason = ev.finish_reason or reason
+                    figs, cached = ev.figures or figs, max(cached, int(ev.cached_tokens or 0))
                     if ev.text or ev.finished:
                         ch = {"index": 0, "text": ev.text,
                               "finish_reason": None if not ev.finished else ("length" if reason == "length" else "stop")}
@@ -373,14 +374,17 @@ def router(ctx: ServerContext) -> APIRouter:
                             ch["logprobs"] = _lp_text(llm, ev.token_ids, ev.logprobs, bool(body.get("return_tokens_as_token_ids")))
                         yield _sse({**base, "choices": [ch]})
                 if (body.get("stream_options") or {}).get("include_usage"):
-                    yield _sse({**base, "choices": [], "usage": Usage(len(ids), n_out).openai()})
+                    yield _sse({**base, "choices": [], "usage": Usage(len(ids), n_out, cached, figures=figs).openai()})
                 yield b"data: [DONE]\n\n"
 
             return StreamingResponse(iterate_in_threadpool(gen()), media_type="text/event-stream",
                                      headers={"x-request-id": rid})
 
         def run_all():
+            from ..utils.figures import sum_figures
+
             choices, n_in, n_out = [], 0, 0
+            fig_parts, cached = [], 0
             for pi, ids in enumerate(id_lists):
                 for k in range(params.n):
                     text, toks, lps, reason = "", [], [], None
@@ -391,6 +395,9 @@ def router(ctx: ServerContext) -> APIRouter:
                         toks += ev.token_ids
                         lps += ev.logprobs or []
                         reason = ev.finish_reason or reason
+                        cached = max(cached, int(ev.cached_tokens or 0))
+                        if ev.figures:
+                            fig_parts.append(ev.figures)
                     if params.echo and isinstance(prompts[pi], str):
                         text = prompts[pi] + text
                     ch = {"index": len(choices), "text": text,
@@ -401,7 +408,7 @@ def router(ctx: ServerContext) -> APIRouter:
                     n_out += len(toks)
                 n_in += len(ids)
             return {"id": rid, "object": "text_completion", "created": created, "model": llm.model_id,
-                    "choices": choices, "usage": Usage(n_in, n_out).openai()}
+                    "choices": choices, "usage": Usage(n_in, n_out, cached, figures=sum_figures(fig_parts)).openai()}
 
         return JSONResponse(await run_in_threadpool(run_all), headers={"x-request-id": rid})
 

@@ -169,8 +169,13 @@ class RemoteTicket:
                     raise PeerFailed(str(line["error"]))
                 toks = [int(t) for t in line.get("t", [])]
                 lp = [(float(a), [(int(t), float(l)) for t, l in top]) for a, top in line["lp"]] if line.get("lp") else None
+                fig = line.get("fig")
+                if isinstance(fig, dict):
+                    # what a request cost is what every node spent on it: the figures say who answered
+                    # (reference: `src/distributed/evidence.rs:1-24`, per-node cost of one request)
+                    fig = dict(fig, nodes=[{"node": self.peer_node or self.peer, "role": "answered", "tokens": len(self.emitted) + len(toks)}])
                 so = StepOutput(-1, toks, bool(line.get("fin")), line.get("reason"), lp,
-                                figures=line.get("fig"), cached_tokens=int(line.get("cached", 0)))
+                                figures=fig, cached_tokens=int(line.get("cached", 0)))
                 self.emitted += toks
                 self.events.put(so)
                 if so.finished:
@@ -202,11 +207,24 @@ class RemoteTicket:
             return
         p2 = dataclasses.replace(p, max_tokens=left, resume_position=p.resume_position + len(self.emitted),
                                  min_tokens=max(0, p.min_tokens - len(self.emitted)))
+        n_peer = len(self.emitted)
+
+        def relay(ev):
+            if not isinstance(ev, Exception):
+                self.emitted += list(ev.new_tokens)
+            # the last local event carries the figures: they name both nodes and what each wrote
+            fig = getattr(ev, "figures", None)
+            if isinstance(fig, dict):
+                ev.figures = dict(fig, nodes=[{"node": self.peer_node or self.peer, "role": "left", "tokens": n_peer},
+                                              {"node": "self", "role": "continued", "tokens": len(self.emitted) - n_peer}],
+                                  taken_back=self.taken_back)
+            self.events.put(ev)
+
         with self._lock:
             if self._cancelled:
                 return
             try:
-                self.local = self.llm.submit(self.prompt_ids + self.emitted, p2, on_event=self.events.put)
+                self.local = self.llm.submit(self.prompt_ids + self.emitted, p2, on_event=relay)
             except Exception as e:
                 self.events.put(e)
                 return

@@ -88,6 +88,10 @@ def sum_figures(parts: List[dict]) -> dict:
                 e["share"] = "work"
         if "kv" in p:
             out["kv"] = p["kv"]
+        if p.get("nodes"):                    # a generation a peer answered, or left and this node continued
+            out.setdefault("nodes", []).extend(p["nodes"])
+        if p.get("taken_back"):
+            out["taken_back"] = p["taken_back"]
     return out
 
 

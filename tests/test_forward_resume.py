@@ -208,3 +208,16 @@ def test_long_prompts_ask_the_peers_what_they_hold():
     asked.clear()
     ask(cA, prompt="short")
     assert asked == []
+
+
+def test_figures_name_the_nodes_that_wrote_the_answer():
+    cA, ctx, llmA, llmB = two_nodes()
+    lk = ask(cA).json()["usage"]["loken"]
+    assert lk["nodes"] == [{"node": "B", "role": "answered", "tokens": len(REPLY) + 1}] and "decode_ms" in lk
+    cA, ctx, llmA, llmB = two_nodes(fail_after=5)
+    lk = ask(cA).json()["usage"]["loken"]
+    assert [n["role"] for n in lk["nodes"]] == ["left", "continued"] and lk["nodes"][0]["tokens"] == 5
+    assert lk["nodes"][1]["tokens"] == len(REPLY) + 1 - 5 and "ConnectionError" in lk["taken_back"]
+    # a plain local request carries its figures on the completions route as on the chat route
+    cB, _, _, _ = two_nodes(refuse=True)
+    assert "queue_ms" in ask(cB).json()["usage"]["loken"]
