@@ -46,6 +46,8 @@ class ModelRegistry:
         self.strict = strict
         self.lock = threading.Lock()
 
+    on_missing = None        # callable(name): may load the model and add it
+
     def add(self, llm: LLM, default: bool = False):
         with self.lock:
             self.models[llm.model_id] = llm
@@ -98,6 +100,16 @@ class ModelRegistry:
         return llm
 
     def _get(self, name: Optional[str]) -> LLM:
+        # a model whose keep-alive ended sleeps on the host (or was unloaded): the request that names it brings
+        # it back before the lookup (`api/context.py: ServerContext._wake`)
+        if self.on_missing is not None:
+            with self.lock:
+                known = bool(self.models) if not name else (name in self.models or name in self.aliases)
+            if not known:
+                try:
+                    self.on_missing(name)
+                except Exception:
+                    pass
         with self.lock:
             if name and name in self.aliases and self.aliases[name] in self.models:
                 return self.models[self.aliases[name]]

@@ -49,6 +49,7 @@ class ServerSettings:
     # requests go to the peer that is predicted to finish them sooner (cluster/routing.py, cluster/forward.py);
     # an answer a peer left unfinished is continued here only when both nodes hold the same bytes, unless
     # `resume_unverified` allows it anyway
+    keep_alive_s: float = 300.0             # a model idle this long leaves the device (-1: never); its files stay warm on the host
     route_requests: bool = False
     prefix_ask_min_tokens: int = 512        # prompts at least this long ask the peers how much of them they hold
     resume_unverified: bool = False
@@ -74,6 +75,12 @@ class ServerContext:
         self.opener = None                       # transport of pulls (store.download.Opener); None = requests
         from ..cluster.routing import RateMeter
 
+        from ..place.sleep import SleepRegistry
+
+        self.sleepers = SleepRegistry()          # models whose keep-alive ended: off the device, files warm on the host
+        self.asleep = {}                         # model id -> what it was loaded with, for every model the reaper took down
+        self.loader = None                       # callable(path, model_id=..., **kw) -> LLM; None = LLM.load
+        registry.on_missing = self._wake
         self.rate = RateMeter()                  # this node's decode rate, published by the gossip
         self.prefill_rate = RateMeter()          # and the rate at which it reads prompts
         self.ask_prefix = None                   # callable(addr, model, ids) -> cached tokens on that peer; None = HTTP
@@ -81,6 +88,53 @@ class ServerContext:
         self.membership = None
         self.router = None                       # cluster.routing.Router once a membership exists and routing is on
         self.open_peer_stream = None             # transport of forwarded requests; None = HTTP (cluster/forward.py)
+
+    # ---- keep-alive: a model that nobody used for a while leaves the device, and comes back when it is named ----
+    def reap_idle(self, now: Optional[float] = None) -> List[str]:
+        """Takes every model down whose last use is older than the keep-alive and that has no request in flight.
+        Its files are kept read into host memory when they fit the host's budget (`place/sleep.py`), so the next
+        request that names it loads without touching the disk; otherwise it is simply unloaded.  The last loaded
+        model is taken down as well: an idle server holds no device memory.  Returns the ids taken down."""
+        ka = self.settings.keep_alive_s
+        if ka is None or ka < 0:
+            return []
+        now = time.time() if now is None else now
+        gone = []
+        for m in self.registry.list():
+            if getattr(m.worker, "tickets", None):
+                continue
+            last = max(self.registry.last_used.get(m.model_id, 0.0), m.loaded_at)
+            if now - last < ka:
+                continue
+            path, kw = m.path, dict(getattr(m, "load_kwargs", None) or {})
+            if not self.registry.drop(m.model_id):
+                continue
+            rec = self.sleepers.put_to_sleep(m.model_id, path, kw)
+            if path:
+                self.asleep[m.model_id] = {"path": path, "kwargs": kw, "sleeping": rec is not None}
+            self.metrics.count("models_put_to_sleep" if rec is not None else "models_unloaded_idle")
+            gone.append(m.model_id)
+        return gone
+
+    def _wake(self, name: str):
+        """A request names a model the reaper took down: load it again (from warm pages when it sleeps)."""
+        if name not in self.asleep and not self.registry.list() and len(self.asleep) == 1:
+            name = next(iter(self.asleep))      # the only model this server holds, named loosely or not at all
+        info = self.asleep.pop(name, None) if name else None
+        if info is None:
+            return None
+        rec = self.sleepers.wake(name)
+        try:
+            load = self.loader
+            if load is None:
+                load = LLM.load
+            llm = load(info["path"], model_id=name, **info["kwargs"])
+            self.registry.add(llm, default=not self.registry.list())
+            self.metrics.count("models_woken")
+            return llm
+        finally:
+            if rec is not None:
+                rec.release()
 
     def _route(self, llm: LLM, ids, params: GenerationParams):
         """The peer that should answer this request, or None for this node."""

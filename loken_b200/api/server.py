@@ -915,9 +915,26 @@ def serve(registry: ModelRegistry, settings: Optional[ServerSettings] = None, cl
             except OSError as e:
                 print(f"loken: multicast discovery is off ({e}); the seed list still applies", flush=True)
         loop.start()
+    import threading
+
+    stop_reaper = threading.Event()
+
+    def reaper():
+        # the keep-alive: checked a few times per period, never more often than every five seconds
+        ka = app.state.ctx.settings.keep_alive_s
+        period = max(5.0, (ka if ka and ka > 0 else 60.0) / 4.0)
+        while not stop_reaper.wait(period):
+            try:
+                app.state.ctx.reap_idle()
+            except Exception as e:
+                print(f"loken: keep-alive check failed: {e}", flush=True)
+
+    if s.keep_alive_s is not None and s.keep_alive_s >= 0:
+        threading.Thread(target=reaper, name="keep-alive", daemon=True).start()
     try:
         uvicorn.run(app, host=s.host, port=s.port, log_level="info")
     finally:
+        stop_reaper.set()
         if loop is not None:
             loop.stop()
         if disco is not None:

@@ -30,6 +30,8 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--max-ctx", type=int)
     s.add_argument("--draft-model")
     s.add_argument("--draft-k", type=int)
+    s.add_argument("--keep-alive", help="how long a model stays on the device after its last request (5m, 300s, 1h, a bare "
+                                        "number is seconds; -1 keeps it for ever); OLLAMA_KEEP_ALIVE is read too")
     s.add_argument("--lora", help="PEFT adapter directory merged into a bf16 / block-fp8 checkpoint at load")
     s.add_argument("--tp-sum", choices=["boundary", "push", "fused", "nccl"],
                    help="how tensor-parallel layers are summed (boundary = one kernel per layer boundary: "
@@ -52,6 +54,10 @@ def apply_flags(cfg, args):
         v = getattr(args, name, None)
         if v is not None:
             setattr(target, attr, v)
+    if getattr(args, "keep_alive", None) is not None:
+        from ..config import _parse_duration
+
+        i.keep_alive_s = _parse_duration(args.keep_alive)
     return cfg.validate()
 
 
@@ -123,6 +129,7 @@ def serve(cfg, requant=None) -> int:
                                    rate_limit_burst=s.rate_limit_burst, max_body_bytes=s.max_body_mb << 20,
                                    request_timeout_s=s.request_timeout_s, gate_slots=i.max_seqs,
                                    prefill_peer=i.prefill_peer, route_requests=cfg.cluster.route_requests,
+                                   keep_alive_s=(i.keep_alive_s if world == 1 else -1.0),
                                    resume_unverified=cfg.cluster.resume_unverified, node_id=cfg.cluster.node_id),
           cluster=cfg.cluster, catalogue=catalogue)
     return 0

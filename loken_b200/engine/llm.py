@@ -291,6 +291,9 @@ class LLM:
         (random-init weights).  `lora`: a PEFT adapter directory, or a list of directories or
         (directory, weight) pairs, merged into a bf16 / block-fp8 checkpoint as it loads."""
         dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        # what a reload after a keep-alive needs to bring the same model back (one rank only)
+        kept = {k: v for k, v in dict(engine_kw, requant=requant, kv_format=kv_format, lora=lora).items()
+                if v is not None and isinstance(v, (int, float, str, bool, list, tuple))} if tp_size == 1 else {}
         group = None
         watchdog = None
         draft = engine_kw.pop("draft", None)       # (model, k): a drafter attached on every rank before wrapping
@@ -349,6 +352,7 @@ class LLM:
                 tk = ByteTokenizer(w.cfg.vocab)
             eng = LLMEngine(w.cfg, weights=w, device=dev, tp_rank=tp_rank, tp_size=tp_size, comm=comm, **engine_kw)
             llm = cls(wrap(eng), tk, model_id or os.path.basename(os.path.normpath(model)), hf, path=model)
+            llm.load_kwargs = kept
             llm.control_group, llm.watchdog = group, watchdog
             return llm
         if lora:
@@ -362,6 +366,7 @@ class LLM:
             eng = LLMEngine(w.cfg, weights=w, device=dev, tp_rank=tp_rank, tp_size=tp_size, comm=comm, **engine_kw)
             name = model_id or os.path.splitext(os.path.basename(model))[0]
             llm = cls(wrap(eng), tk, name, meta, path=model)
+            llm.load_kwargs = kept
             llm.control_group, llm.watchdog = group, watchdog
             return llm
         cfg = get_config(model)

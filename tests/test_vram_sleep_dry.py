@@ -134,3 +134,54 @@ def test_give_way_is_one_rung_at_a_time():
     assert r.reclaimed == [("pool", 5)] and not r.evicted and models == ["b"]       # a reclaimer gave: nobody is unloaded
     va.unregister("pool")
     assert va.give_way().evicted == ["b"] and not va.give_way().evicted
+
+
+def test_keep_alive_takes_an_idle_model_down_and_a_request_brings_it_back(tmp_path):
+    """The reaper unloads a model nobody used for the keep-alive (files kept warm when they fit the host), and the
+    next request that names it, or names nothing while it is the only one, loads it again with what it was loaded with."""
+    from fastapi.testclient import TestClient
+
+    from fakes import fake_llm
+    from loken_b200.api.common import ModelRegistry
+    from loken_b200.api.context import ServerSettings
+    from loken_b200.api.server import create_app
+
+    f = tmp_path / "m.gguf"
+    f.write_bytes(b"x" * 4096)
+    reg = ModelRegistry()
+    llm = fake_llm(model_id="m1")
+    llm.path, llm.load_kwargs = str(f), {"max_seqs": 8}
+    reg.add(llm)
+    app = create_app(reg, ServerSettings(keep_alive_s=60.0))
+    ctx = app.state.ctx
+    c = TestClient(app)
+    loads = []
+
+    def loader(path, model_id=None, **kw):
+        loads.append((path, model_id, kw))
+        m = fake_llm(model_id=model_id)
+        m.path, m.load_kwargs = path, kw
+        return m
+
+    ctx.loader = loader
+    assert c.post("/v1/completions", json={"model": "m1", "prompt": "x", "max_tokens": 2}).status_code == 200
+    import time as _t
+
+    now = _t.time()
+    assert ctx.reap_idle(now + 30) == []                                      # used half a minute ago: stays
+    assert ctx.reap_idle(now + 120) == ["m1"] and reg.list() == []
+    assert ctx.asleep["m1"]["sleeping"] and ctx.sleepers.bytes_held() >= 4096   # its file stays read into host memory
+    assert ctx.metrics.counters["models_put_to_sleep"] == 1
+    r = c.post("/v1/completions", json={"model": "m1", "prompt": "x", "max_tokens": 2})
+    assert r.status_code == 200 and loads == [(str(f), "m1", {"max_seqs": 8})]
+    assert [m.model_id for m in reg.list()] == ["m1"] and ctx.sleepers.bytes_held() == 0 and ctx.asleep == {}
+    # asleep again; a request that names nothing wakes the only model there is
+    assert ctx.reap_idle(_t.time() + 120) == ["m1"]
+    assert c.post("/v1/completions", json={"prompt": "x", "max_tokens": 2}).status_code == 200 and len(loads) == 2
+    # -1 keeps a model for ever; a model with requests in flight is never taken down
+    ctx.settings.keep_alive_s = -1
+    assert ctx.reap_idle(_t.time() + 1e6) == []
+    ctx.settings.keep_alive_s = 1.0
+    reg.list()[0].worker.tickets[99] = object()
+    assert ctx.reap_idle(_t.time() + 1e6) == []
+    reg.list()[0].worker.tickets.pop(99)
