@@ -146,6 +146,7 @@ def build_parser() -> argparse.ArgumentParser:
     la.add_argument("--config", action="store_true", help="print or write the configuration and start nothing")
     la.add_argument("args", nargs="*", help="arguments handed to the agent, after --")
     sub.add_parser("popular")
+    sub.add_parser("peers", help="the nodes this server sees: alive, suspicion, round trip, what each serves")
     ca = sub.add_parser("calibrate")
     ca.add_argument("model", help="the checkpoint: a path or a name in the model stores")
     ca.add_argument("-n", "--name", required=True, help="the record's name, which convert refers to")
@@ -309,6 +310,15 @@ def main(argv=None, out=sys.stdout) -> int:
             last = ev
             p(json.dumps(ev))
         return 0 if last is not None and "error" not in last else 1
+    elif args.cmd == "peers":
+        rep = cl.json("GET", "/api/cluster/peers")
+        if not rep.get("clustered"):
+            p("this server sees no other node ([cluster] peers or discovery join it to others)")
+        for n in rep.get("peers", []):
+            st = n.get("state") or {}
+            rtt = "-" if n.get("rtt_ms") is None else f"{n['rtt_ms']:.1f} ms"
+            p(f"{n['node_id']:20s} {'self ' if n['is_self'] else ('alive' if n['alive'] else 'gone ')} phi {n['phi']:5.2f}  rtt {rtt:>9s}  "
+              f"{st.get('tok_per_s', 0.0):7.1f} tok/s  {', '.join(st.get('models', [])) or '-'}")
     elif args.cmd == "plan-cut":
         from ..cluster.cut_plan import plan_from_request
 
