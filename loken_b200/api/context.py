@@ -107,6 +107,8 @@ class ServerContext:
             if now - last < ka:
                 continue
             path, kw = m.path, dict(getattr(m, "load_kwargs", None) or {})
+            if not path:
+                continue             # random-init weights of a built-in shape: nothing on disk could bring them back
             if not self.registry.drop(m.model_id):
                 continue
             rec = self.sleepers.put_to_sleep(m.model_id, path, kw)

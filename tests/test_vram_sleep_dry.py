@@ -185,3 +185,17 @@ def test_keep_alive_takes_an_idle_model_down_and_a_request_brings_it_back(tmp_pa
     reg.list()[0].worker.tickets[99] = object()
     assert ctx.reap_idle(_t.time() + 1e6) == []
     reg.list()[0].worker.tickets.pop(99)
+
+
+def test_a_model_without_files_is_never_reaped():
+    from fakes import fake_llm
+    from loken_b200.api.common import ModelRegistry
+    from loken_b200.api.context import ServerSettings
+    from loken_b200.api.server import create_app
+
+    reg = ModelRegistry()
+    reg.add(fake_llm(model_id="shape"))                 # no path: random weights of a built-in shape
+    ctx = create_app(reg, ServerSettings(keep_alive_s=1.0)).state.ctx
+    import time as _t
+
+    assert ctx.reap_idle(_t.time() + 1e6) == [] and [m.model_id for m in reg.list()] == ["shape"]
